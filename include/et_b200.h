@@ -1,0 +1,249 @@
+/*
+ * et_b200 — C ABI of the B200 (sm_100a) encoder-layer hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA
+ * stream, returns an int status (0 = ok, negative = error, see et_status_string), never
+ * throws, never synchronises the device and never allocates: scratch memory is passed
+ * in by the caller.  One host thread per GPU may call into the library concurrently.
+ *
+ * Layout conventions (all from the reference, cctry/SCpaper-2021):
+ *   - activations: row-major fp16 [tokens, features], tokens = batch * seq, heads are
+ *     contiguous feature ranges (Attention/OTFkernel_full.h:34,49,116);
+ *   - dense weight: W[out, in] row-major, y = x W^T + b (Linear/Linear.h:11-15);
+ *   - index arrays: int32.
+ *
+ * The reference has no C ABI (it is a C++17 template library); each function below
+ * names the reference member function or kernel launch it stands in for.
+ */
+#ifndef ET_B200_H
+#define ET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* fp16 values cross the ABI as raw 16-bit words (IEEE binary16). */
+typedef uint16_t et_half;
+/* cudaStream_t crosses the ABI as an opaque pointer. */
+typedef void* et_stream;
+
+/* ---- status codes --------------------------------------------------------------- */
+#define ET_OK 0
+#define ET_ERR_INVALID_ARG (-1)   /* null pointer, non-positive size, bad enum        */
+#define ET_ERR_ALIGNMENT (-2)     /* pointer or leading dimension not 16-byte aligned  */
+#define ET_ERR_SHAPE (-3)         /* a size the kernels do not support (see each call) */
+#define ET_ERR_INDEX (-4)         /* corrupt index array found by a validator          */
+#define ET_ERR_CUDA (-5)          /* a CUDA runtime / driver call failed               */
+#define ET_ERR_WORKSPACE (-6)     /* scratch buffer missing or too small               */
+#define ET_ERR_DEVICE_TIMEOUT (-7)/* a kernel gave up on a bounded wait                */
+#define ET_ERR_NO_DEVICE (-8)     /* no sm_100 device is current                       */
+
+const char* et_status_string(int status);
+
+/* Library version, and the compute capability the kernels were built for (100). */
+int et_version(void);
+int et_built_for_sm(void);
+
+/* Reads (and clears) the device-side error word of the current device.  Kernels never
+ * trap: a bounded wait that runs out records a code there and the kernel returns.
+ * This call synchronises the device.  *code = 0 when no kernel reported a problem.
+ * Replaces the reference's cudaChk/assert/exit(1) convention (lib/utils.cu:28-35). */
+int et_device_error(int* code);
+
+/* ---- activation / epilogue selectors ------------------------------------------- */
+#define ET_ACT_NONE 0
+#define ET_ACT_RELU 1 /* Encoder/Encoder.h:29-32                                       */
+#define ET_ACT_GELU 2 /* tanh form, constants of Encoder/Encoder.cu:25-39              */
+
+/* ---- attention mask selectors --------------------------------------------------- */
+#define ET_MASK_NONE 0     /* all keys visible                                        */
+#define ET_MASK_CAUSAL 1   /* key j <= query i: the mask Attention.h:97-104 builds     */
+#define ET_MASK_PADDING 2  /* keys >= valid_len[b] dropped                             */
+#define ET_MASK_ADDITIVE 3 /* fp16 [seq, seq] added to the scaled scores (0 / -inf)    */
+
+/* =================================================================================
+ * Linear layers:  Y[T, out] = act( X[T, in] . W^T + bias )
+ * bias may be NULL (treated as zero).  X, Y and weight pointers must be 16-byte
+ * aligned; in % 16 == 0 and out % 16 == 0 (the reference's own precondition).
+ * ================================================================================= */
+
+/* Dense weights W[out, in].
+ * Stands in for Linear<base_mat>::forward (Linear/Linear.h:53-64: cuBLAS GEMM followed
+ * by a separate bias pass) and, with act != NONE, for the act<> pass of
+ * Encoder/Encoder.h:27-37. */
+int et_linear_dense_fwd(const et_half* X, const et_half* W, const et_half* bias, et_half* Y,
+                        int T, int in, int out, int act, et_stream stream);
+
+/* 16x16 tile-CSR weights: row_ptr[out/16 + 1], row_off[nnz] (input block column,
+ * ascending inside a block row), tiles[nnz][16][16] row-major [out_local][in_local].
+ * Only stored tiles are loaded.  Stands in for Linear<tile_mat>::forward
+ * (Linear/SPMM_tile.cu:312-324 launching the kernel at :250-310). */
+int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,
+                       int nnz_tiles, const et_half* bias, const et_half* X, et_half* Y, int T,
+                       int in, int out, int act, et_stream stream);
+
+/* Row-pruned weights: rows[nn_row, in] are the weights of output features
+ * row_id[0..nn_row) (ascending); every other output column receives the bias alone.
+ * Stands in for Linear<row_mat>::forward(half*, half*) (Linear/SPMM_row.cu:62-75:
+ * cuBLAS on the kept rows, scatter kernel :14-30, bias pass).  Y needs no pre-zeroing. */
+int et_linear_row_fwd(const int32_t* row_id, const et_half* rows, int nn_row,
+                      const et_half* bias, const et_half* X, et_half* Y, int T, int in, int out,
+                      int act, et_stream stream);
+
+/* Row-pruned weights with COMPRESSED output Yc[T, nn_row] (column k = feature row_id[k]),
+ * bias of the kept features added.  Stands in for Linear<row_mat>::forward(col_mat*, ...)
+ * (Linear/SPMM_row.cu:78-95), which feeds the pruned-V attention. */
+int et_linear_row_compressed_fwd(const int32_t* row_id, const et_half* rows, int nn_row,
+                                 const et_half* bias, const et_half* X, et_half* Yc, int T,
+                                 int in, et_stream stream);
+
+/* Column-pruned weights: cols[out, nn_col] multiply the input features col_id[0..nn_col).
+ * scratch must hold T * nn_col fp16 values (the gathered activations).
+ * Stands in for Linear<col_mat>::forward (Linear/SPMM_col.cu:57-69: gather kernel :8-23
+ * into the operator's workspace, cuBLAS, bias pass). */
+int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
+                      const et_half* bias, const et_half* X, et_half* Y, int T, int in, int out,
+                      int act, et_half* scratch, size_t scratch_bytes, et_stream stream);
+
+/* 1x16-vector weights: tile_idx[(out/16) * (in/16 + 1)], row_idx[nvec], data[nvec][16]
+ * (mat_type/mat1x16/mat1x16.h:9-15).  Stands in for Linear<mat1x16>::forward
+ * (Linear/SPMM1x16.cu:89-115, whose body the reference leaves empty; the intended
+ * product of :56-83 is computed). */
+int et_linear_1x16_fwd(const int32_t* tile_idx, const int32_t* row_idx, const et_half* data,
+                       int nvec, const et_half* bias, const et_half* X, et_half* Y, int T, int in,
+                       int out, int act, et_stream stream);
+
+/* CSR weights W[out, in].  Stands in for Linear<csr_mat>::forward (Linear/cusp.cu:23-50:
+ * cuSPARSE SpMM + bias pass). */
+int et_linear_csr_fwd(const int32_t* indptr, const int32_t* indices, const et_half* data,
+                      int nnz, const et_half* bias, const et_half* X, et_half* Y, int T, int in,
+                      int out, int act, et_stream stream);
+
+/* Host-side validators for index arrays that live in HOST memory (call before upload).
+ * Return ET_OK or ET_ERR_INDEX; they never touch the GPU. */
+int et_validate_tile_mat(const int32_t* row_ptr, const int32_t* row_off, int nnz_tiles, int in,
+                         int out);
+int et_validate_id_list(const int32_t* ids, int n, int limit, int require_sorted);
+int et_validate_1x16(const int32_t* tile_idx, const int32_t* row_idx, int nvec, int in, int out);
+int et_validate_csr(const int32_t* indptr, const int32_t* indices, int nnz, int in, int out);
+
+/* =================================================================================
+ * Normalisation and element-wise passes
+ * ================================================================================= */
+
+/* out = LayerNorm(src + skip) * gamma + beta, eps 1e-5, statistics in fp32.
+ * Stands in for SkipLayerNorm::forward (SkipLayerNorm/SkipLayerNorm.cu:73-82). */
+int et_skip_layernorm_fwd(const et_half* src, const et_half* skip, const et_half* gamma,
+                          const et_half* beta, et_half* out, int rows, int size, et_stream stream);
+
+/* out = LayerNorm(src) * gamma + beta.  Stands in for LayerNorm::forward
+ * (LayerNorm/LayerNorm.cu:51-57), without its per-call device synchronisation. */
+int et_layernorm_fwd(const et_half* src, const et_half* gamma, const et_half* beta, et_half* out,
+                     int rows, int size, et_stream stream);
+
+/* In-place capable activation pass over n values.  Stands in for act<RELU_OP|GELU_OP>
+ * (Encoder/Encoder.h:27-37) and GELU::computeGelu (Encoder/Encoder.cu:41-68). */
+int et_act_fwd(const et_half* in, et_half* out, size_t n, int act, et_stream stream);
+
+/* data[r, c] += bias[c]; the reference's bias map (Linear/Linear.h:57-63). */
+int et_bias_add_fwd(et_half* data, const et_half* bias, int rows, int cols, et_stream stream);
+
+/* =================================================================================
+ * Attention
+ * ================================================================================= */
+
+/* Z[b*seq+i, h*dh_v ..] = softmax_j( scale * Q_i.K_j + mask_ij ) V_j  for every
+ * sequence b and head h, scores never written to memory.
+ * Q/K/V/Z are [batch*seq, ld*] with head h at feature offset h*dh; the three inputs
+ * may alias one fused [Q | K | V] projection buffer (ldq = ldk = ldv = 2*kdim + vdim).
+ * dh_qk, dh_v: multiples of 16, at most 128.  ld*: multiples of 8.
+ * mask: fp16 [seq, seq] for ET_MASK_ADDITIVE, else NULL; valid_len: int32[batch] for
+ * ET_MASK_PADDING, else NULL.  A query whose keys are all dropped yields zeros.
+ * Stands in for Multihead_atttion<OTF_attn_full> (Attention/Attention.cu:80-95 launching
+ * Attention/OTFkernel_full.h:17-125) and the fused-QKV launch of
+ * Attention/Attention.h:246-265 (Attention/Attention_single.cu:10-108). */
+int et_attention_fwd(const et_half* Q, const et_half* K, const et_half* V, et_half* Z, int batch,
+                     int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,
+                     int mask_kind, const et_half* mask, const int32_t* valid_len, float scale,
+                     et_stream stream);
+
+/* Attention whose V is column-compressed: Vc[T, nnz_col] holds the value features
+ * col_id[0..nnz_col) (ascending); head_ptr[h]..head_ptr[h+1] delimits head h's entries
+ * (mat_type/col_mat/col_mat.cu:34-58).  Z[T, nhead*dh_v] is written in full: pruned
+ * features are zero.  Stands in for Multihead_atttion<Prune_attn>
+ * (Attention/Attention.cu:55-78, kernel Attention/kernels.cu:363-460). */
+int et_attention_pruned_v_fwd(const et_half* Q, const et_half* K, const et_half* Vc,
+                              const int32_t* col_id, const int32_t* head_ptr, int nnz_col,
+                              et_half* Z, int batch, int seq, int nhead, int dh_qk, int dh_v,
+                              int ldq, int ldk, int ldz, int mask_kind, const et_half* mask,
+                              const int32_t* valid_len, float scale, et_stream stream);
+
+/* Attention followed by a tile-CSR output projection in one call:
+ * out = tileLinear_O( attention(Q, K, V) ) + bias_o.  Z[T, nhead*dh_v] is caller scratch.
+ * Stands in for Multihead_atttion_fuseO (Attention/kernel_fuseO.cu:254-290). */
+int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,
+                            const et_half* mask, et_half* Z, const int32_t* o_row_ptr,
+                            const int32_t* o_row_off, const et_half* o_tiles, int o_nnz,
+                            const et_half* o_bias, et_half* out, int batch, int seq, int nhead,
+                            int dh_qk, int dh_v, int ldq, int ldk, int ldv, int emdim,
+                            int mask_kind, const int32_t* valid_len, float scale,
+                            et_stream stream);
+
+/* Pre-multiplied V.O attention: out[t, :] = sum_h P_h[t, :] . VO_h + bias_o with
+ * VO given as [batch][nhead][seq][emdim] (Fused_attention/Linear_VO.h:38-58).
+ * Heads are reduced in a fixed order (the reference uses half2 atomics).
+ * Stands in for Fused_Multihead_attention<OTF_fused_attn>
+ * (Fused_attention/Fused_attention.cu:231-253, kernel :10-116). */
+int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half* VO,
+                              const et_half* bias_o, et_half* out, int batch, int seq, int nhead,
+                              int dh_qk, int emdim, int ldq, int ldk, int mask_kind,
+                              const et_half* mask, const int32_t* valid_len, float scale,
+                              et_stream stream);
+
+/* VO[b][h] = X_b . W_VO[h] + bias[h] for W_VO [nhead][emdim(in)][emdim(out)].
+ * Stands in for Linear_VO::forward (Fused_attention/Linear_VO.h:38-58 + Linear_VO.cu:32-45). */
+int et_linear_vo_fwd(const et_half* X, const et_half* Wvo_t, const et_half* bias, et_half* VO,
+                     int batch, int seq, int nhead, int emdim, et_stream stream);
+
+/* =================================================================================
+ * Whole encoder layer (post-LN), the call Encoder<config>::forward makes
+ * (Encoder/Encoder.h:81-96):
+ *   a = O(attention(QKV(x)));  y = LN1(a + x);  out = LN2(W2 act(W1 y + b1) + b2 + y)
+ * ================================================================================= */
+#define ET_FMT_DENSE 0
+#define ET_FMT_TILE 1
+
+typedef struct {
+    int format;             /* ET_FMT_DENSE or ET_FMT_TILE                              */
+    int in, out;
+    const et_half* weight;  /* dense: W[out, in]; tile: tiles[nnz][256]                 */
+    const int32_t* row_ptr; /* tile only                                                */
+    const int32_t* row_off; /* tile only                                                */
+    int nnz_tiles;          /* tile only                                                */
+    const et_half* bias;    /* [out] or NULL                                            */
+} et_linear_t;
+
+typedef struct {
+    et_linear_t qkv;  /* hidden -> 2*kdim + vdim, output features ordered Q | K | V     */
+    et_linear_t o;    /* vdim -> hidden                                                 */
+    et_linear_t ffn1; /* hidden -> ff                                                   */
+    et_linear_t ffn2; /* ff -> hidden                                                   */
+    const et_half *ln1_gamma, *ln1_beta, *ln2_gamma, *ln2_beta; /* [hidden]              */
+    int hidden, nhead, kdim, vdim, ff;
+    int act;          /* ET_ACT_RELU or ET_ACT_GELU                                     */
+} et_encoder_layer_t;
+
+size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq);
+
+int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_half* out,
+                         int batch, int seq, int mask_kind, const et_half* mask,
+                         const int32_t* valid_len, void* workspace, size_t workspace_bytes,
+                         et_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ET_B200_H */

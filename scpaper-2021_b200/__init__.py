@@ -1,0 +1,365 @@
+"""Python harness over the C ABI of libet_b200.so (include/et_b200.h).
+
+PyTorch is used only to own device memory and streams; every computation goes through the
+C ABI with raw device pointers.  There is no fallback: if the CUDA library is missing or a
+call reports an error, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_size_t, c_void_p
+
+from . import synth  # noqa: F401
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libet_b200.so")
+
+ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
+MASK_NONE, MASK_CAUSAL, MASK_PADDING, MASK_ADDITIVE = 0, 1, 2, 3
+FMT_DENSE, FMT_TILE = 0, 1
+
+# Every symbol include/et_b200.h declares (checked by the CPU test-suite against the header).
+ABI_SYMBOLS = [
+    "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
+    "et_linear_dense_fwd", "et_linear_tile_fwd", "et_linear_row_fwd",
+    "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_1x16_fwd",
+    "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
+    "et_validate_csr", "et_skip_layernorm_fwd", "et_layernorm_fwd", "et_act_fwd",
+    "et_bias_add_fwd", "et_attention_fwd", "et_attention_pruned_v_fwd",
+    "et_attention_fuse_o_fwd", "et_fused_vo_attention_fwd", "et_linear_vo_fwd",
+    "et_encoder_layer_workspace_bytes", "et_encoder_layer_fwd",
+]
+
+
+class EtError(RuntimeError):
+    pass
+
+
+class LinearDesc(ctypes.Structure):
+    """et_linear_t"""
+    _fields_ = [("format", c_int), ("in_", c_int), ("out", c_int), ("weight", c_void_p),
+                ("row_ptr", c_void_p), ("row_off", c_void_p), ("nnz_tiles", c_int),
+                ("bias", c_void_p)]
+
+
+class EncoderLayerDesc(ctypes.Structure):
+    """et_encoder_layer_t"""
+    _fields_ = [("qkv", LinearDesc), ("o", LinearDesc), ("ffn1", LinearDesc), ("ffn2", LinearDesc),
+                ("ln1_gamma", c_void_p), ("ln1_beta", c_void_p), ("ln2_gamma", c_void_p),
+                ("ln2_beta", c_void_p), ("hidden", c_int), ("nhead", c_int), ("kdim", c_int),
+                ("vdim", c_int), ("ff", c_int), ("act", c_int)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the CUDA library; raises if it has not been built (no CPU fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise EtError(f"{LIB_PATH} is missing: run `python scpaper-2021_b200/build.py` "
+                          "(the library has no CPU fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        L.et_status_string.restype = ctypes.c_char_p
+        L.et_status_string.argtypes = [c_int]
+        L.et_encoder_layer_workspace_bytes.restype = c_size_t
+        L.et_encoder_layer_workspace_bytes.argtypes = [c_void_p, c_int, c_int]
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str = "") -> None:
+    if status != 0:
+        raise EtError(f"{what}: status {status} ({lib().et_status_string(status).decode()})")
+
+
+def device_error() -> int:
+    """Synchronises and returns (then clears) the device error word; 0 = no kernel complained."""
+    code = c_int(0)
+    check(lib().et_device_error(ctypes.byref(code)), "et_device_error")
+    return code.value
+
+
+def _p(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _empty(shape, like):
+    import torch
+    return torch.empty(shape, dtype=torch.float16, device=like.device)
+
+
+# ---- Linear layers ------------------------------------------------------------------------
+
+def linear_dense(x, w, bias=None, act=ACT_NONE):
+    T, inn = x.shape
+    out = w.shape[0]
+    y = _empty((T, out), x)
+    check(lib().et_linear_dense_fwd(_p(x), _p(w), _p(bias), _p(y), c_int(T), c_int(inn),
+                                    c_int(out), c_int(act), _stream()), "et_linear_dense_fwd")
+    return y
+
+
+def linear_tile(x, row_ptr, row_off, tiles, out, bias=None, act=ACT_NONE):
+    T, inn = x.shape
+    y = _empty((T, out), x)
+    nnz = int(tiles.shape[0]) if tiles is not None else 0
+    check(lib().et_linear_tile_fwd(_p(row_ptr), _p(row_off) if nnz else None,
+                                   _p(tiles) if nnz else None, c_int(nnz), _p(bias), _p(x), _p(y),
+                                   c_int(T), c_int(inn), c_int(out), c_int(act), _stream()),
+          "et_linear_tile_fwd")
+    return y
+
+
+def linear_row(x, row_id, rows, out, bias=None, act=ACT_NONE):
+    T, inn = x.shape
+    y = _empty((T, out), x)
+    nn = int(row_id.shape[0])
+    check(lib().et_linear_row_fwd(_p(row_id) if nn else None, _p(rows) if nn else None, c_int(nn),
+                                  _p(bias), _p(x), _p(y), c_int(T), c_int(inn), c_int(out),
+                                  c_int(act), _stream()), "et_linear_row_fwd")
+    return y
+
+
+def linear_row_compressed(x, row_id, rows, bias=None):
+    T, inn = x.shape
+    nn = int(row_id.shape[0])
+    y = _empty((T, nn), x)
+    check(lib().et_linear_row_compressed_fwd(_p(row_id), _p(rows), c_int(nn), _p(bias), _p(x),
+                                             _p(y), c_int(T), c_int(inn), _stream()),
+          "et_linear_row_compressed_fwd")
+    return y
+
+
+def linear_col(x, col_id, cols, bias=None, act=ACT_NONE, scratch=None):
+    T, inn = x.shape
+    out, nn = cols.shape
+    y = _empty((T, out), x)
+    if scratch is None:
+        scratch = _empty((T, nn), x)
+    check(lib().et_linear_col_fwd(_p(col_id), _p(cols), c_int(nn), _p(bias), _p(x), _p(y),
+                                  c_int(T), c_int(inn), c_int(out), c_int(act), _p(scratch),
+                                  c_size_t(scratch.numel() * 2), _stream()), "et_linear_col_fwd")
+    return y
+
+
+def linear_1x16(x, tile_idx, row_idx, data, out, bias=None, act=ACT_NONE):
+    T, inn = x.shape
+    y = _empty((T, out), x)
+    nvec = int(row_idx.shape[0])
+    check(lib().et_linear_1x16_fwd(_p(tile_idx), _p(row_idx) if nvec else None,
+                                   _p(data) if nvec else None, c_int(nvec), _p(bias), _p(x), _p(y),
+                                   c_int(T), c_int(inn), c_int(out), c_int(act), _stream()),
+          "et_linear_1x16_fwd")
+    return y
+
+
+def linear_csr(x, indptr, indices, data, out, bias=None, act=ACT_NONE):
+    T, inn = x.shape
+    y = _empty((T, out), x)
+    nnz = int(indices.shape[0])
+    check(lib().et_linear_csr_fwd(_p(indptr), _p(indices) if nnz else None,
+                                  _p(data) if nnz else None, c_int(nnz), _p(bias), _p(x), _p(y),
+                                  c_int(T), c_int(inn), c_int(out), c_int(act), _stream()),
+          "et_linear_csr_fwd")
+    return y
+
+
+# ---- normalisation / element-wise ---------------------------------------------------------
+
+def skip_layernorm(src, skip, gamma, beta):
+    rows, size = src.shape
+    out = _empty((rows, size), src)
+    check(lib().et_skip_layernorm_fwd(_p(src), _p(skip), _p(gamma), _p(beta), _p(out), c_int(rows),
+                                      c_int(size), _stream()), "et_skip_layernorm_fwd")
+    return out
+
+
+def layernorm(src, gamma, beta):
+    rows, size = src.shape
+    out = _empty((rows, size), src)
+    check(lib().et_layernorm_fwd(_p(src), _p(gamma), _p(beta), _p(out), c_int(rows), c_int(size),
+                                 _stream()), "et_layernorm_fwd")
+    return out
+
+
+def act(x, kind, inplace=False):
+    out = x if inplace else _empty(tuple(x.shape), x)
+    check(lib().et_act_fwd(_p(x), _p(out), c_size_t(x.numel()), c_int(kind), _stream()),
+          "et_act_fwd")
+    return out
+
+
+def bias_add_(data, bias):
+    rows, cols = data.shape
+    check(lib().et_bias_add_fwd(_p(data), _p(bias), c_int(rows), c_int(cols), _stream()),
+          "et_bias_add_fwd")
+    return data
+
+
+# ---- attention ----------------------------------------------------------------------------
+
+def attention(q, k, v, batch, seq, nhead, dh_qk, dh_v, mask_kind=MASK_NONE, mask=None,
+              valid_len=None, scale=None, ldq=None, ldk=None, ldv=None):
+    """q/k/v: fp16 tensors (possibly views into one fused buffer); ld* default to the row
+    stride of each tensor."""
+    ldq = q.stride(0) if ldq is None else ldq
+    ldk = k.stride(0) if ldk is None else ldk
+    ldv = v.stride(0) if ldv is None else ldv
+    z = _empty((batch * seq, nhead * dh_v), q)
+    scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
+    check(lib().et_attention_fwd(_p(q), _p(k), _p(v), _p(z), c_int(batch), c_int(seq),
+                                 c_int(nhead), c_int(dh_qk), c_int(dh_v), c_int(ldq), c_int(ldk),
+                                 c_int(ldv), c_int(nhead * dh_v), c_int(mask_kind), _p(mask),
+                                 _p(valid_len), c_float(scale), _stream()), "et_attention_fwd")
+    return z
+
+
+def attention_pruned_v(q, k, vc, col_id, head_ptr, batch, seq, nhead, dh_qk, dh_v,
+                       mask_kind=MASK_NONE, mask=None, valid_len=None, scale=None):
+    z = _empty((batch * seq, nhead * dh_v), q)
+    scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
+    check(lib().et_attention_pruned_v_fwd(_p(q), _p(k), _p(vc), _p(col_id), _p(head_ptr),
+                                          c_int(int(col_id.shape[0])), _p(z), c_int(batch),
+                                          c_int(seq), c_int(nhead), c_int(dh_qk), c_int(dh_v),
+                                          c_int(q.stride(0)), c_int(k.stride(0)),
+                                          c_int(nhead * dh_v), c_int(mask_kind), _p(mask),
+                                          _p(valid_len), c_float(scale), _stream()),
+          "et_attention_pruned_v_fwd")
+    return z
+
+
+def attention_fuse_o(q, k, v, o_row_ptr, o_row_off, o_tiles, o_bias, batch, seq, nhead, dh_qk,
+                     dh_v, emdim, mask_kind=MASK_NONE, mask=None, valid_len=None, scale=None):
+    z = _empty((batch * seq, nhead * dh_v), q)
+    out = _empty((batch * seq, emdim), q)
+    scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
+    check(lib().et_attention_fuse_o_fwd(_p(q), _p(k), _p(v), _p(mask), _p(z), _p(o_row_ptr),
+                                        _p(o_row_off), _p(o_tiles), c_int(int(o_tiles.shape[0])),
+                                        _p(o_bias), _p(out), c_int(batch), c_int(seq),
+                                        c_int(nhead), c_int(dh_qk), c_int(dh_v),
+                                        c_int(q.stride(0)), c_int(k.stride(0)),
+                                        c_int(v.stride(0)), c_int(emdim), c_int(mask_kind),
+                                        _p(valid_len), c_float(scale), _stream()),
+          "et_attention_fuse_o_fwd")
+    return out
+
+
+def linear_vo(x, w_vo, bias, batch, seq, nhead, emdim):
+    vo = _empty((batch * nhead * seq, emdim), x)
+    check(lib().et_linear_vo_fwd(_p(x), _p(w_vo), _p(bias), _p(vo), c_int(batch), c_int(seq),
+                                 c_int(nhead), c_int(emdim), _stream()), "et_linear_vo_fwd")
+    return vo
+
+
+def fused_vo_attention(q, k, vo, bias_o, batch, seq, nhead, dh_qk, emdim, mask_kind=MASK_NONE,
+                       mask=None, valid_len=None, scale=None):
+    out = _empty((batch * seq, emdim), q)
+    scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
+    check(lib().et_fused_vo_attention_fwd(_p(q), _p(k), _p(vo), _p(bias_o), _p(out), c_int(batch),
+                                          c_int(seq), c_int(nhead), c_int(dh_qk), c_int(emdim),
+                                          c_int(q.stride(0)), c_int(k.stride(0)),
+                                          c_int(mask_kind), _p(mask), _p(valid_len),
+                                          c_float(scale), _stream()),
+          "et_fused_vo_attention_fwd")
+    return out
+
+
+# ---- encoder layer / stack ----------------------------------------------------------------
+
+class EncoderLayer:
+    """Device-resident weights of one encoder layer plus the et_encoder_layer_t that
+    describes them.  `weights` is the dict of numpy fp16 arrays synth.encoder_layer_weights
+    returns; tile_sparse=True stores the four Linear layers in tile-CSR form."""
+
+    def __init__(self, weights: dict, nhead: int, act_kind: int = ACT_GELU, device="cuda",
+                 tile_sparse: bool = False):
+        import numpy as np
+        import torch
+        self._keep = []
+
+        def dev(a):
+            t = torch.from_numpy(np.ascontiguousarray(a)).to(device)
+            self._keep.append(t)
+            return t
+
+        def lin(wname, bname):
+            W = weights[wname]
+            d = LinearDesc()
+            d.out, d.in_ = int(W.shape[0]), int(W.shape[1])
+            d.bias = weights[bname] is not None and dev(weights[bname]).data_ptr() or None
+            if tile_sparse:
+                rp, ro, tiles = synth.dense_to_tile(W)
+                d.format = FMT_TILE
+                d.row_ptr = dev(rp).data_ptr()
+                d.nnz_tiles = int(tiles.shape[0])
+                if d.nnz_tiles:
+                    d.row_off = dev(ro).data_ptr()
+                    d.weight = dev(tiles).data_ptr()
+            else:
+                d.format = FMT_DENSE
+                d.weight = dev(W).data_ptr()
+            return d
+
+        self.desc = EncoderLayerDesc()
+        self.desc.qkv = lin("wqkv", "bqkv")
+        self.desc.o = lin("wo", "bo")
+        self.desc.ffn1 = lin("w1", "b1")
+        self.desc.ffn2 = lin("w2", "b2")
+        self.desc.ln1_gamma = dev(weights["ln1_g"]).data_ptr()
+        self.desc.ln1_beta = dev(weights["ln1_b"]).data_ptr()
+        self.desc.ln2_gamma = dev(weights["ln2_g"]).data_ptr()
+        self.desc.ln2_beta = dev(weights["ln2_b"]).data_ptr()
+        hidden = int(weights["wo"].shape[0])
+        vdim = int(weights["wo"].shape[1])
+        kdim = (int(weights["wqkv"].shape[0]) - vdim) // 2
+        self.desc.hidden, self.desc.nhead = hidden, nhead
+        self.desc.kdim, self.desc.vdim = kdim, vdim
+        self.desc.ff = int(weights["w1"].shape[0])
+        self.desc.act = act_kind
+        self.hidden = hidden
+
+    def workspace_bytes(self, batch: int, seq: int) -> int:
+        return int(lib().et_encoder_layer_workspace_bytes(ctypes.byref(self.desc), c_int(batch),
+                                                          c_int(seq)))
+
+    def forward(self, x, out, batch, seq, workspace, mask_kind=MASK_NONE, mask=None,
+                valid_len=None):
+        check(lib().et_encoder_layer_fwd(ctypes.byref(self.desc), _p(x), _p(out), c_int(batch),
+                                         c_int(seq), c_int(mask_kind), _p(mask), _p(valid_len),
+                                         _p(workspace), c_size_t(workspace.numel() *
+                                                                 workspace.element_size()),
+                                         _stream()), "et_encoder_layer_fwd")
+        return out
+
+
+class EncoderStack:
+    """N chained encoder layers sharing one workspace and two ping-pong activation buffers."""
+
+    def __init__(self, layers, batch: int, seq: int, device="cuda"):
+        import torch
+        self.layers = list(layers)
+        self.batch, self.seq = batch, seq
+        ws = max(l.workspace_bytes(batch, seq) for l in self.layers)
+        if ws == 0:
+            raise EtError("invalid encoder layer description")
+        self.workspace = torch.empty(ws, dtype=torch.uint8, device=device)
+        hidden = self.layers[0].hidden
+        self.buf = [torch.empty((batch * seq, hidden), dtype=torch.float16, device=device)
+                    for _ in range(2)]
+
+    def forward(self, x, mask_kind=MASK_NONE, mask=None, valid_len=None):
+        cur = x
+        for i, layer in enumerate(self.layers):
+            out = self.buf[i & 1]
+            layer.forward(cur, out, self.batch, self.seq, self.workspace, mask_kind, mask,
+                          valid_len)
+            cur = out
+        return cur

@@ -1,0 +1,417 @@
+// On-the-fly fused self-attention on tcgen05 tensor cores: scores never leave the SM.
+//
+// One CTA owns 128 queries of one (sequence, head).  Warp 0 streams Q once and then K / V
+// blocks of 128 keys with TMA (3-D tensor maps {feature, position, sequence}, so positions
+// past the end of a sequence are zero-filled and never read the next sequence).  One
+// thread of warp 1 issues S = Q.K^T (M=128, N=128) into tensor memory, the four softmax
+// warps (one query row per thread) read S back, apply scale and mask, keep a running
+// max / sum (online softmax, exp2 with log2(e)/sqrt(dh) folded into one FMA), write the
+// fp16 probabilities into 128-byte-swizzled shared memory as the A operand of the second
+// product, rescale the output accumulator when the running max moved, and the MMA thread
+// accumulates O += P.V with V consumed directly in its row-major (MN-major) layout.
+// After the last block each softmax thread divides its row by the sum and stores fp16.
+// All waits are bounded.
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace et {
+
+namespace {
+
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr int ATT_THREADS = 192;
+constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 fp16, one 128-byte-swizzled atom
+constexpr int TMEM_COLS_ATT = 256;     // S: columns [0,128), O: columns [128, 128 + dh_v)
+
+struct AttnArgs {
+    __half* Z;
+    const __half* mask;
+    const int* valid_len;
+    int ldz;
+    int batch, seq, nhead, dh_qk, dh_v;
+    int mask_kind;
+    float scale_log2;  // scale * log2(e)
+    int* err_word;
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const int nqa = (a.dh_qk + 63) >> 6;  // 64-feature atoms of Q / K
+    const int nva = (a.dh_v + 63) >> 6;   // 64-feature atoms of V
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + nqa * ATOM_BYTES;
+    uint8_t* sV = sK + nqa * ATOM_BYTES;
+    uint8_t* sP = sV + nva * ATOM_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATOM_BYTES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 2;
+    uint64_t* v_full = bars + 3;
+    uint64_t* v_empty = bars + 4;
+    uint64_t* s_full = bars + 5;
+    uint64_t* s_free = bars + 6;
+    uint64_t* p_full = bars + 7;
+    uint64_t* o_full = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int q0 = blockIdx.x * BQ;
+    const int h = blockIdx.y;
+    const int b = blockIdx.z;
+
+    int kv_len = a.seq;
+    if (a.mask_kind == ET_MASK_PADDING) {
+        kv_len = a.valid_len[b];
+        kv_len = kv_len < 0 ? 0 : (kv_len > a.seq ? a.seq : kv_len);
+    }
+    int n_kv = (kv_len + BKV - 1) / BKV;
+    if (a.mask_kind == ET_MASK_CAUSAL) {
+        const int last_q = (q0 + BQ - 1 < a.seq ? q0 + BQ - 1 : a.seq - 1);
+        const int lim = last_q / BKV + 1;
+        n_kv = n_kv < lim ? n_kv : lim;
+    }
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 128);
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS_ATT);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_S = tmem_base;
+    const uint32_t tmem_O = tmem_base + 128;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (n_kv > 0 && elect_one()) {
+            tma_prefetch_desc(&tmQ);
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+            mbar_arrive_expect_tx(q_full, nqa * ATOM_BYTES);
+            for (int t = 0; t < nqa; ++t)
+                tma_load_3d(sQ + t * ATOM_BYTES, &tmQ, q_full, h * a.dh_qk + t * 64, q0, b);
+            int k_issued = 0, v_issued = 0;
+            for (int j = 0; j < n_kv; ++j) {
+                const uint32_t ph = j & 1;
+                if (!mbar_wait_bounded(k_empty, ph ^ 1, abort_flag)) {
+                    report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_PRODUCER);
+                    break;
+                }
+                mbar_arrive_expect_tx(k_full, nqa * ATOM_BYTES);
+                for (int t = 0; t < nqa; ++t)
+                    tma_load_3d(sK + t * ATOM_BYTES, &tmK, k_full, h * a.dh_qk + t * 64, j * BKV, b);
+                ++k_issued;
+                if (!mbar_wait_bounded(v_empty, ph ^ 1, abort_flag)) {
+                    report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_PRODUCER);
+                    break;
+                }
+                mbar_arrive_expect_tx(v_full, nva * ATOM_BYTES);
+                for (int t = 0; t < nva; ++t)
+                    tma_load_3d(sV + t * ATOM_BYTES, &tmV, v_full, h * a.dh_v + t * 64, j * BKV, b);
+                ++v_issued;
+            }
+            if (*abort_flag) {
+                // let copies in flight land before shared memory is released
+                for (uint32_t it = 0; it < ET_SPIN_LIMIT; ++it)
+                    if (mbar_try_wait(q_full, 0)) break;
+                if (k_issued > 0)
+                    for (uint32_t it = 0; it < ET_SPIN_LIMIT; ++it)
+                        if (mbar_try_wait(k_full, (k_issued - 1) & 1)) break;
+                if (v_issued > 0)
+                    for (uint32_t it = 0; it < ET_SPIN_LIMIT; ++it)
+                        if (mbar_try_wait(v_full, (v_issued - 1) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (n_kv > 0 && elect_one()) {
+            const uint32_t idesc_s = make_idesc_f16(BQ, BKV, 0, 0);
+            const uint32_t idesc_o = make_idesc_f16(BQ, a.dh_v, 0, 1);  // V is MN-major
+            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV),
+                           p_addr = smem_u32(sP);
+            bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
+            if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const uint32_t ph = j & 1;
+                ok = mbar_wait_bounded(k_full, ph, abort_flag) &&
+                     mbar_wait_bounded(s_free, ph ^ 1, abort_flag);
+                if (!ok) {
+                    report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
+                    break;
+                }
+                tc_fence_after_sync();
+                const int ksteps = a.dh_qk >> 4;
+                for (int kk = 0; kk < ksteps; ++kk) {
+                    const uint32_t off = (kk >> 2) * ATOM_BYTES + (kk & 3) * 32;
+                    mma_f16_ss(tmem_S, make_smem_desc(q_addr + off, 16, 1024, SWZ_128B),
+                               make_smem_desc(k_addr + off, 16, 1024, SWZ_128B), idesc_s,
+                               kk != 0 ? 1u : 0u);
+                }
+                mma_commit(s_full);
+                mma_commit(k_empty);
+
+                ok = mbar_wait_bounded(p_full, ph, abort_flag) &&
+                     mbar_wait_bounded(v_full, ph, abort_flag);
+                if (!ok) {
+                    report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
+                    break;
+                }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk) {
+                    const uint32_t p_off = (kk >> 2) * ATOM_BYTES + (kk & 3) * 32;
+                    // V tile: 16 keys = two groups of 8 rows of 128 bytes (SBO = 1024); a second
+                    // 64-feature atom sits ATOM_BYTES further (LBO).
+                    mma_f16_ss(tmem_O, make_smem_desc(p_addr + p_off, 16, 1024, SWZ_128B),
+                               make_smem_desc(v_addr + kk * 2048, ATOM_BYTES, 1024, SWZ_128B),
+                               idesc_o, (j | kk) != 0 ? 1u : 0u);
+                }
+                mma_commit(o_full);
+                mma_commit(v_empty);
+            }
+        }
+    } else {
+        // ---------------- softmax / output warps: one query row per thread ----------------
+        const int qd = warp & 3;
+        const int r = qd * 32 + lane;  // row inside the CTA tile
+        const int qrow = q0 + r;       // position inside the sequence
+        const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+        const float NINF = -INFINITY;
+        float m_run = NINF, l_run = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < n_kv; ++j) {
+            const uint32_t ph = j & 1;
+            ok = mbar_wait_bounded(s_full, ph, abort_flag);
+            if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+
+            const int kbase = j * BKV;
+            const bool need_mask = (kbase + BKV > kv_len) || (a.mask_kind == ET_MASK_ADDITIVE) ||
+                                   (a.mask_kind == ET_MASK_CAUSAL && kbase + BKV - 1 > q0);
+            const __half* mrow = (a.mask_kind == ET_MASK_ADDITIVE && qrow < a.seq)
+                                     ? a.mask + static_cast<size_t>(qrow) * a.seq
+                                     : nullptr;
+            auto score = [&](uint32_t raw, int kc) -> float {
+                float s = __uint_as_float(raw) * a.scale_log2;
+                if (need_mask) {
+                    if (kc >= kv_len || (a.mask_kind == ET_MASK_CAUSAL && kc > qrow)) return NINF;
+                    if (mrow) s += __half2float(__ldg(mrow + kc)) * 1.4426950408889634f;
+                }
+                return s;
+            };
+
+            // pass 1: row maximum of this block
+            float mx = NINF;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_S + lane_off + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(v[i], kbase + c * 32 + i));
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = (m_new == NINF) ? 0.f : m_new;
+            const float alpha = exp2_approx(m_run - m_use);  // 0 when m_run = -inf
+
+            if (j > 0) {
+                // P and O of the previous block must have been consumed / produced
+                ok = mbar_wait_bounded(o_full, ph ^ 1, abort_flag);
+                if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+                    for (int c = 0; c < (a.dh_v >> 4); ++c) {
+                        uint32_t o[16];
+                        tmem_ld16(tmem_O + lane_off + c * 16, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st16(tmem_O + lane_off + c * 16, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+
+            // pass 2: probabilities -> shared memory (A operand of P.V), row sum
+            float rowsum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_S + lane_off + c * 32, v);
+                tmem_ld_wait();
+                float p[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    p[i] = exp2_approx(score(v[i], kbase + c * 32 + i) - m_use);
+                    rowsum += p[i];
+                }
+                uint8_t* prow = sP + (c >> 1) * ATOM_BYTES + r * 128;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 pk;
+                    pk.x = pack_half2(p[g * 8 + 0], p[g * 8 + 1]);
+                    pk.y = pack_half2(p[g * 8 + 2], p[g * 8 + 3]);
+                    pk.z = pack_half2(p[g * 8 + 4], p[g * 8 + 5]);
+                    pk.w = pack_half2(p[g * 8 + 6], p[g * 8 + 7]);
+                    const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) = pk;
+                }
+            }
+            l_run = l_run * alpha + rowsum;
+            m_run = m_new;
+
+            tc_fence_before_sync();
+            mbar_arrive(s_free);       // S may be overwritten by the next Q.K^T
+            fence_proxy_async_smem();  // P visible to the tensor core's reads
+            mbar_arrive(p_full);
+        }
+
+        if (ok && n_kv > 0) {
+            ok = mbar_wait_bounded(o_full, (n_kv - 1) & 1, abort_flag);
+            if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __half* zrow = a.Z + (static_cast<size_t>(b) * a.seq + (qrow < a.seq ? qrow : 0)) * a.ldz +
+                           static_cast<size_t>(h) * a.dh_v;
+            for (int c = 0; c < (a.dh_v >> 4); ++c) {
+                uint32_t o[16];
+                if (n_kv > 0) {
+                    tmem_ld16(tmem_O + lane_off + c * 16, o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = 0u;
+                }
+                if (qrow < a.seq) {
+                    uint4 w0, w1;
+                    w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+                    w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+                    w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+                    w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+                    w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+                    w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+                    w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+                    w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+                    *reinterpret_cast<uint4*>(zrow + c * 16) = w0;
+                    *reinterpret_cast<uint4*>(zrow + c * 16 + 8) = w1;
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS_ATT);
+}
+
+}  // namespace
+
+int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
+                     int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,
+                     int mask_kind, const __half* mask, const int* valid_len, float scale,
+                     cudaStream_t stream) {
+    if (!Q || !K || !V || !Z || batch <= 0 || seq <= 0 || nhead <= 0 || dh_qk <= 0 || dh_v <= 0)
+        return ET_ERR_INVALID_ARG;
+    if (mask_kind < ET_MASK_NONE || mask_kind > ET_MASK_ADDITIVE) return ET_ERR_INVALID_ARG;
+    if (mask_kind == ET_MASK_ADDITIVE && !mask) return ET_ERR_INVALID_ARG;
+    if (mask_kind == ET_MASK_PADDING && !valid_len) return ET_ERR_INVALID_ARG;
+    if (dh_qk % 16 || dh_v % 16 || dh_qk > 128 || dh_v > 128) return ET_ERR_SHAPE;
+    if (ldq % 8 || ldk % 8 || ldv % 8 || ldz % 8) return ET_ERR_SHAPE;
+    if (ldq < nhead * dh_qk || ldk < nhead * dh_qk || ldv < nhead * dh_v || ldz < nhead * dh_v)
+        return ET_ERR_SHAPE;
+    if (batch > 65535 || nhead > 65535) return ET_ERR_SHAPE;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(Z)) return ET_ERR_ALIGNMENT;
+    int* err = device_error_word();
+    if (!err) return ET_ERR_NO_DEVICE;
+
+    CUtensorMap tmQ, tmK, tmV;
+    const uint32_t box[3] = {64, 128, 1};
+    auto make = [&](CUtensorMap* m, const __half* p, int ld, int width) {
+        const uint64_t dims[3] = {static_cast<uint64_t>(width), static_cast<uint64_t>(seq),
+                                  static_cast<uint64_t>(batch)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2,
+                                     static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(seq)};
+        return make_tensor_map_f16(m, p, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    };
+    int st;
+    if ((st = make(&tmQ, Q, ldq, nhead * dh_qk)) != ET_OK) return st;
+    if ((st = make(&tmK, K, ldk, nhead * dh_qk)) != ET_OK) return st;
+    if ((st = make(&tmV, V, ldv, nhead * dh_v)) != ET_OK) return st;
+
+    const int nqa = (dh_qk + 63) / 64, nva = (dh_v + 63) / 64;
+    const int smem_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + 256 + 1024;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (2 * 2 + 2 + 2) * ATOM_BYTES + 256 + 1024) != cudaSuccess)
+            return ET_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    AttnArgs a;
+    a.Z = Z;
+    a.mask = mask;
+    a.valid_len = valid_len;
+    a.ldz = ldz;
+    a.batch = batch;
+    a.seq = seq;
+    a.nhead = nhead;
+    a.dh_qk = dh_qk;
+    a.dh_v = dh_v;
+    a.mask_kind = mask_kind;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.err_word = err;
+    dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
+    attention_kernel<<<grid, ATT_THREADS, smem_bytes, stream>>>(tmQ, tmK, tmV, a);
+    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+}
+
+}  // namespace et
+
+extern "C" {
+
+int et_attention_fwd(const et_half* Q, const et_half* K, const et_half* V, et_half* Z, int batch,
+                     int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,
+                     int mask_kind, const et_half* mask, const int32_t* valid_len, float scale,
+                     et_stream stream) {
+    return et::launch_attention(
+        reinterpret_cast<const __half*>(Q), reinterpret_cast<const __half*>(K),
+        reinterpret_cast<const __half*>(V), reinterpret_cast<__half*>(Z), batch, seq, nhead, dh_qk,
+        dh_v, ldq, ldk, ldv, ldz, mask_kind, reinterpret_cast<const __half*>(mask), valid_len,
+        scale, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,142 @@
+// Whole post-LN encoder layer: the sequence of launches Encoder<config>::forward makes in
+// the reference (Encoder/Encoder.h:81-96), with bias / activation folded into the GEMM
+// epilogues and the fused [Q | K | V] projection feeding the on-the-fly attention kernel.
+//
+//   qkv = QKV(x)                      [T, 2*kdim + vdim]
+//   z   = attention(qkv)              [T, vdim]
+//   a   = O(z)                        [T, hidden]
+//   y   = LN1(a + x)                  [T, hidden]
+//   f   = act(W1 y + b1)              [T, ff]
+//   a   = W2 f + b2                   [T, hidden]
+//   out = LN2(a + y)
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace et {
+namespace {
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct LayerBuffers {
+    __half *qkv, *z, *a, *y, *f;
+    size_t total;
+};
+
+LayerBuffers carve(const et_encoder_layer_t* L, int batch, int seq, void* base) {
+    const size_t T = static_cast<size_t>(batch) * seq;
+    LayerBuffers b;
+    uint8_t* p = static_cast<uint8_t*>(base);
+    size_t off = 0;
+    auto take = [&](size_t elems) {
+        __half* r = reinterpret_cast<__half*>(p + off);
+        off += align256(elems * sizeof(__half));
+        return r;
+    };
+    b.qkv = take(T * (2 * static_cast<size_t>(L->kdim) + L->vdim));
+    b.z = take(T * L->vdim);
+    b.a = take(T * L->hidden);
+    b.y = take(T * L->hidden);
+    b.f = take(T * L->ff);
+    b.total = off;
+    return b;
+}
+
+int run_linear(const et_linear_t& lin, const __half* X, __half* Y, int T, int act,
+               cudaStream_t stream) {
+    if (lin.format == ET_FMT_DENSE)
+        return launch_gemm_f16(X, lin.in, reinterpret_cast<const __half*>(lin.weight), lin.in,
+                               reinterpret_cast<const __half*>(lin.bias), Y, lin.out, nullptr, 0, T,
+                               lin.out, lin.in, act, stream);
+    if (lin.format == ET_FMT_TILE)
+        return launch_linear_tile(lin.row_ptr, lin.row_off,
+                                  reinterpret_cast<const __half*>(lin.weight), lin.nnz_tiles,
+                                  reinterpret_cast<const __half*>(lin.bias), X, Y, T, lin.in,
+                                  lin.out, act, stream);
+    return ET_ERR_INVALID_ARG;
+}
+
+int check_layer(const et_encoder_layer_t* L) {
+    if (!L) return ET_ERR_INVALID_ARG;
+    if (L->hidden <= 0 || L->nhead <= 0 || L->kdim <= 0 || L->vdim <= 0 || L->ff <= 0)
+        return ET_ERR_INVALID_ARG;
+    if (L->kdim % L->nhead || L->vdim % L->nhead) return ET_ERR_SHAPE;
+    if (L->qkv.in != L->hidden || L->qkv.out != 2 * L->kdim + L->vdim) return ET_ERR_SHAPE;
+    if (L->o.in != L->vdim || L->o.out != L->hidden) return ET_ERR_SHAPE;
+    if (L->ffn1.in != L->hidden || L->ffn1.out != L->ff) return ET_ERR_SHAPE;
+    if (L->ffn2.in != L->ff || L->ffn2.out != L->hidden) return ET_ERR_SHAPE;
+    if (!L->ln1_gamma || !L->ln1_beta || !L->ln2_gamma || !L->ln2_beta) return ET_ERR_INVALID_ARG;
+    if (L->act != ET_ACT_RELU && L->act != ET_ACT_GELU) return ET_ERR_INVALID_ARG;
+    return ET_OK;
+}
+
+}  // namespace
+}  // namespace et
+
+extern "C" {
+
+size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq) {
+    if (et::check_layer(layer) != ET_OK || batch <= 0 || seq <= 0) return 0;
+    return et::carve(layer, batch, seq, nullptr).total;
+}
+
+int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_half* out,
+                         int batch, int seq, int mask_kind, const et_half* mask,
+                         const int32_t* valid_len, void* workspace, size_t workspace_bytes,
+                         et_stream stream) {
+    int st = et::check_layer(layer);
+    if (st != ET_OK) return st;
+    if (!x || !out || batch <= 0 || seq <= 0) return ET_ERR_INVALID_ARG;
+    if (!workspace) return ET_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return ET_ERR_ALIGNMENT;
+    const et::LayerBuffers b = et::carve(layer, batch, seq, workspace);
+    if (workspace_bytes < b.total) return ET_ERR_WORKSPACE;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int T = batch * seq;
+    const __half* xin = reinterpret_cast<const __half*>(x);
+    const int ldqkv = 2 * layer->kdim + layer->vdim;
+    const int dh_qk = layer->kdim / layer->nhead, dh_v = layer->vdim / layer->nhead;
+
+    if ((st = et::run_linear(layer->qkv, xin, b.qkv, T, ET_ACT_NONE, s)) != ET_OK) return st;
+    if ((st = et::launch_attention(b.qkv, b.qkv + layer->kdim, b.qkv + 2 * layer->kdim, b.z, batch,
+                                   seq, layer->nhead, dh_qk, dh_v, ldqkv, ldqkv, ldqkv, layer->vdim,
+                                   mask_kind, reinterpret_cast<const __half*>(mask), valid_len,
+                                   1.0f / sqrtf(static_cast<float>(dh_qk)), s)) != ET_OK)
+        return st;
+    if ((st = et::run_linear(layer->o, b.z, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
+    if ((st = et::launch_skip_layernorm(b.a, xin, reinterpret_cast<const __half*>(layer->ln1_gamma),
+                                        reinterpret_cast<const __half*>(layer->ln1_beta), b.y, T,
+                                        layer->hidden, s)) != ET_OK)
+        return st;
+    if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, s)) != ET_OK) return st;
+    if ((st = et::run_linear(layer->ffn2, b.f, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
+    return et::launch_skip_layernorm(b.a, b.y, reinterpret_cast<const __half*>(layer->ln2_gamma),
+                                     reinterpret_cast<const __half*>(layer->ln2_beta),
+                                     reinterpret_cast<__half*>(out), T, layer->hidden, s);
+}
+
+int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,
+                            const et_half* mask, et_half* Z, const int32_t* o_row_ptr,
+                            const int32_t* o_row_off, const et_half* o_tiles, int o_nnz,
+                            const et_half* o_bias, et_half* out, int batch, int seq, int nhead,
+                            int dh_qk, int dh_v, int ldq, int ldk, int ldv, int emdim,
+                            int mask_kind, const int32_t* valid_len, float scale,
+                            et_stream stream) {
+    if (!Z || !out) return ET_ERR_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vdim = nhead * dh_v;
+    int st = et::launch_attention(reinterpret_cast<const __half*>(Q),
+                                  reinterpret_cast<const __half*>(K),
+                                  reinterpret_cast<const __half*>(V), reinterpret_cast<__half*>(Z),
+                                  batch, seq, nhead, dh_qk, dh_v, ldq, ldk, ldv, vdim, mask_kind,
+                                  reinterpret_cast<const __half*>(mask), valid_len, scale, s);
+    if (st != ET_OK) return st;
+    return et::launch_linear_tile(o_row_ptr, o_row_off, reinterpret_cast<const __half*>(o_tiles),
+                                  o_nnz, reinterpret_cast<const __half*>(o_bias),
+                                  reinterpret_cast<const __half*>(Z), reinterpret_cast<__half*>(out),
+                                  batch * seq, vdim, emdim, ET_ACT_NONE, s);
+}
+
+}  // extern "C"

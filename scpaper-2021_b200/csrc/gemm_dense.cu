@@ -1,0 +1,405 @@
+// Dense fp16 GEMM  Y[M, N] = act(X[M, K] . W[N, K]^T + bias)  on tcgen05 tensor cores.
+//
+// One CTA computes a 128 x BN output tile.  Warp 0 streams 128x64 (X) and BNx64 (W)
+// K-major tiles into a ring of 128-byte-swizzled shared-memory stages with TMA; one
+// thread of warp 1 issues tcgen05.mma (M=128, N=BN, K=16) with the fp32 accumulator in
+// tensor memory; warps 2-5 read the accumulator back (tcgen05.ld), add the bias, apply
+// the activation and store fp16 with 128-bit writes.  Rows/columns/K beyond the problem
+// are zero-filled by TMA and masked in the epilogue.  Every mbarrier wait is bounded.
+//
+// The same kernel serves the row-pruned Linear (output columns scattered through an
+// index list) and the column-pruned Linear (after a gather of the kept input features).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace et {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+
+template <int BN, int STAGES>
+struct GemmCfg {
+    static constexpr int B_STAGE_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + align slack
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+template <int BN, int STAGES, int MIN_CTAS>
+__global__ void __launch_bounds__(GEMM_THREADS, MIN_CTAS)
+gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                __half* __restrict__ Y, int ldy, const __half* __restrict__ bias,
+                const int* __restrict__ col_map, int scatter, int M, int N, int K, int act,
+                int* err_word) {
+    using Cfg = GemmCfg<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * BM;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) {
+                    report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_PRODUCER);
+                    break;
+                }
+                mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                tma_load_2d(sA + s * A_STAGE_BYTES, &tmA, &full_bar[s], kb * BK, m0);
+                tma_load_2d(sB + s * Cfg::B_STAGE_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+                ++issued;
+            }
+            if (*abort_flag) {
+                // Let copies already in flight land before the CTA's shared memory is released.
+                const int first = issued > STAGES ? issued - STAGES : 0;
+                for (int kb = first; kb < issued; ++kb)
+                    for (uint32_t it = 0; it < ET_SPIN_LIMIT; ++it)
+                        if (mbar_try_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc_f16(BM, BN, 0, 0);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
+                    report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_MMA);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+                const uint32_t b_addr = smem_u32(sB + s * Cfg::B_STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B);
+                    mma_f16_ss(tmem_base, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                }
+                mma_commit(&empty_bar[s]);
+            }
+            if (ok) mma_commit(acc_bar);
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        const int row = m0 + q * 32 + lane;
+        bool ok = true;
+        if (num_kb > 0) {
+            ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
+            if (!ok) report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_EPILOGUE);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= N) break;  // warp-uniform
+                uint32_t r[32];
+                if (num_kb > 0) {
+                    tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                if (row < M) {
+                    if (col_map == nullptr) {
+                        __half* yrow = Y + static_cast<size_t>(row) * ldy + col0;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (col0 + g * 8 >= N) break;
+                            float v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+                            if (bias != nullptr) {
+                                const uint4 bq =
+                                    __ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8));
+                                const __half2* bh = reinterpret_cast<const __half2*>(&bq);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float2 bf = __half22float2(bh[j]);
+                                    v[2 * j] += bf.x;
+                                    v[2 * j + 1] += bf.y;
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], act);
+                            uint4 o;
+                            o.x = pack_half2(v[0], v[1]);
+                            o.y = pack_half2(v[2], v[3]);
+                            o.z = pack_half2(v[4], v[5]);
+                            o.w = pack_half2(v[6], v[7]);
+                            *reinterpret_cast<uint4*>(yrow + g * 8) = o;
+                        }
+                    } else {
+                        // index-list epilogue: the bias belongs to feature col_map[n]; the value is
+                        // stored there (scatter) or at the compressed position n.
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int n = col0 + j;
+                            if (n < N) {
+                                const int feat = __ldg(col_map + n);
+                                float v = __uint_as_float(r[j]);
+                                if (bias != nullptr) v += __half2float(__ldg(bias + feat));
+                                v = apply_act(v, act);
+                                Y[static_cast<size_t>(row) * ldy + (scatter ? feat : n)] =
+                                    __float2half_rn(v);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// out[r, c] = act(bias[c]) for every element: the columns a row-pruned Linear never computes.
+__global__ void fill_bias_kernel(__half* __restrict__ Y, const __half* __restrict__ bias, int rows,
+                                 int cols, int act) {
+    const size_t n8 = static_cast<size_t>(rows) * cols / 8;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>((i * 8) % cols);
+        float v[8];
+        if (bias != nullptr) {
+            const uint4 bq = __ldg(reinterpret_cast<const uint4*>(bias + c));
+            const __half2* bh = reinterpret_cast<const __half2*>(&bq);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(bh[j]);
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        }
+        uint4 o;
+        o.x = pack_half2(apply_act(v[0], act), apply_act(v[1], act));
+        o.y = pack_half2(apply_act(v[2], act), apply_act(v[3], act));
+        o.z = pack_half2(apply_act(v[4], act), apply_act(v[5], act));
+        o.w = pack_half2(apply_act(v[6], act), apply_act(v[7], act));
+        reinterpret_cast<uint4*>(Y)[i] = o;
+    }
+}
+
+// G[t, k] = X[t, col_id[k]]: the kept input features of a column-pruned Linear.
+__global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __restrict__ col_id,
+                                   __half* __restrict__ G, int T, int in, int nn_col) {
+    const size_t total = static_cast<size_t>(T) * nn_col;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = i / nn_col;
+        const int k = static_cast<int>(i - t * nn_col);
+        G[i] = X[t * in + __ldg(col_id + k)];
+    }
+}
+
+template <int BN, int STAGES, int MIN_CTAS>
+int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, __half* Y, int ldy,
+               const __half* bias, const int* col_map, int scatter, int M, int N, int K, int act,
+               cudaStream_t stream) {
+    using Cfg = GemmCfg<BN, STAGES>;
+    auto kern = gemm_f16_kernel<BN, STAGES, MIN_CTAS>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::SMEM_BYTES) != cudaSuccess)
+            return ET_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, Y, ldy, bias, col_map, scatter,
+                                                          M, N, K, act, device_error_word());
+    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+}
+
+int g_force_bn = 0;
+
+int pick_bn(int M, int N) {
+    if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) return g_force_bn;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const int mt = (M + BM - 1) / BM;
+    int best_bn = 128;
+    long best_cost = -1;
+    const int cands[3] = {256, 128, 64};
+    for (int bn : cands) {
+        const long tiles = static_cast<long>(mt) * ((N + bn - 1) / bn);
+        const long waves = (tiles + sms - 1) / sms;
+        const long cost = waves * (bn + 48);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best_bn = bn;
+        }
+    }
+    return best_bn;
+}
+
+}  // namespace
+
+void gemm_force_bn(int bn) { g_force_bn = bn; }
+
+int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
+                    __half* Y, int ldy, const int* col_map, int scatter, int M, int N, int K,
+                    int act, cudaStream_t stream) {
+    if (!X || !W || !Y || M <= 0 || N <= 0 || K <= 0) return ET_ERR_INVALID_ARG;
+    if (act < ET_ACT_NONE || act > ET_ACT_GELU) return ET_ERR_INVALID_ARG;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(Y) || (bias && !aligned16(bias)))
+        return ET_ERR_ALIGNMENT;
+    if (ldx % 8 || ldw % 8 || K % 8) return ET_ERR_SHAPE;
+    if (col_map == nullptr && (N % 8 || ldy % 8)) return ET_ERR_SHAPE;
+    if (!device_error_word()) return ET_ERR_NO_DEVICE;
+
+    const int bn = pick_bn(M, N);
+    CUtensorMap tmA, tmB;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
+        const uint32_t box[2] = {BK, BM};
+        int st = make_tensor_map_f16(&tmA, X, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldw) * 2};
+        const uint32_t box[2] = {BK, static_cast<uint32_t>(bn)};
+        int st = make_tensor_map_f16(&tmB, W, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
+    }
+    switch (bn) {
+        case 256:
+            return launch_cfg<256, 4, 1>(tmA, tmB, Y, ldy, bias, col_map, scatter, M, N, K, act,
+                                         stream);
+        case 64:
+            return launch_cfg<64, 4, 2>(tmA, tmB, Y, ldy, bias, col_map, scatter, M, N, K, act,
+                                        stream);
+        default:
+            return launch_cfg<128, 3, 2>(tmA, tmB, Y, ldy, bias, col_map, scatter, M, N, K, act,
+                                         stream);
+    }
+}
+
+}  // namespace et
+
+using et::launch_gemm_f16;
+
+extern "C" {
+
+// Test hook: 0 = automatic tile width, else 64 / 128 / 256.
+void et_debug_force_gemm_bn(int bn) { et::gemm_force_bn(bn); }
+
+int et_linear_dense_fwd(const et_half* X, const et_half* W, const et_half* bias, et_half* Y,
+                        int T, int in, int out, int act, et_stream stream) {
+    if (in % 16 || out % 16) return (in <= 0 || out <= 0) ? ET_ERR_INVALID_ARG : ET_ERR_SHAPE;
+    return launch_gemm_f16(reinterpret_cast<const __half*>(X), in,
+                           reinterpret_cast<const __half*>(W), in,
+                           reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Y),
+                           out, nullptr, 0, T, out, in, act, static_cast<cudaStream_t>(stream));
+}
+
+int et_linear_row_fwd(const int32_t* row_id, const et_half* rows, int nn_row,
+                      const et_half* bias, const et_half* X, et_half* Y, int T, int in, int out,
+                      int act, et_stream stream) {
+    if (!X || !Y || T <= 0 || in <= 0 || out <= 0 || nn_row < 0 || (nn_row > 0 && (!row_id || !rows)))
+        return ET_ERR_INVALID_ARG;
+    if (in % 16 || out % 16) return ET_ERR_SHAPE;
+    if (!et::aligned16(Y) || (bias && !et::aligned16(bias))) return ET_ERR_ALIGNMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t n8 = static_cast<size_t>(T) * out / 8;
+    const int blocks = static_cast<int>((n8 + 255) / 256 < 4096 ? (n8 + 255) / 256 : 4096);
+    et::fill_bias_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<__half*>(Y),
+                                                reinterpret_cast<const __half*>(bias), T, out, act);
+    if (cudaGetLastError() != cudaSuccess) return ET_ERR_CUDA;
+    if (nn_row == 0) return ET_OK;
+    return launch_gemm_f16(reinterpret_cast<const __half*>(X), in,
+                           reinterpret_cast<const __half*>(rows), in,
+                           reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Y),
+                           out, row_id, 1, T, nn_row, in, act, s);
+}
+
+int et_linear_row_compressed_fwd(const int32_t* row_id, const et_half* rows, int nn_row,
+                                 const et_half* bias, const et_half* X, et_half* Yc, int T,
+                                 int in, et_stream stream) {
+    if (!row_id || !rows || nn_row <= 0) return ET_ERR_INVALID_ARG;
+    if (in % 16) return ET_ERR_SHAPE;
+    return launch_gemm_f16(reinterpret_cast<const __half*>(X), in,
+                           reinterpret_cast<const __half*>(rows), in,
+                           reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Yc),
+                           nn_row, row_id, 0, T, nn_row, in, ET_ACT_NONE,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
+                      const et_half* bias, const et_half* X, et_half* Y, int T, int in, int out,
+                      int act, et_half* scratch, size_t scratch_bytes, et_stream stream) {
+    if (!X || !Y || !col_id || !cols || T <= 0 || in <= 0 || out <= 0 || nn_col <= 0)
+        return ET_ERR_INVALID_ARG;
+    if (in % 16 || out % 16 || nn_col % 8) return ET_ERR_SHAPE;
+    if (!scratch || scratch_bytes < static_cast<size_t>(T) * nn_col * sizeof(et_half))
+        return ET_ERR_WORKSPACE;
+    if (!et::aligned16(scratch)) return ET_ERR_ALIGNMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t total = static_cast<size_t>(T) * nn_col;
+    const int blocks = static_cast<int>((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    et::gather_cols_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __half*>(X), col_id,
+                                                  reinterpret_cast<__half*>(scratch), T, in, nn_col);
+    if (cudaGetLastError() != cudaSuccess) return ET_ERR_CUDA;
+    return launch_gemm_f16(reinterpret_cast<const __half*>(scratch), nn_col,
+                           reinterpret_cast<const __half*>(cols), nn_col,
+                           reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Y),
+                           out, nullptr, 0, T, out, nn_col, act, s);
+}
+
+}  // extern "C"

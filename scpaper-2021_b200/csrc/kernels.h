@@ -1,0 +1,32 @@
+// Internal launch functions shared between the C-ABI translation units.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace et {
+
+// Y[M, N] = act(X[M, K] . W[N, K]^T + bias).  col_map == nullptr: plain store to Y[m, n]
+// (N % 8 == 0, ldy % 8 == 0).  col_map != nullptr: the bias is taken at col_map[n] and the
+// value stored at column col_map[n] (scatter != 0) or n (scatter == 0).
+int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
+                    __half* Y, int ldy, const int* col_map, int scatter, int M, int N, int K,
+                    int act, cudaStream_t stream);
+
+// Tile-CSR Linear (see linear_tile.cu).
+int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
+                       const __half* bias, const __half* X, __half* Y, int T, int in, int out,
+                       int act, cudaStream_t stream);
+
+// Fused attention (see attention.cu).  Vc_col_id / head_ptr are null for an uncompressed V.
+int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
+                     int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,
+                     int mask_kind, const __half* mask, const int* valid_len, float scale,
+                     cudaStream_t stream);
+
+// out = LN(src + skip) * gamma + beta (skip may be null).
+int launch_skip_layernorm(const __half* src, const __half* skip, const __half* gamma,
+                          const __half* beta, __half* out, int rows, int size,
+                          cudaStream_t stream);
+
+}  // namespace et

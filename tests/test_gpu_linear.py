@@ -1,0 +1,160 @@
+"""GPU parity of the Linear layers (all five weight formats + dense) through the C ABI
+against the CPU oracle.  Shapes follow the reference's benchmarks: the four BERT-base GEMMs
+768->2304, 768->768, 768->3072, 3072->768 (Linear/test/benchmark/test.sh:5-8) plus ragged and
+tiny cases; sparsity sweep values from Linear/test/test_concurrent.cu:14-52."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, cuda):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def _host(t):
+    return t.float().cpu().numpy()
+
+
+def _case(et, seed, T, inn, out, std=0.05):
+    x = et.synth.normal(seed, 1, (T, inn), 1.0)
+    w = et.synth.normal(seed, 2, (out, inn), std)
+    b = et.synth.normal(seed, 3, (out,), 0.1)
+    return x, w, b
+
+
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("T,inn,out,act", [
+    (128, 64, 128, 0), (256, 768, 768, 0), (2048, 768, 2304, 0), (512, 768, 3072, 2),
+    (512, 3072, 768, 0), (100, 80, 48, 1), (1, 16, 16, 0), (333, 1024, 1008, 2),
+])
+def test_dense(et, orc, cuda, T, inn, out, act, bn):
+    x, w, b = _case(et, 11, T, inn, out)
+    et.lib().et_debug_force_gemm_bn(bn)
+    try:
+        y = et.linear_dense(_dev(x, cuda), _dev(w, cuda), _dev(b, cuda), act)
+        assert et.device_error() == 0
+    finally:
+        et.lib().et_debug_force_gemm_bn(0)
+    assert_close(_host(y), orc.linear_dense(x, w, b, act), f"dense {T}x{inn}x{out} bn{bn}",
+                 dump=f"dense_{T}_{inn}_{out}_{bn}")
+
+
+def test_dense_constant_closed_form(et, cuda):
+    """W = 1, x = 1, b = 0.5 gives in + 0.5 everywhere (the reference's constant generators,
+    Linear/gen_linear.hpp:15-23, Linear/test/test_tile.cu:61-74)."""
+    import torch
+    T, inn, out = 128, 256, 64
+    x = torch.ones((T, inn), dtype=torch.float16, device=cuda)
+    w = torch.ones((out, inn), dtype=torch.float16, device=cuda)
+    b = torch.full((out,), 0.5, dtype=torch.float16, device=cuda)
+    y = et.linear_dense(x, w, b)
+    assert et.device_error() == 0
+    assert torch.all(y.float() == inn + 0.5)
+
+
+def test_dense_no_bias(et, orc, cuda):
+    x, w, _ = _case(et, 12, 200, 128, 96)
+    y = et.linear_dense(_dev(x, cuda), _dev(w, cuda), None, 0)
+    assert_close(_host(y), orc.linear_dense(x, w, None, 0), "dense no bias")
+
+
+@pytest.mark.parametrize("sparsity", [0.0, 0.5, 0.8, 0.95, 1.0])
+@pytest.mark.parametrize("T,inn,out,act", [(256, 768, 768, 0), (300, 768, 3072, 2),
+                                           (128, 3072, 768, 0), (64, 64, 48, 1)])
+def test_tile(et, orc, cuda, T, inn, out, act, sparsity):
+    x, w, b = _case(et, 21, T, inn, out)
+    w = et.synth.prune_tiles(w, 21, 4, sparsity)
+    rp, ro, tiles = et.synth.dense_to_tile(w)
+    assert et.lib().et_validate_tile_mat(rp.ctypes.data, ro.ctypes.data if len(ro) else None,
+                                         len(ro), inn, out) == 0
+    y = et.linear_tile(_dev(x, cuda), _dev(rp, cuda), _dev(ro, cuda) if len(ro) else None,
+                       _dev(tiles, cuda) if len(ro) else None, out, _dev(b, cuda), act)
+    assert et.device_error() == 0
+    ref = orc.linear_tile(x, rp, ro, tiles.astype(np.float32), out, b, act)
+    assert_close(_host(y), ref, f"tile {T}x{inn}x{out} s={sparsity}",
+                 dump=f"tile_{T}_{inn}_{out}_{sparsity}")
+    # format-native loop agrees with the dense evaluation of the densified weights
+    assert_close(ref, orc.linear_dense(x, w, b, act), "oracle tile vs dense", 1e-5, 1e-4)
+
+
+def test_tile_empty_block_rows(et, orc, cuda):
+    """Block rows without any tile receive the bias alone."""
+    x, w, b = _case(et, 22, 160, 128, 256)
+    w[16:48] = 0
+    w[240:] = 0
+    rp, ro, tiles = et.synth.dense_to_tile(w)
+    y = et.linear_tile(_dev(x, cuda), _dev(rp, cuda), _dev(ro, cuda), _dev(tiles, cuda), 256,
+                       _dev(b, cuda), 0)
+    assert et.device_error() == 0
+    assert_close(_host(y), orc.linear_dense(x, w, b, 0), "tile empty rows")
+
+
+@pytest.mark.parametrize("sparsity", [0.0, 0.5, 0.9])
+def test_row(et, orc, cuda, sparsity):
+    T, inn, out = 300, 256, 512
+    x, w, b = _case(et, 31, T, inn, out)
+    row_id = et.synth.choose_ids(31, 5, out, sparsity)
+    rid, rows = et.synth.dense_to_row(w, row_id)
+    for act in (0, 2):
+        y = et.linear_row(_dev(x, cuda), _dev(rid, cuda), _dev(rows, cuda), out, _dev(b, cuda), act)
+        assert et.device_error() == 0
+        assert_close(_host(y), orc.linear_row(x, rid, rows, out, b, act), f"row s={sparsity}")
+    yc = et.linear_row_compressed(_dev(x, cuda), _dev(rid, cuda), _dev(rows, cuda), _dev(b, cuda))
+    assert_close(_host(yc), orc.linear_row_compressed(x, rid, rows, b), "row compressed")
+
+
+@pytest.mark.parametrize("sparsity", [0.0, 0.5, 0.9])
+def test_col(et, orc, cuda, sparsity):
+    T, inn, out = 260, 512, 256
+    x, w, b = _case(et, 41, T, inn, out)
+    col_id = et.synth.choose_ids(41, 5, inn, sparsity)
+    cid, cols = et.synth.dense_to_col(w, col_id)
+    y = et.linear_col(_dev(x, cuda), _dev(cid, cuda), _dev(cols, cuda), _dev(b, cuda), 1)
+    assert et.device_error() == 0
+    assert_close(_host(y), orc.linear_col(x, cid, cols, b, 1), f"col s={sparsity}")
+
+
+@pytest.mark.parametrize("sparsity", [0.0, 0.9, 1.0])
+def test_1x16(et, orc, cuda, sparsity):
+    T, inn, out = 200, 256, 128
+    x, w, b = _case(et, 51, T, inn, out)
+    w = et.synth.prune_1x16(w, 51, 6, sparsity)
+    ti, ri, data = et.synth.dense_to_1x16(w)
+    y = et.linear_1x16(_dev(x, cuda), _dev(ti, cuda), _dev(ri, cuda) if len(ri) else None,
+                       _dev(data, cuda) if len(ri) else None, out, _dev(b, cuda), 2)
+    assert et.device_error() == 0
+    assert_close(_host(y), orc.linear_1x16(x, ti, ri, data, out, b, 2), f"1x16 s={sparsity}")
+
+
+@pytest.mark.parametrize("sparsity", [0.5, 0.95])
+def test_csr(et, orc, cuda, sparsity):
+    T, inn, out = 100, 256, 200
+    x, w, b = _case(et, 61, T, inn, out)
+    keep = et.synth.keep_exact(61, 7, out * inn, sparsity).reshape(out, inn)
+    w = w * keep
+    ip, ix, data = et.synth.dense_to_csr(w)
+    y = et.linear_csr(_dev(x, cuda), _dev(ip, cuda), _dev(ix, cuda), _dev(data, cuda), out,
+                      _dev(b, cuda), 0)
+    assert et.device_error() == 0
+    assert_close(_host(y), orc.linear_csr(x, ip, ix, data, out, b, 0), f"csr s={sparsity}")
+
+
+def test_bad_arguments_are_rejected_before_launch(et, cuda):
+    """Host-side failure injection: bad shapes / pointers return a status, nothing launches."""
+    import torch
+    x = torch.zeros((16, 24), dtype=torch.float16, device=cuda)
+    w = torch.zeros((16, 24), dtype=torch.float16, device=cuda)
+    with pytest.raises(et.EtError):
+        et.linear_dense(x, w)  # in % 16 != 0
+    x = torch.zeros((16, 32), dtype=torch.float16, device=cuda)
+    w = torch.zeros((16, 32), dtype=torch.float16, device=cuda)
+    st = et.lib().et_linear_dense_fwd(None, w.data_ptr(), None, x.data_ptr(), 16, 32, 16, 0, None)
+    assert st == -1
+    st = et.lib().et_linear_dense_fwd(x.data_ptr() + 2, w.data_ptr(), None, x.data_ptr(), 16, 32,
+                                      16, 0, None)
+    assert st == -2
+    assert et.device_error() == 0
