@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Throughput benchmark of the encoder hot path: BERT-base, seq 128, sequences/s.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...  # CPU evaluation of the same math
+
+A step is one forward pass of the 12-layer BERT-base encoder stack (hidden 768, 12 heads,
+FFN 3072, GELU, post-LN) over one batch of 16 sequences of 128 tokens per GPU, fp16 storage
+with fp32 accumulation, all-ones attention mask, seeded synthetic weights ~N(0, 0.02) and
+inputs ~N(0, 1).  With N > 1 (launched by torch.distributed.run, one process per GPU) every
+rank runs its own batch with replicated weights and no data-path collective (weak scaling).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "BERT-base seq128 sequences/s"
+UNIT = "sequences/s"
+HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
+SEED = 2021
+KERNELS_PER_LAYER = 7  # QKV, attention, O, skip-LN, FFN1(+GELU), FFN2, skip-LN
+
+
+def flops_per_sequence(keep_lin: float = 1.0) -> float:
+    lin = SEQ * 2 * (4 * HIDDEN * HIDDEN + 2 * HIDDEN * FF) * keep_lin
+    attn = 4 * SEQ * SEQ * HIDDEN
+    return LAYERS * (lin + attn)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p["bf16_tflops_sustained"],
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0,
+            "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.active = False
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            }
+            while not self._stop_evt.is_set():
+                if self.active:
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                time.sleep(0.002)
+        except Exception as e:  # NVML missing: report what we know
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop_evt.set()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def build_weights(et, tile_sparsity: float = 0.0):
+    ws = []
+    for layer in range(LAYERS):
+        w = et.synth.encoder_layer_weights(SEED, layer, HIDDEN, FF)
+        if tile_sparsity > 0:
+            for i, name in enumerate(("wqkv", "wo", "w1", "w2")):
+                w[name] = et.synth.prune_tiles(w[name], SEED, 100 * (layer + 1) + 50 + i,
+                                               tile_sparsity)
+        ws.append(w)
+    return ws
+
+
+def cpu_sample(et, orc, ws, batch: int, reps: int):
+    """Times the oracle's encoder layer (all host threads) on `batch` sequences; returns the
+    BERT-base sequences/s this extrapolates to (12 identical layers) and the best time."""
+    import numpy as np
+    x = et.synth.normal(SEED, 7, (batch * SEQ, HIDDEN), 1.0).astype(np.float32)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.encoder_layer(x, ws[0], batch, SEQ, NHEAD, 2, 0)
+        best = min(best, time.perf_counter() - t0)
+    return batch / (best * LAYERS), best
+
+
+def run_reference(args, rank: int):
+    """CPU arm: the reference has no CPU implementation and its CUDA sources are not the
+    product; the oracle (a C++/OpenMP port of the same math) is timed on the host cores."""
+    if rank != 0:
+        return
+    et = entry.load_package()
+    orc = entry.load_oracle()
+    orc.build()
+    ws = [et.synth.encoder_layer_weights(SEED, 0, HIDDEN, FF)]
+    batch = 16
+    import numpy as np
+    x = et.synth.normal(SEED, 7, (batch * SEQ, HIDDEN), 1.0).astype(np.float32)
+    for _ in range(max(args.warmup, 1)):
+        orc.encoder_layer(x, ws[0], batch, SEQ, NHEAD, 2, 0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.encoder_layer(x, ws[0], batch, SEQ, NHEAD, 2, 0)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = batch / (dt * LAYERS)
+    sample = (f"{args.steps} steps of one encoder layer over {batch} sequences; "
+              f"sequences/s = {batch} / (step time x {LAYERS} layers)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * LAYERS * BATCH / batch,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "BERT-base 12L h768 12 heads FFN3072 GELU, batch 16, seq 128, dense",
+                   "note": "CPU evaluation (oracle port, OpenMP) of the same encoder math"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def time_kernel(fn, iters: int = 20, warm: int = 3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels directly")
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="skip the pruned / per-kernel / CPU legs (used under profilers)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    et = entry.load_package()
+    et.lib()
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ws = build_weights(et)
+    layers = [et.EncoderLayer(w, NHEAD, et.ACT_GELU, device=dev) for w in ws]
+    stack = et.EncoderStack(layers, BATCH, SEQ, device=dev)
+    x_host = torch.from_numpy(et.synth.normal(SEED, 7000 + rank, (BATCH * SEQ, HIDDEN), 1.0))
+    x_pinned = x_host.pin_memory()
+    y_pinned = torch.empty_like(x_pinned).pin_memory()
+    x_dev = x_pinned.to(dev)
+
+    stream = torch.cuda.Stream(device=dev)
+    graph = None
+
+    def make_step(st):
+        """Returns (callable, graph): one forward of the whole stack on the current stream."""
+        with torch.cuda.stream(stream):
+            st.forward(x_dev)  # warm: sets kernel attributes before capture
+            stream.synchronize()
+            if args.no_graph:
+                return (lambda: st.forward(x_dev)), None
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                out = st.forward(x_dev)
+            return g.replay, g
+
+    def timed(step_fn, steps, with_copies=False, sampler=None):
+        with torch.cuda.stream(stream):
+            for _ in range(args.warmup):
+                if with_copies:
+                    x_dev.copy_(x_pinned, non_blocking=True)
+                step_fn()
+                if with_copies:
+                    y_pinned.copy_(final_out, non_blocking=True)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if sampler:
+                sampler.active = True
+            e0.record(stream)
+            for _ in range(steps):
+                if with_copies:
+                    x_dev.copy_(x_pinned, non_blocking=True)
+                step_fn()
+                if with_copies:
+                    y_pinned.copy_(final_out, non_blocking=True)
+            e1.record(stream)
+            barrier()
+            if sampler:
+                sampler.active = False
+            return max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+
+    final_out = stack.buf[(LAYERS - 1) & 1]
+    step_fn, graph = make_step(stack)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    dt = timed(step_fn, args.steps, sampler=sampler)
+    dt_e2e = timed(step_fn, args.steps, with_copies=True, sampler=sampler)
+    sampler.stop()
+    code = et.device_error()
+    if code != 0:
+        raise SystemExit(f"device error word = {code}")
+
+    value = world * BATCH * args.steps / dt
+    e2e_value = world * BATCH * args.steps / dt_e2e
+    peaks = measured_peaks()
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": "BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, "
+                               "seq 128, dense weights, all-ones mask",
+                   "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"dp{world}",
+                   "l2": "weights (170 MB fp16) exceed the 126 MB L2 and are streamed every step",
+                   "cuda_graph": graph is not None},
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": x_pinned.numel() * 2, "d2h_bytes_per_step": y_pinned.numel() * 2},
+        "gpu_launches": world * args.steps * LAYERS * KERNELS_PER_LAYER,
+        "stack_tflops": value / world * flops_per_sequence() * 1e-12,
+        "stack_frac_of_peak": value / world * flops_per_sequence() * 1e-12 / peaks["bf16_tflops_sustained"],
+    }
+
+    if not args.skip_extras:
+        # ---- dominant kernel in isolation: the FFN1 GEMM [T, 768] x [3072, 768]^T + GELU ----
+        T = BATCH * SEQ
+        with torch.cuda.stream(stream):
+            w1 = torch.from_numpy(ws[0]["w1"]).to(dev)
+            b1 = torch.from_numpy(ws[0]["b1"]).to(dev)
+            xin = x_dev
+            per_kernel = {}
+            shapes = {"qkv": (HIDDEN, 3 * HIDDEN, 0), "o": (HIDDEN, HIDDEN, 0),
+                      "ffn1_gelu": (HIDDEN, FF, 2), "ffn2": (FF, HIDDEN, 0)}
+            for name, (inn, out, act) in shapes.items():
+                a = torch.from_numpy(et.synth.normal(1, 1, (T, inn), 1.0)).to(dev)
+                w = torch.from_numpy(et.synth.normal(1, 2, (out, inn), 0.02)).to(dev)
+                b = torch.zeros(out, dtype=torch.float16, device=dev)
+                sec = time_kernel(lambda: et.linear_dense(a, w, b, act), iters=50)
+                per_kernel[name] = {"us": sec * 1e6, "tflops": 2.0 * T * inn * out / sec * 1e-12}
+            qkv = torch.from_numpy(et.synth.normal(1, 3, (T, 3 * HIDDEN), 1.0)).to(dev)
+            sec = time_kernel(lambda: et.attention(qkv[:, :HIDDEN], qkv[:, HIDDEN:2 * HIDDEN],
+                                                   qkv[:, 2 * HIDDEN:], BATCH, SEQ, NHEAD, 64, 64),
+                              iters=50)
+            per_kernel["attention"] = {"us": sec * 1e6,
+                                       "tflops": 4.0 * BATCH * SEQ * SEQ * HIDDEN / sec * 1e-12}
+            a = torch.from_numpy(et.synth.normal(1, 4, (T, HIDDEN), 1.0)).to(dev)
+            g = torch.ones(HIDDEN, dtype=torch.float16, device=dev)
+            sec = time_kernel(lambda: et.skip_layernorm(a, a, g, g), iters=50)
+            per_kernel["skip_layernorm"] = {"us": sec * 1e6, "gbs": 6.0 * T * HIDDEN / sec * 1e-9}
+        k = per_kernel["ffn1_gelu"]
+        line["roofline"] = {"bound": "tensor", "kernel": "gemm_f16_kernel (FFN1 + GELU, "
+                            f"[{T}x768]x[3072x768]^T)", "achieved": k["tflops"],
+                            "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                            "frac": k["tflops"] / peaks["bf16_tflops"], "traffic": None,
+                            "peak_source": peaks["source"] + " (burst, kernel timed alone)"}
+        line["kernels"] = per_kernel
+
+        # ---- the 80 % tile-pruned stack at the same batch ----
+        wsp = build_weights(et, 0.8)
+        stack_p = et.EncoderStack([et.EncoderLayer(w, NHEAD, et.ACT_GELU, device=dev,
+                                                   tile_sparse=True) for w in wsp], BATCH, SEQ, dev)
+        step_p, _ = make_step(stack_p)
+        dt_p = timed(step_p, args.steps)
+        line["tile_pruned_80"] = {"value": world * BATCH * args.steps / dt_p, "unit": UNIT,
+                                  "ms_per_step": dt_p / args.steps * 1e3,
+                                  "speedup_vs_dense": dt / dt_p}
+
+        # ---- CPU baseline (rank 0, N = 1 only) ----
+        if world == 1:
+            orc = entry.load_oracle()
+            orc.build()
+            cpu_value, best = cpu_sample(et, orc, ws, 128, 3)
+            line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": orc.num_threads(),
+                                    "kind": "port",
+                                    "sample": "best of 3 runs of one encoder layer over 128 sequences "
+                                              f"({best:.2f} s each), x12 layers extrapolated"}
+
+    line["clocks"] = sampler.summary()
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

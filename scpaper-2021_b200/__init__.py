@@ -121,7 +121,7 @@ def linear_tile(x, row_ptr, row_off, tiles, out, bias=None, act=ACT_NONE):
 def linear_row(x, row_id, rows, out, bias=None, act=ACT_NONE):
     T, inn = x.shape
     y = _empty((T, out), x)
-    nn = int(row_id.shape[0])
+    nn = 0 if row_id is None else int(row_id.shape[0])
     check(lib().et_linear_row_fwd(_p(row_id) if nn else None, _p(rows) if nn else None, c_int(nn),
                                   _p(bias), _p(x), _p(y), c_int(T), c_int(inn), c_int(out),
                                   c_int(act), _stream()), "et_linear_row_fwd")
@@ -153,7 +153,7 @@ def linear_col(x, col_id, cols, bias=None, act=ACT_NONE, scratch=None):
 def linear_1x16(x, tile_idx, row_idx, data, out, bias=None, act=ACT_NONE):
     T, inn = x.shape
     y = _empty((T, out), x)
-    nvec = int(row_idx.shape[0])
+    nvec = 0 if row_idx is None else int(row_idx.shape[0])
     check(lib().et_linear_1x16_fwd(_p(tile_idx), _p(row_idx) if nvec else None,
                                    _p(data) if nvec else None, c_int(nvec), _p(bias), _p(x), _p(y),
                                    c_int(T), c_int(inn), c_int(out), c_int(act), _stream()),
@@ -164,7 +164,7 @@ def linear_1x16(x, tile_idx, row_idx, data, out, bias=None, act=ACT_NONE):
 def linear_csr(x, indptr, indices, data, out, bias=None, act=ACT_NONE):
     T, inn = x.shape
     y = _empty((T, out), x)
-    nnz = int(indices.shape[0])
+    nnz = 0 if indices is None else int(indices.shape[0])
     check(lib().et_linear_csr_fwd(_p(indptr), _p(indices) if nnz else None,
                                   _p(data) if nnz else None, c_int(nnz), _p(bias), _p(x), _p(y),
                                   c_int(T), c_int(inn), c_int(out), c_int(act), _stream()),

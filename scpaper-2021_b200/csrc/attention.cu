@@ -35,6 +35,11 @@ struct AttnArgs {
     int mask_kind;
     float scale_log2;  // scale * log2(e)
     int* err_word;
+    // column-compressed V (null for a dense V): feature list and per-head ranges into it
+    const int* col_id;
+    const int* head_ptr;
+    int nva_max;    // 64-feature atoms reserved for a V block in shared memory
+    int tmem_cols;  // tensor-memory columns to allocate (256 or 512)
 };
 
 __global__ void __launch_bounds__(ATT_THREADS, 2)
@@ -44,11 +49,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     const int nqa = (a.dh_qk + 63) >> 6;  // 64-feature atoms of Q / K
-    const int nva = (a.dh_v + 63) >> 6;   // 64-feature atoms of V
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + nqa * ATOM_BYTES;
     uint8_t* sV = sK + nqa * ATOM_BYTES;
-    uint8_t* sP = sV + nva * ATOM_BYTES;
+    uint8_t* sP = sV + a.nva_max * ATOM_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATOM_BYTES);
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;
@@ -67,6 +71,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int q0 = blockIdx.x * BQ;
     const int h = blockIdx.y;
     const int b = blockIdx.z;
+
+    // V window of this head: feature offset v_x0 (a multiple of 8 so the TMA start is 16-byte
+    // aligned), v_n accumulator columns, of which [v_shift, v_shift + v_cnt) are this head's.
+    int v_x0 = h * a.dh_v, v_shift = 0, v_cnt = a.dh_v, v_n = a.dh_v;
+    if (a.head_ptr != nullptr) {
+        const int c0 = a.head_ptr[h];
+        v_cnt = a.head_ptr[h + 1] - c0;
+        v_x0 = c0 & ~7;
+        v_shift = c0 - v_x0;
+        v_n = (v_shift + v_cnt + 15) & ~15;
+        v_n = v_n < 16 ? 16 : v_n;
+    }
+    const int nva = (v_n + 63) >> 6;  // 64-feature atoms of V actually loaded
 
     int kv_len = a.seq;
     if (a.mask_kind == ET_MASK_PADDING) {
@@ -94,7 +111,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, TMEM_COLS_ATT);
+        tmem_alloc(tmem_slot, a.tmem_cols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -130,7 +147,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 mbar_arrive_expect_tx(v_full, nva * ATOM_BYTES);
                 for (int t = 0; t < nva; ++t)
-                    tma_load_3d(sV + t * ATOM_BYTES, &tmV, v_full, h * a.dh_v + t * 64, j * BKV, b);
+                    tma_load_3d(sV + t * ATOM_BYTES, &tmV, v_full, v_x0 + t * 64, j * BKV, b);
                 ++v_issued;
             }
             if (*abort_flag) {
@@ -149,7 +166,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // ---------------- MMA issuer ----------------
         if (n_kv > 0 && elect_one()) {
             const uint32_t idesc_s = make_idesc_f16(BQ, BKV, 0, 0);
-            const uint32_t idesc_o = make_idesc_f16(BQ, a.dh_v, 0, 1);  // V is MN-major
+            const uint32_t idesc_o = make_idesc_f16(BQ, v_n, 0, 1);  // V is MN-major
             const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV),
                            p_addr = smem_u32(sP);
             bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
@@ -248,7 +265,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after_sync();
                 if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
-                    for (int c = 0; c < (a.dh_v >> 4); ++c) {
+                    for (int c = 0; c < (v_n >> 4); ++c) {
                         uint32_t o[16];
                         tmem_ld16(tmem_O + lane_off + c * 16, o);
                         tmem_ld_wait();
@@ -305,7 +322,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             __half* zrow = a.Z + (static_cast<size_t>(b) * a.seq + (qrow < a.seq ? qrow : 0)) * a.ldz +
                            static_cast<size_t>(h) * a.dh_v;
-            for (int c = 0; c < (a.dh_v >> 4); ++c) {
+            if (a.head_ptr != nullptr && qrow < a.seq) {
+                // pruned features of this head are zero; kept ones are scattered below
+                for (int c = 0; c < (a.dh_v >> 3); ++c)
+                    *reinterpret_cast<uint4*>(zrow + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            for (int c = 0; c < (v_n >> 4); ++c) {
                 uint32_t o[16];
                 if (n_kv > 0) {
                     tmem_ld16(tmem_O + lane_off + c * 16, o);
@@ -315,17 +337,28 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     for (int i = 0; i < 16; ++i) o[i] = 0u;
                 }
                 if (qrow < a.seq) {
-                    uint4 w0, w1;
-                    w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
-                    w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
-                    w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
-                    w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
-                    w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
-                    w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
-                    w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
-                    w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
-                    *reinterpret_cast<uint4*>(zrow + c * 16) = w0;
-                    *reinterpret_cast<uint4*>(zrow + c * 16 + 8) = w1;
+                    if (a.head_ptr == nullptr) {
+                        uint4 w0, w1;
+                        w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+                        w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+                        w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+                        w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+                        w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+                        w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+                        w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+                        w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+                        *reinterpret_cast<uint4*>(zrow + c * 16) = w0;
+                        *reinterpret_cast<uint4*>(zrow + c * 16 + 8) = w1;
+                    } else {
+                        const int* ids = a.col_id + a.head_ptr[h];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int k = c * 16 + i - v_shift;  // index into this head's list
+                            if (k >= 0 && k < v_cnt)
+                                a.Z[(static_cast<size_t>(b) * a.seq + qrow) * a.ldz + __ldg(ids + k)] =
+                                    __float2half_rn(__uint_as_float(o[i]) * inv);
+                        }
+                    }
                 }
             }
         }
@@ -333,15 +366,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS_ATT);
+    if (warp == 1) tmem_dealloc(tmem_base, a.tmem_cols);
 }
 
 }  // namespace
 
-int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
-                     int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,
-                     int mask_kind, const __half* mask, const int* valid_len, float scale,
-                     cudaStream_t stream) {
+namespace {
+int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
+                          int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
+                          int ldz, int mask_kind, const __half* mask, const int* valid_len,
+                          float scale, const int* col_id, const int* head_ptr, int nnz_col,
+                          cudaStream_t stream) {
     if (!Q || !K || !V || !Z || batch <= 0 || seq <= 0 || nhead <= 0 || dh_qk <= 0 || dh_v <= 0)
         return ET_ERR_INVALID_ARG;
     if (mask_kind < ET_MASK_NONE || mask_kind > ET_MASK_ADDITIVE) return ET_ERR_INVALID_ARG;
@@ -349,8 +384,10 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
     if (mask_kind == ET_MASK_PADDING && !valid_len) return ET_ERR_INVALID_ARG;
     if (dh_qk % 16 || dh_v % 16 || dh_qk > 128 || dh_v > 128) return ET_ERR_SHAPE;
     if (ldq % 8 || ldk % 8 || ldv % 8 || ldz % 8) return ET_ERR_SHAPE;
-    if (ldq < nhead * dh_qk || ldk < nhead * dh_qk || ldv < nhead * dh_v || ldz < nhead * dh_v)
-        return ET_ERR_SHAPE;
+    const bool pruned = head_ptr != nullptr;
+    if (pruned && (!col_id || nnz_col <= 0)) return ET_ERR_INVALID_ARG;
+    if (ldq < nhead * dh_qk || ldk < nhead * dh_qk || ldz < nhead * dh_v) return ET_ERR_SHAPE;
+    if (ldv < (pruned ? nnz_col : nhead * dh_v)) return ET_ERR_SHAPE;
     if (batch > 65535 || nhead > 65535) return ET_ERR_SHAPE;
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(Z)) return ET_ERR_ALIGNMENT;
     int* err = device_error_word();
@@ -368,16 +405,18 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
     int st;
     if ((st = make(&tmQ, Q, ldq, nhead * dh_qk)) != ET_OK) return st;
     if ((st = make(&tmK, K, ldk, nhead * dh_qk)) != ET_OK) return st;
-    if ((st = make(&tmV, V, ldv, nhead * dh_v)) != ET_OK) return st;
+    if ((st = make(&tmV, V, ldv, pruned ? nnz_col : nhead * dh_v)) != ET_OK) return st;
 
-    const int nqa = (dh_qk + 63) / 64, nva = (dh_v + 63) / 64;
+    // a compressed V window may start up to 7 features before the head's first kept feature
+    const int v_n_max = pruned ? ((7 + dh_v + 15) & ~15) : dh_v;
+    const int nqa = (dh_qk + 63) / 64, nva = (v_n_max + 63) / 64;
     const int smem_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + 256 + 1024;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (2 * 2 + 2 + 2) * ATOM_BYTES + 256 + 1024) != cudaSuccess)
+                                 (2 * 2 + 3 + 2) * ATOM_BYTES + 256 + 1024) != cudaSuccess)
             return ET_ERR_CUDA;
         attr_set[dev] = true;
     }
@@ -394,9 +433,22 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
     a.mask_kind = mask_kind;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.err_word = err;
+    a.col_id = col_id;
+    a.head_ptr = head_ptr;
+    a.nva_max = nva;
+    a.tmem_cols = (128 + v_n_max > 256) ? 512 : TMEM_COLS_ATT;
     dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
     attention_kernel<<<grid, ATT_THREADS, smem_bytes, stream>>>(tmQ, tmK, tmV, a);
     return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+}
+}  // namespace
+
+int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
+                     int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,
+                     int mask_kind, const __half* mask, const int* valid_len, float scale,
+                     cudaStream_t stream) {
+    return launch_attention_impl(Q, K, V, Z, batch, seq, nhead, dh_qk, dh_v, ldq, ldk, ldv, ldz,
+                                 mask_kind, mask, valid_len, scale, nullptr, nullptr, 0, stream);
 }
 
 }  // namespace et
@@ -412,6 +464,20 @@ int et_attention_fwd(const et_half* Q, const et_half* K, const et_half* V, et_ha
         reinterpret_cast<const __half*>(V), reinterpret_cast<__half*>(Z), batch, seq, nhead, dh_qk,
         dh_v, ldq, ldk, ldv, ldz, mask_kind, reinterpret_cast<const __half*>(mask), valid_len,
         scale, static_cast<cudaStream_t>(stream));
+}
+
+int et_attention_pruned_v_fwd(const et_half* Q, const et_half* K, const et_half* Vc,
+                              const int32_t* col_id, const int32_t* head_ptr, int nnz_col,
+                              et_half* Z, int batch, int seq, int nhead, int dh_qk, int dh_v,
+                              int ldq, int ldk, int ldz, int mask_kind, const et_half* mask,
+                              const int32_t* valid_len, float scale, et_stream stream) {
+    if (!col_id || !head_ptr || nnz_col <= 0) return ET_ERR_INVALID_ARG;
+    if (nnz_col % 8) return ET_ERR_SHAPE;  // row pitch of the compressed V must be 16-byte aligned
+    return et::launch_attention_impl(
+        reinterpret_cast<const __half*>(Q), reinterpret_cast<const __half*>(K),
+        reinterpret_cast<const __half*>(Vc), reinterpret_cast<__half*>(Z), batch, seq, nhead, dh_qk,
+        dh_v, ldq, ldk, nnz_col, ldz, mask_kind, reinterpret_cast<const __half*>(mask), valid_len,
+        scale, col_id, head_ptr, nnz_col, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
