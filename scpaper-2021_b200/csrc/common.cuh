@@ -166,6 +166,23 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Tiled store shared -> global (bulk async group); rows / columns outside the tensor are
+// clipped by the hardware.  The issuing thread must commit and wait before the shared
+// memory is reused or the CTA exits.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x,
+                                             int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes,
                                           uint64_t* bar) {

@@ -16,6 +16,16 @@ namespace et {
 
 namespace {
 
+// Optional per-CTA timestamps for bring-up builds (-DET_TIMELINE); compiled out otherwise.
+#ifdef ET_TIMELINE
+__device__ long long et_timeline[65536];
+#define ET_TL(slot)                                                                       \
+    et_timeline[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = \
+        clock64()
+#else
+#define ET_TL(slot) ((void)0)
+#endif
+
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
@@ -25,18 +35,38 @@ template <int BN, int STAGES>
 struct GemmCfg {
     static constexpr int B_STAGE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int BAR_BYTES = 256;
+    static constexpr int BAR_BYTES = 256 + 8 * BN;  // barriers + staged bias (fp32) and column ids
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + align slack
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
 };
 
-template <int BN, int STAGES, int MIN_CTAS>
+// Arguments beyond the two tensor maps.  Groups (blockIdx.z) share X and use the g-th
+// weight matrix / bias; their output rows are interleaved: row m of group g lands at
+// (m / grp_rows) * grp_stride + g * grp_rows + m % grp_rows  (grp_rows == 0: plain rows).
+struct GemmArgs {
+    __half* Y;
+    const __half* bias;
+    const int* col_map;
+    int ldy, scatter, M, N, K, act;
+    int grp_rows, grp_stride;
+    int tma_store;  // 1: plain row-major output written through the Y tensor map
+    int* err_word;
+};
+
+// B_MN == false: W is [N, K] with K contiguous (the Linear weight layout).
+// B_MN == true : W is [groups][K, N] with N contiguous; its tiles are consumed in place
+//                as MN-major operands (64-column atoms of 64 K-rows, 8 KB each).
+template <int BN, int STAGES, int MIN_CTAS, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, MIN_CTAS)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                __half* __restrict__ Y, int ldy, const __half* __restrict__ bias,
-                const int* __restrict__ col_map, int scatter, int M, int N, int K, int act,
-                int* err_word) {
+                const __grid_constant__ CUtensorMap tmY, const GemmArgs g) {
     using Cfg = GemmCfg<BN, STAGES>;
+    __half* __restrict__ Y = g.Y;
+    const int grp = blockIdx.z;
+    const __half* __restrict__ bias = g.bias ? g.bias + static_cast<size_t>(grp) * g.N : nullptr;
+    const int* __restrict__ col_map = g.col_map;
+    const int ldy = g.ldy, scatter = g.scatter, M = g.M, N = g.N, K = g.K, act = g.act;
+    int* err_word = g.err_word;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -55,6 +85,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int num_kb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
+        ET_TL(0);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
@@ -71,6 +102,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) ET_TL(1);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -87,9 +119,18 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
                 tma_load_2d(sA + s * A_STAGE_BYTES, &tmA, &full_bar[s], kb * BK, m0);
-                tma_load_2d(sB + s * Cfg::B_STAGE_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+                if (B_MN) {
+#pragma unroll
+                    for (int t = 0; t < BN / 64; ++t)
+                        tma_load_3d(sB + s * Cfg::B_STAGE_BYTES + t * (BK * 128), &tmB, &full_bar[s],
+                                    n0 + t * 64, kb * BK, grp);
+                } else {
+                    tma_load_2d(sB + s * Cfg::B_STAGE_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+                }
                 ++issued;
+                if (kb == 0) ET_TL(2);
             }
+            ET_TL(3);
             if (*abort_flag) {
                 // Let copies already in flight land before the CTA's shared memory is released.
                 const int first = issued > STAGES ? issued - STAGES : 0;
@@ -101,7 +142,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
-            constexpr uint32_t idesc = make_idesc_f16(BM, BN, 0, 0);
+            constexpr uint32_t idesc = make_idesc_f16(BM, BN, 0, B_MN ? 1 : 0);
             bool ok = true;
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
@@ -112,22 +153,44 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     break;
                 }
                 tc_fence_after_sync();
+                if (kb == 0) ET_TL(4);
                 const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
                 const uint32_t b_addr = smem_u32(sB + s * Cfg::B_STAGE_BYTES);
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k) {
                     const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024, SWZ_128B);
-                    const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B);
+                    // MN-major: 16 K-rows = two 8-row groups of 128 bytes (SBO 1024); the next
+                    // 64-column atom sits BK * 128 bytes further (LBO).
+                    const uint64_t bd =
+                        B_MN ? make_smem_desc(b_addr + k * 2048, BK * 128, 1024, SWZ_128B)
+                             : make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B);
                     mma_f16_ss(tmem_base, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
                 }
                 mma_commit(&empty_bar[s]);
             }
             if (ok) mma_commit(acc_bar);
+            ET_TL(5);
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         const int row = m0 + q * 32 + lane;
+        size_t out_row = static_cast<size_t>(row);
+        if (g.grp_rows > 0)
+            out_row = static_cast<size_t>(row / g.grp_rows) * g.grp_stride +
+                      static_cast<size_t>(grp) * g.grp_rows + row % g.grp_rows;
+        // While the main loop runs, stage this tile's bias (and output column ids) in shared
+        // memory: read per chunk from global they cost a cold L2 round trip each time.
+        float* s_bias = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
+        int* s_col = reinterpret_cast<int*>(s_bias + BN);
+        for (int i = threadIdx.x - 64; i < BN; i += 128) {
+            const int n = n0 + i;
+            int feat = n;
+            if (col_map != nullptr && n < N) feat = __ldg(col_map + n);
+            s_col[i] = feat;
+            s_bias[i] = (bias != nullptr && n < N) ? __half2float(__ldg(bias + feat)) : 0.f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         bool ok = true;
         if (num_kb > 0) {
             ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
@@ -136,6 +199,63 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
+            if (threadIdx.x == 64) ET_TL(6);
+            if (g.tma_store) {
+                // Coalesced path: each warp converts its 32 rows into a 128-byte-swizzled
+                // staging tile (64 columns = 128 bytes per row, conflict-free 16-byte writes) in
+                // the now idle pipeline stages and hands it to a TMA store.
+                uint8_t* stg = smem + q * (BN / 64) * 4096;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 >= N) break;  // warp-uniform
+                    uint32_t r[32];
+                    if (num_kb > 0) {
+                        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    }
+                    if (threadIdx.x == 64 && c == 0) ET_TL(9);
+                    uint8_t* srow = stg + (c >> 1) * 4096 + lane * 128;
+#pragma unroll
+                    for (int gq = 0; gq < 4; ++gq) {
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[gq * 8 + j]);
+                        {
+                            const float4 b0 = *reinterpret_cast<const float4*>(s_bias + c * 32 + gq * 8);
+                            const float4 b1 =
+                                *reinterpret_cast<const float4*>(s_bias + c * 32 + gq * 8 + 4);
+                            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], act);
+                        uint4 o;
+                        o.x = pack_half2(v[0], v[1]);
+                        o.y = pack_half2(v[2], v[3]);
+                        o.z = pack_half2(v[4], v[5]);
+                        o.w = pack_half2(v[6], v[7]);
+                        const int chunk = (((c & 1) << 2) + gq) ^ (lane & 7);
+                        *reinterpret_cast<uint4*>(srow + chunk * 16) = o;
+                    }
+                    if (threadIdx.x == 64 && c == 0) ET_TL(10);
+                    if ((c & 1) || col0 + 32 >= N) {  // a 64-column group is complete
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && m0 + q * 32 < M)
+                            tma_store_2d(&tmY, stg + (c >> 1) * 4096, n0 + (c >> 1) * 64, m0 + q * 32);
+                        if (threadIdx.x == 64 && c == 1) ET_TL(11);
+                    }
+                }
+                if (threadIdx.x == 64) ET_TL(12);
+                if (lane == 0) {
+                    tma_store_commit();
+                    tma_store_wait_read();
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col0 = n0 + c * 32;
@@ -150,24 +270,15 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 if (row < M) {
                     if (col_map == nullptr) {
-                        __half* yrow = Y + static_cast<size_t>(row) * ldy + col0;
+                        __half* yrow = Y + out_row * ldy + col0;
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             if (col0 + g * 8 >= N) break;
                             float v[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
-                            if (bias != nullptr) {
-                                const uint4 bq =
-                                    __ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8));
-                                const __half2* bh = reinterpret_cast<const __half2*>(&bq);
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float2 bf = __half22float2(bh[j]);
-                                    v[2 * j] += bf.x;
-                                    v[2 * j + 1] += bf.y;
-                                }
-                            }
+                            for (int j = 0; j < 8; ++j) v[j] += s_bias[c * 32 + g * 8 + j];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], act);
                             uint4 o;
@@ -184,11 +295,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         for (int j = 0; j < 32; ++j) {
                             const int n = col0 + j;
                             if (n < N) {
-                                const int feat = __ldg(col_map + n);
-                                float v = __uint_as_float(r[j]);
-                                if (bias != nullptr) v += __half2float(__ldg(bias + feat));
+                                const int feat = s_col[c * 32 + j];
+                                float v = __uint_as_float(r[j]) + s_bias[c * 32 + j];
                                 v = apply_act(v, act);
-                                Y[static_cast<size_t>(row) * ldy + (scatter ? feat : n)] =
+                                Y[out_row * ldy + (scatter ? feat : n)] =
                                     __float2half_rn(v);
                             }
                         }
@@ -198,8 +308,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     }
 
+    if (threadIdx.x == 64) ET_TL(7);
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) ET_TL(8);
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
@@ -245,12 +357,11 @@ __global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __re
     }
 }
 
-template <int BN, int STAGES, int MIN_CTAS>
-int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, __half* Y, int ldy,
-               const __half* bias, const int* col_map, int scatter, int M, int N, int K, int act,
-               cudaStream_t stream) {
+template <int BN, int STAGES, int MIN_CTAS, bool B_MN>
+int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+               const GemmArgs& args, int groups, cudaStream_t stream) {
     using Cfg = GemmCfg<BN, STAGES>;
-    auto kern = gemm_f16_kernel<BN, STAGES, MIN_CTAS>;
+    auto kern = gemm_f16_kernel<BN, STAGES, MIN_CTAS, B_MN>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -260,15 +371,14 @@ int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, __half* Y, int ld
             return ET_ERR_CUDA;
         attr_set[dev] = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, Y, ldy, bias, col_map, scatter,
-                                                          M, N, K, act, device_error_word());
+    dim3 grid((args.N + BN - 1) / BN, (args.M + BM - 1) / BM, groups);
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmY, args);
     return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
 }
 
 int g_force_bn = 0;
 
-int pick_bn(int M, int N) {
+int pick_bn(int M, int N, int groups = 1) {
     if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) return g_force_bn;
     const int sms = sm_count() > 0 ? sm_count() : 148;
     const int mt = (M + BM - 1) / BM;
@@ -276,7 +386,7 @@ int pick_bn(int M, int N) {
     long best_cost = -1;
     const int cands[3] = {256, 128, 64};
     for (int bn : cands) {
-        const long tiles = static_cast<long>(mt) * ((N + bn - 1) / bn);
+        const long tiles = static_cast<long>(mt) * ((N + bn - 1) / bn) * groups;
         const long waves = (tiles + sms - 1) / sms;
         const long cost = waves * (bn + 48);
         if (best_cost < 0 || cost < best_cost) {
@@ -318,17 +428,80 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
         int st = make_tensor_map_f16(&tmB, W, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != ET_OK) return st;
     }
-    switch (bn) {
-        case 256:
-            return launch_cfg<256, 4, 1>(tmA, tmB, Y, ldy, bias, col_map, scatter, M, N, K, act,
-                                         stream);
-        case 64:
-            return launch_cfg<64, 4, 2>(tmA, tmB, Y, ldy, bias, col_map, scatter, M, N, K, act,
-                                        stream);
-        default:
-            return launch_cfg<128, 3, 2>(tmA, tmB, Y, ldy, bias, col_map, scatter, M, N, K, act,
-                                         stream);
+    CUtensorMap tmY = tmA;  // placeholder when the index-list epilogue is used
+    if (col_map == nullptr) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldy) * 2};
+        const uint32_t box[2] = {64, 32};
+        int st = make_tensor_map_f16(&tmY, Y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
     }
+    GemmArgs args;
+    args.tma_store = col_map == nullptr ? 1 : 0;
+    args.Y = Y;
+    args.bias = bias;
+    args.col_map = col_map;
+    args.ldy = ldy;
+    args.scatter = scatter;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.act = act;
+    args.grp_rows = 0;
+    args.grp_stride = 0;
+    args.err_word = device_error_word();
+    switch (bn) {
+        case 256: return launch_cfg<256, 4, 1, false>(tmA, tmB, tmY, args, 1, stream);
+        case 64: return launch_cfg<64, 4, 2, false>(tmA, tmB, tmY, args, 1, stream);
+        default: return launch_cfg<128, 3, 2, false>(tmA, tmB, tmY, args, 1, stream);
+    }
+}
+
+// Y[(m / grp_rows) * groups * grp_rows + g * grp_rows + m % grp_rows, :] = X[m, :] . W[g] + bias[g]
+// for W [groups][K, N] row-major (N contiguous), bias [groups][N] or null.
+int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const __half* bias,
+                               __half* Y, int M, int N, int K, int groups, int grp_rows,
+                               cudaStream_t stream) {
+    if (!X || !W || !Y || M <= 0 || N <= 0 || K <= 0 || groups <= 0 || grp_rows <= 0)
+        return ET_ERR_INVALID_ARG;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(Y) || (bias && !aligned16(bias)))
+        return ET_ERR_ALIGNMENT;
+    if (ldx % 8 || K % 8 || N % 8 || groups > 65535) return ET_ERR_SHAPE;
+    if (!device_error_word()) return ET_ERR_NO_DEVICE;
+    const int bn = pick_bn(M, N, groups) == 64 ? 64 : 128;
+    CUtensorMap tmA, tmB;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
+        const uint32_t box[2] = {BK, BM};
+        int st = make_tensor_map_f16(&tmA, X, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
+    }
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K),
+                                  static_cast<uint64_t>(groups)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(N) * 2,
+                                     static_cast<uint64_t>(N) * 2 * static_cast<uint64_t>(K)};
+        const uint32_t box[3] = {64, BK, 1};
+        int st = make_tensor_map_f16(&tmB, W, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
+    }
+    GemmArgs args;
+    args.tma_store = 0;
+    args.Y = Y;
+    args.bias = bias;
+    args.col_map = nullptr;
+    args.ldy = N;
+    args.scatter = 0;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.act = ET_ACT_NONE;
+    args.grp_rows = grp_rows;
+    args.grp_stride = groups * grp_rows;
+    args.err_word = device_error_word();
+    if (bn == 64) return launch_cfg<64, 4, 2, true>(tmA, tmB, tmA, args, groups, stream);
+    return launch_cfg<128, 3, 2, true>(tmA, tmB, tmA, args, groups, stream);
 }
 
 }  // namespace et
@@ -400,6 +573,16 @@ int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
                            reinterpret_cast<const __half*>(cols), nn_col,
                            reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Y),
                            out, nullptr, 0, T, out, nn_col, act, s);
+}
+
+int et_linear_vo_fwd(const et_half* X, const et_half* Wvo_t, const et_half* bias, et_half* VO,
+                     int batch, int seq, int nhead, int emdim, et_stream stream) {
+    if (batch <= 0 || seq <= 0 || nhead <= 0 || emdim <= 0) return ET_ERR_INVALID_ARG;
+    if (emdim % 16) return ET_ERR_SHAPE;
+    return et::launch_gemm_f16_grouped_kn(
+        reinterpret_cast<const __half*>(X), emdim, reinterpret_cast<const __half*>(Wvo_t),
+        reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(VO), batch * seq, emdim,
+        emdim, nhead, seq, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

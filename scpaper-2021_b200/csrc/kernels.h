@@ -13,6 +13,11 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
                     __half* Y, int ldy, const int* col_map, int scatter, int M, int N, int K,
                     int act, cudaStream_t stream);
 
+// Grouped GEMM over weights stored [groups][K, N] (N contiguous); see gemm_dense.cu.
+int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const __half* bias,
+                               __half* Y, int M, int N, int K, int groups, int grp_rows,
+                               cudaStream_t stream);
+
 // Tile-CSR Linear (see linear_tile.cu).
 int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
                        const __half* bias, const __half* X, __half* Y, int T, int in, int out,

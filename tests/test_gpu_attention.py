@@ -112,3 +112,78 @@ def test_attention_is_deterministic(et, cuda):
     a = et.attention(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), 2, 256, 4, 64, 64, 1)
     b = et.attention(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), 2, 256, 4, 64, 64, 1)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("batch,seq,nhead,dh,sparsity", [
+    (2, 128, 4, 64, 0.5), (1, 200, 12, 64, 0.3), (2, 64, 2, 32, 0.75), (1, 300, 3, 128, 0.5),
+])
+@pytest.mark.parametrize("mask_kind", [0, 1])
+def test_attention_pruned_v(et, orc, cuda, batch, seq, nhead, dh, sparsity, mask_kind):
+    """V arrives column-compressed (the output of a row-pruned V projection); Z is written in
+    full with zeros at pruned features (Attention/kernels.cu:425-459 + the missing store)."""
+    T, vdim = batch * seq, nhead * dh
+    q, k, v = _qkv(et, 300 + seq, batch, seq, nhead, dh, dh)
+    col_id = et.synth.choose_ids(301, 5, vdim, sparsity, multiple=8)
+    if seq == 64:  # leave one head without any kept feature
+        col_id = col_id[col_id >= dh]
+        col_id = col_id[: len(col_id) // 8 * 8]
+    hp = et.synth.head_ptr_for(col_id, nhead, vdim)
+    vc = np.ascontiguousarray(v[:, col_id])
+    z = et.attention_pruned_v(_dev(q, cuda), _dev(k, cuda), _dev(vc, cuda), _dev(col_id, cuda),
+                              _dev(hp, cuda), batch, seq, nhead, dh, dh, mask_kind)
+    assert et.device_error() == 0
+    ref = orc.attention_pruned_v(q, k, vc, col_id, hp, batch, seq, nhead, dh, dh, mask_kind)
+    assert_close(z.float().cpu().numpy(), ref, f"pruned V s{seq} h{nhead}",
+                 dump=f"prunedv_{seq}_{nhead}_{mask_kind}")
+    pruned = np.setdiff1d(np.arange(vdim), col_id)
+    assert np.all(z.float().cpu().numpy()[:, pruned] == 0)
+
+
+@pytest.mark.parametrize("batch,seq,nhead,dh,emdim", [
+    (2, 128, 4, 64, 256), (1, 128, 12, 64, 768), (2, 96, 2, 32, 80), (1, 300, 3, 64, 320),
+    (1, 512, 2, 64, 256),
+])
+@pytest.mark.parametrize("mask_kind", [0, 1])
+def test_fused_vo_attention(et, orc, cuda, batch, seq, nhead, dh, emdim, mask_kind):
+    """out = sum_h P_h (X W_vo,h + b_h) + b_o (Fused_attention.cu:94-115, Linear_VO.h:38-58)."""
+    T = batch * seq
+    q = et.synth.normal(400 + seq, 1, (T, nhead * dh), 1.0)
+    k = et.synth.normal(400 + seq, 2, (T, nhead * dh), 1.0)
+    x = et.synth.normal(400 + seq, 3, (T, emdim), 1.0)
+    wvo = et.synth.normal(400 + seq, 4, (nhead, emdim, emdim), 0.05)
+    bvo = et.synth.normal(400 + seq, 5, (nhead, emdim), 0.05)
+    bo = et.synth.normal(400 + seq, 6, (emdim,), 0.1)
+    vo = et.linear_vo(_dev(x, cuda), _dev(wvo, cuda), _dev(bvo, cuda), batch, seq, nhead, emdim)
+    assert et.device_error() == 0
+    # VO[b][h] = X_b W_vo[h] + b[h]
+    xf = x.astype(np.float32).reshape(batch, seq, emdim)
+    vo_ref = np.einsum("bse,heo->bhso", xf, wvo.astype(np.float32)) + \
+        bvo.astype(np.float32)[None, :, None, :]
+    assert_close(vo.float().cpu().numpy(), vo_ref.reshape(-1, emdim), "linear_vo",
+                 dump=f"linvo_{seq}_{emdim}")
+    out = et.fused_vo_attention(_dev(q, cuda), _dev(k, cuda), vo, _dev(bo, cuda), batch, seq,
+                                nhead, dh, emdim, mask_kind)
+    assert et.device_error() == 0
+    vo16 = vo.float().cpu().numpy()
+    ref = orc.fused_vo_attention(q, k, vo16, bo, batch, seq, nhead, dh, emdim, mask_kind)
+    assert_close(out.float().cpu().numpy(), ref, f"fused VO s{seq} e{emdim}",
+                 dump=f"fusedvo_{seq}_{emdim}_{mask_kind}")
+    out2 = et.fused_vo_attention(_dev(q, cuda), _dev(k, cuda), vo, _dev(bo, cuda), batch, seq,
+                                 nhead, dh, emdim, mask_kind)
+    import torch
+    assert torch.equal(out, out2), "head reduction must be deterministic"
+
+
+def test_attention_fuse_o(et, orc, cuda):
+    """Attention followed by the tile-CSR output projection in one call (kernel_fuseO.cu)."""
+    batch, seq, nhead, dh, em = 2, 128, 4, 64, 256
+    q, k, v = _qkv(et, 500, batch, seq, nhead, dh, dh)
+    wo = et.synth.prune_tiles(et.synth.normal(500, 4, (em, nhead * dh), 0.05), 500, 5, 0.6)
+    bo = et.synth.normal(500, 6, (em,), 0.1)
+    rp, ro, tiles = et.synth.dense_to_tile(wo)
+    out = et.attention_fuse_o(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), _dev(rp, cuda),
+                              _dev(ro, cuda), _dev(tiles, cuda), _dev(bo, cuda), batch, seq, nhead,
+                              dh, dh, em, 1)
+    assert et.device_error() == 0
+    z = orc.round_fp16(orc.attention(q, k, v, batch, seq, nhead, dh, dh, 1))
+    assert_close(out.float().cpu().numpy(), orc.linear_dense(z, wo, bo), "attention + tile O")
