@@ -69,8 +69,10 @@ def test_tile(et, orc, cuda, T, inn, out, act, sparsity):
     x, w, b = _case(et, 21, T, inn, out)
     w = et.synth.prune_tiles(w, 21, 4, sparsity)
     rp, ro, tiles = et.synth.dense_to_tile(w)
-    assert et.lib().et_validate_tile_mat(rp.ctypes.data, ro.ctypes.data if len(ro) else None,
-                                         len(ro), inn, out) == 0
+    import ctypes
+    vp = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    assert et.lib().et_validate_tile_mat(vp(rp), vp(ro) if len(ro) else None, len(ro), inn,
+                                         out) == 0
     y = et.linear_tile(_dev(x, cuda), _dev(rp, cuda), _dev(ro, cuda) if len(ro) else None,
                        _dev(tiles, cuda) if len(ro) else None, out, _dev(b, cuda), act)
     assert et.device_error() == 0
@@ -152,9 +154,12 @@ def test_bad_arguments_are_rejected_before_launch(et, cuda):
         et.linear_dense(x, w)  # in % 16 != 0
     x = torch.zeros((16, 32), dtype=torch.float16, device=cuda)
     w = torch.zeros((16, 32), dtype=torch.float16, device=cuda)
-    st = et.lib().et_linear_dense_fwd(None, w.data_ptr(), None, x.data_ptr(), 16, 32, 16, 0, None)
+    import ctypes
+    vp = ctypes.c_void_p
+    st = et.lib().et_linear_dense_fwd(None, vp(w.data_ptr()), None, vp(x.data_ptr()), 16, 32, 16, 0,
+                                      None)
     assert st == -1
-    st = et.lib().et_linear_dense_fwd(x.data_ptr() + 2, w.data_ptr(), None, x.data_ptr(), 16, 32,
-                                      16, 0, None)
+    st = et.lib().et_linear_dense_fwd(vp(x.data_ptr() + 2), vp(w.data_ptr()), None,
+                                      vp(x.data_ptr()), 16, 32, 16, 0, None)
     assert st == -2
     assert et.device_error() == 0
