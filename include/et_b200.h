@@ -108,6 +108,25 @@ int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
                       const et_half* bias, const et_half* X, et_half* Y, int T, int in, int out,
                       int act, et_half* scratch, size_t scratch_bytes, et_stream stream);
 
+/* The same column-pruned Linear for callers that have no way to hand over scratch memory:
+ * code that runs where device allocation is off limits, for example a plugin that is only
+ * given its input and output tensors by a host framework that owns every allocation, or a
+ * latency-critical serving loop that must not touch the allocator once it is running.  The
+ * gathered activations go to a fixed 8 MiB array inside the library image (held by every
+ * GPU that loads the library until the process exits), so T * nn_col may not exceed
+ * 4 194 304 values; larger problems return ET_ERR_WORKSPACE and must use
+ * et_linear_col_fwd.  No cudaMalloc / cudaFree or allocating routine is called.
+ * The first call on a device looks up the array's device address; make that call before
+ * starting any stream capture.  All calls share the one array: it keeps whatever the last
+ * call gathered (nothing in it has to start at zero, each call overwrites the part it
+ * reads), and two calls that overlap in time on the GPU race on it - issue them on one
+ * stream or order them yourself.
+ * This entry point has no counterpart in the reference, whose Linear<col_mat> always owns
+ * a cudaMalloc'ed workspace. */
+int et_linear_col_noalloc_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
+                              const et_half* bias, const et_half* X, et_half* Y, int T, int in,
+                              int out, int act, et_stream stream);
+
 /* 1x16-vector weights: tile_idx[(out/16) * (in/16 + 1)], row_idx[nvec], data[nvec][16]
  * (mat_type/mat1x16/mat1x16.h:9-15).  Stands in for Linear<mat1x16>::forward
  * (Linear/SPMM1x16.cu:89-115, whose body the reference leaves empty; the intended

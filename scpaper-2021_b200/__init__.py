@@ -23,7 +23,8 @@ FMT_DENSE, FMT_TILE = 0, 1
 ABI_SYMBOLS = [
     "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
     "et_linear_dense_fwd", "et_linear_tile_fwd", "et_linear_row_fwd",
-    "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_1x16_fwd",
+    "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
+    "et_linear_1x16_fwd",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
     "et_validate_csr", "et_skip_layernorm_fwd", "et_layernorm_fwd", "et_act_fwd",
     "et_bias_add_fwd", "et_attention_fwd", "et_attention_pruned_v_fwd",
@@ -147,6 +148,17 @@ def linear_col(x, col_id, cols, bias=None, act=ACT_NONE, scratch=None):
     check(lib().et_linear_col_fwd(_p(col_id), _p(cols), c_int(nn), _p(bias), _p(x), _p(y),
                                   c_int(T), c_int(inn), c_int(out), c_int(act), _p(scratch),
                                   c_size_t(scratch.numel() * 2), _stream()), "et_linear_col_fwd")
+    return y
+
+
+def linear_col_noalloc(x, col_id, cols, y, bias=None, act=ACT_NONE):
+    """Column-pruned Linear through the entry point that uses the library's built-in scratch;
+    the caller supplies the output tensor too, so nothing is allocated here either."""
+    T, inn = x.shape
+    out, nn = cols.shape
+    check(lib().et_linear_col_noalloc_fwd(_p(col_id), _p(cols), c_int(nn), _p(bias), _p(x), _p(y),
+                                          c_int(T), c_int(inn), c_int(out), c_int(act),
+                                          _stream()), "et_linear_col_noalloc_fwd")
     return y
 
 

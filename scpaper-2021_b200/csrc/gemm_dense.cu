@@ -401,6 +401,27 @@ int pick_bn(int M, int N, int groups = 1) {
 
 void gemm_force_bn(int bn) { g_force_bn = bn; }
 
+// ---- built-in gather scratch of et_linear_col_noalloc_fwd -------------------------------
+// Callers that cannot allocate device memory (see the entry point) use this array instead of
+// a buffer of their own.  It is part of the library image: every GPU that loads the library
+// holds these 8 MiB until the process exits.
+constexpr size_t kNoAllocScratchHalves = 4u * 1024u * 1024u;  // T * nn_col may not exceed this
+static __device__ __align__(256) __half g_col_gather_scratch[kNoAllocScratchHalves];
+
+// The array's name is only a host-side handle; kernels need its device address, looked up
+// once per device (with that device current) and cached.
+__half* col_gather_scratch_address() {
+    static __half* cached[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cached[dev] != nullptr) return cached[dev];
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_col_gather_scratch) != cudaSuccess || p == nullptr)
+        return nullptr;
+    cached[dev] = static_cast<__half*>(p);
+    return cached[dev];
+}
+
 int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
                     __half* Y, int ldy, const int* col_map, int scatter, int M, int N, int K,
                     int act, cudaStream_t stream) {
@@ -573,6 +594,19 @@ int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
                            reinterpret_cast<const __half*>(cols), nn_col,
                            reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Y),
                            out, nullptr, 0, T, out, nn_col, act, s);
+}
+
+int et_linear_col_noalloc_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
+                              const et_half* bias, const et_half* X, et_half* Y, int T, int in,
+                              int out, int act, et_stream stream) {
+    if (nn_col <= 0 || T <= 0) return ET_ERR_INVALID_ARG;
+    if (static_cast<size_t>(T) * static_cast<size_t>(nn_col) > et::kNoAllocScratchHalves)
+        return ET_ERR_WORKSPACE;  // larger than the built-in scratch: use et_linear_col_fwd
+    __half* scratch = et::col_gather_scratch_address();
+    if (scratch == nullptr) return ET_ERR_CUDA;
+    return et_linear_col_fwd(col_id, cols, nn_col, bias, X, Y, T, in, out, act,
+                             reinterpret_cast<et_half*>(scratch),
+                             et::kNoAllocScratchHalves * sizeof(__half), stream);
 }
 
 int et_linear_vo_fwd(const et_half* X, const et_half* Wvo_t, const et_half* bias, et_half* VO,
