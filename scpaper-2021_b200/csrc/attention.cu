@@ -46,8 +46,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~static_cast<uintptr_t>(1023));
+    // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
+    // shared-memory provenance (plain LDS / STS instead of generic accesses)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int nqa = (a.dh_qk + 63) >> 6;  // 64-feature atoms of Q / K
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + nqa * ATOM_BYTES;
@@ -120,13 +121,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_S = tmem_base;
     const uint32_t tmem_O = tmem_base + 128;
+    pdl_launch_dependents();
+    if (warp != 0) pdl_wait();  // Z may still be read by an earlier kernel until here
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (n_kv > 0 && elect_one()) {
+        if (lane == 0) {
             tma_prefetch_desc(&tmQ);
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmV);
+        }
+        pdl_wait();  // Q, K, V come from the previous kernel
+        if (n_kv > 0 && elect_one()) {
             mbar_arrive_expect_tx(q_full, nqa * ATOM_BYTES);
             for (int t = 0; t < nqa; ++t)
                 tma_load_3d(sQ + t * ATOM_BYTES, &tmQ, q_full, h * a.dh_qk + t * 64, q0, b);
@@ -438,8 +444,10 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     a.nva_max = nva;
     a.tmem_cols = (128 + v_n_max > 256) ? 512 : TMEM_COLS_ATT;
     dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
-    attention_kernel<<<grid, ATT_THREADS, smem_bytes, stream>>>(tmQ, tmK, tmV, a);
-    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+    return launch_kernel(attention_kernel, grid, dim3(ATT_THREADS), smem_bytes, stream, tmQ, tmK,
+                         tmV, a) == cudaSuccess
+               ? ET_OK
+               : ET_ERR_CUDA;
 }
 }  // namespace
 

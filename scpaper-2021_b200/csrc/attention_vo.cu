@@ -41,8 +41,9 @@ __global__ void __launch_bounds__(VO_THREADS, 1)
 attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmVO, const VoArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~static_cast<uintptr_t>(1023));
+    // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
+    // shared-memory provenance (plain LDS / STS instead of generic accesses)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int nqa = (a.dh_qk + 63) >> 6;
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + nqa * ATOM_BYTES;
@@ -103,6 +104,8 @@ attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_S = tmem_base;
     const uint32_t tmem_O = tmem_base + 128;
+    pdl_launch_dependents();
+    pdl_wait();  // every input is produced by earlier kernels on the stream
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -415,9 +418,10 @@ int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half*
     a.scale_log2 = scale * 1.4426950408889634f;
     a.err_word = err;
     dim3 grid((seq + BQ - 1) / BQ, (emdim + MAX_NC - 1) / MAX_NC, batch);
-    attention_vo_kernel<<<grid, VO_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
-        tmQ, tmK, tmVO, a);
-    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+    return launch_kernel(attention_vo_kernel, grid, dim3(VO_THREADS), smem_bytes,
+                         static_cast<cudaStream_t>(stream), tmQ, tmK, tmVO, a) == cudaSuccess
+               ? ET_OK
+               : ET_ERR_CUDA;
 }
 
 }  // extern "C"

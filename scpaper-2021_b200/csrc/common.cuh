@@ -29,7 +29,18 @@ int make_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint
                         const uint64_t* strides_bytes, const uint32_t* box,
                         CUtensorMapSwizzle swizzle);
 
+int make_tensor_map_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box,
+                        CUtensorMapSwizzle swizzle);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Programmatic dependent launch: when enabled (default) kernels are launched so that their
+// prologue (barrier set-up, tensor-memory allocation, weight prefetch) may overlap the tail
+// of the previous kernel on the stream; each kernel calls pdl_wait() before it touches data
+// the previous kernel produced.  et_debug_set_pdl(0) falls back to plain launches.
+bool pdl_enabled();
+void set_pdl_enabled(bool on);
 
 // Device error codes (stored in the device error word; reported by et_device_error).
 enum : int {
@@ -50,9 +61,34 @@ enum : int {
 
 #if defined(__CUDACC__)
 
+// Launches `kernel` with the programmatic-stream-serialization attribute when PDL is on.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------------------------
 // Small device utilities
 // ------------------------------------------------------------------------------------
+
+// Blocks until every kernel this one depends on has completed and its writes are visible.
+// A no-op when the kernel was launched without programmatic dependencies.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream start its prologue.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -176,6 +212,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                  "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                  : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x,
+                                             int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::
+                     "l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -233,6 +276,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+// Waits for outstanding tcgen05.ld and ties the wait to the destination registers, so that
+// the compiler cannot schedule a consumer of a load that is still in flight above the wait
+// (needed when another chunk is processed between the load and its wait).
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
+                   "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
+                   "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
+                   "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                   "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -19,10 +19,24 @@ namespace {
 
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
+constexpr int kMaxSplits = 4;
+
 struct LayerBuffers {
     __half *qkv, *z, *a, *y, *f;
+    float* part;  // split-K partial sums [kMaxSplits][T, hidden]
     size_t total;
 };
+
+// Number of K slices for a dense [T, K] x [hidden, K]^T product feeding a LayerNorm: few
+// output tiles and a long K leave most SMs idle unless K is split.
+int pick_splits(int T, int hidden, int K) {
+    const int tiles = ((T + 127) / 128) * ((hidden + 127) / 128);
+    const int slots = 2 * (sm_count() > 0 ? sm_count() : 148);
+    int s = slots / (tiles > 0 ? tiles : 1);
+    s = s < 1 ? 1 : (s > kMaxSplits ? kMaxSplits : s);
+    while (s > 1 && (K / 64) / s < 8) --s;  // keep at least 8 K blocks per slice
+    return s;
+}
 
 LayerBuffers carve(const et_encoder_layer_t* L, int batch, int seq, void* base) {
     const size_t T = static_cast<size_t>(batch) * seq;
@@ -39,6 +53,7 @@ LayerBuffers carve(const et_encoder_layer_t* L, int batch, int seq, void* base) 
     b.a = take(T * L->hidden);
     b.y = take(T * L->hidden);
     b.f = take(T * L->ff);
+    b.part = reinterpret_cast<float*>(take(2 * kMaxSplits * T * L->hidden));
     b.total = off;
     return b;
 }
@@ -111,6 +126,23 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                                         layer->hidden, s)) != ET_OK)
         return st;
     if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, s)) != ET_OK) return st;
+    const int splits = (layer->ffn2.format == ET_FMT_DENSE && layer->hidden <= 2048)
+                           ? et::pick_splits(T, layer->hidden, layer->ff)
+                           : 1;
+    if (splits > 1) {
+        // FFN2 as split-K partial sums, reduced (with bias and residual) inside the LayerNorm
+        if ((st = et::launch_gemm_f16_splitk(b.f, layer->ff,
+                                             reinterpret_cast<const __half*>(layer->ffn2.weight),
+                                             layer->ff, b.part, T, layer->hidden, layer->ff, splits,
+                                             s)) != ET_OK)
+            return st;
+        return et::launch_skip_layernorm_partials(
+            b.part, splits, static_cast<size_t>(T) * layer->hidden,
+            reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
+            reinterpret_cast<const __half*>(layer->ln2_gamma),
+            reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
+            layer->hidden, s);
+    }
     if ((st = et::run_linear(layer->ffn2, b.f, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
     return et::launch_skip_layernorm(b.a, b.y, reinterpret_cast<const __half*>(layer->ln2_gamma),
                                      reinterpret_cast<const __half*>(layer->ln2_beta),

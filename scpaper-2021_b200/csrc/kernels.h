@@ -18,6 +18,15 @@ int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const 
                                __half* Y, int M, int N, int K, int groups, int grp_rows,
                                cudaStream_t stream);
 
+// Split-K fp32 partial sums P[splits][M, N] (no bias) and the LayerNorm that consumes them:
+// out = LN(sum_p P[p] + bias + skip) * gamma + beta.  size <= 2048.
+int launch_gemm_f16_splitk(const __half* X, int ldx, const __half* W, int ldw, float* P, int M,
+                           int N, int K, int splits, cudaStream_t stream);
+int launch_skip_layernorm_partials(const float* partials, int nsplit, size_t split_stride,
+                                   const __half* bias, const __half* skip, const __half* gamma,
+                                   const __half* beta, __half* out, int rows, int size,
+                                   cudaStream_t stream);
+
 // Tile-CSR Linear (see linear_tile.cu).
 int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
                        const __half* bias, const __half* X, __half* Y, int T, int in, int out,

@@ -35,6 +35,8 @@ skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__
                       __half* __restrict__ out, int rows, int size, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * LN_WARPS + warp;
+    pdl_launch_dependents();
+    pdl_wait();
     if (row >= rows) return;
     const int nchunk = size >> 3;
     const uint4* s4 = reinterpret_cast<const uint4*>(src + static_cast<size_t>(row) * size);
@@ -106,6 +108,82 @@ skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__
     }
 }
 
+// Same normalisation fed by split-K partial sums: the row is
+//   sum_p partials[p][row, :] + bias + skip[row, :]
+// so the GEMM that precedes it never rounds its result to fp16 nor adds its bias.
+__global__ void __launch_bounds__(LN_WARPS * 32)
+skip_layernorm_partials_kernel(const float* __restrict__ partials, int nsplit, size_t split_stride,
+                               const __half* __restrict__ bias, const __half* __restrict__ skip,
+                               const __half* __restrict__ gamma, const __half* __restrict__ beta,
+                               __half* __restrict__ out, int rows, int size, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * LN_WARPS + warp;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (row >= rows) return;
+    const int nchunk = size >> 3;
+    const uint4* k4 =
+        skip ? reinterpret_cast<const uint4*>(skip + static_cast<size_t>(row) * size) : nullptr;
+    uint4* o4 = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * size);
+    float cache[LN_MAX_CHUNKS][8];
+    float sum = 0.f, sq = 0.f;
+#pragma unroll
+    for (int it = 0; it < LN_MAX_CHUNKS; ++it) {
+        const int c = lane + it * 32;
+        if (c < nchunk) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+            for (int p = 0; p < nsplit; ++p) {
+                const float4* src = reinterpret_cast<const float4*>(
+                    partials + p * split_stride + static_cast<size_t>(row) * size + c * 8);
+                const float4 a = __ldg(src), b = __ldg(src + 1);
+                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+                v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+            }
+            float w[8];
+            if (bias) {
+                unpack8(__ldg(reinterpret_cast<const uint4*>(bias) + c), w);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += w[j];
+            }
+            if (k4) {
+                unpack8(__ldg(k4 + c), w);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += w[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                sum += v[j];
+                sq += v[j] * v[j];
+                cache[it][j] = v[j];
+            }
+        }
+    }
+    sum = warp_sum(sum);
+    sq = warp_sum(sq);
+    const float mean = sum / size;
+    const float var = fmaxf(sq / size - mean * mean, 0.f);
+    const float rstd = rsqrtf(var + eps);
+#pragma unroll
+    for (int it = 0; it < LN_MAX_CHUNKS; ++it) {
+        const int c = lane + it * 32;
+        if (c < nchunk) {
+            float g[8], b[8], v[8];
+            unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + c), g);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(beta) + c), b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (cache[it][j] - mean) * rstd * g[j] + b[j];
+            uint4 o;
+            o.x = pack_half2(v[0], v[1]);
+            o.y = pack_half2(v[2], v[3]);
+            o.z = pack_half2(v[4], v[5]);
+            o.w = pack_half2(v[6], v[7]);
+            o4[c] = o;
+        }
+    }
+}
+
 // in and out may be the same buffer (the reference applies the activation in place).
 __global__ void act_kernel(const __half* in, __half* out, size_t n, int act) {
     const size_t n8 = n >> 3;
@@ -164,13 +242,29 @@ int launch_skip_layernorm(const __half* src, const __half* skip, const __half* g
         (skip && !aligned16(skip)))
         return ET_ERR_ALIGNMENT;
     const int blocks = (rows + LN_WARPS - 1) / LN_WARPS;
+    cudaError_t e;
     if (size <= LN_MAX_CHUNKS * 8 * 32)
-        skip_layernorm_kernel<true><<<blocks, LN_WARPS * 32, 0, stream>>>(src, skip, gamma, beta,
-                                                                          out, rows, size, 1e-5f);
+        e = launch_kernel(skip_layernorm_kernel<true>, dim3(blocks), dim3(LN_WARPS * 32), 0, stream,
+                          src, skip, gamma, beta, out, rows, size, 1e-5f);
     else
-        skip_layernorm_kernel<false><<<blocks, LN_WARPS * 32, 0, stream>>>(src, skip, gamma, beta,
-                                                                           out, rows, size, 1e-5f);
-    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+        e = launch_kernel(skip_layernorm_kernel<false>, dim3(blocks), dim3(LN_WARPS * 32), 0,
+                          stream, src, skip, gamma, beta, out, rows, size, 1e-5f);
+    return e == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+}
+
+int launch_skip_layernorm_partials(const float* partials, int nsplit, size_t split_stride,
+                                   const __half* bias, const __half* skip, const __half* gamma,
+                                   const __half* beta, __half* out, int rows, int size,
+                                   cudaStream_t stream) {
+    if (!partials || !gamma || !beta || !out || rows <= 0 || size <= 0 || nsplit <= 0)
+        return ET_ERR_INVALID_ARG;
+    if (size % 8 || size > LN_MAX_CHUNKS * 8 * 32) return ET_ERR_SHAPE;
+    const int blocks = (rows + LN_WARPS - 1) / LN_WARPS;
+    return launch_kernel(skip_layernorm_partials_kernel, dim3(blocks), dim3(LN_WARPS * 32), 0,
+                         stream, partials, nsplit, split_stride, bias, skip, gamma, beta, out, rows,
+                         size, 1e-5f) == cudaSuccess
+               ? ET_OK
+               : ET_ERR_CUDA;
 }
 
 }  // namespace et

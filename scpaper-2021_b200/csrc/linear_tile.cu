@@ -36,8 +36,9 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                    const __half* __restrict__ bias, __half* __restrict__ Y, int T, int in, int out,
                    int act, int* err_word) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~static_cast<uintptr_t>(1023));
+    // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
+    // shared-memory provenance (plain LDS / STS instead of generic accesses)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int nbc = in >> 4;                        // input block columns
     const int nchunk = (in + CHUNK - 1) / CHUNK;
     uint8_t* sX = smem;
@@ -92,6 +93,8 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const int panel_tiles = rp[PANEL_ROWS] - rp[0];
+    pdl_launch_dependents();
+    pdl_wait();  // the index tables above are weights; activations and Y need the wait
 
     if (warp == 0) {
         // ---------------- producer (whole warp: lane = row * 4 + column in chunk) ----------------
@@ -229,6 +232,8 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
 __global__ void tile_fill_bias_kernel(__half* __restrict__ Y, const __half* __restrict__ bias,
                                       size_t rows, int cols, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t total = rows * cols;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -255,8 +260,10 @@ int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* til
     if (nnz_tiles == 0) {
         const size_t total = static_cast<size_t>(T) * out;
         const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-        tile_fill_bias_kernel<<<blocks, 256, 0, stream>>>(Y, bias, T, out, act);
-        return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+        return launch_kernel(tile_fill_bias_kernel, dim3(blocks), dim3(256), 0, stream, Y, bias,
+                             static_cast<size_t>(T), out, act) == cudaSuccess
+                   ? ET_OK
+                   : ET_ERR_CUDA;
     }
 
     CUtensorMap tmX, tmW;
@@ -288,9 +295,10 @@ int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* til
         attr_bytes[dev] = smem_bytes;
     }
     dim3 grid((out + TBN - 1) / TBN, (T + TBM - 1) / TBM);
-    linear_tile_kernel<<<grid, TILE_THREADS, smem_bytes, stream>>>(tmX, tmW, row_ptr, row_off, bias,
-                                                                   Y, T, in, out, act, err);
-    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+    return launch_kernel(linear_tile_kernel, grid, dim3(TILE_THREADS), smem_bytes, stream, tmX, tmW,
+                         row_ptr, row_off, bias, Y, T, in, out, act, err) == cudaSuccess
+               ? ET_OK
+               : ET_ERR_CUDA;
 }
 
 }  // namespace et

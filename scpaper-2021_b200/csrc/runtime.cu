@@ -48,6 +48,12 @@ PerDevice* current_device() {
 
 }  // namespace
 
+namespace {
+bool g_pdl = true;
+}
+bool pdl_enabled() { return g_pdl; }
+void set_pdl_enabled(bool on) { g_pdl = on; }
+
 int* device_error_word() {
     PerDevice* pd = current_device();
     return pd ? pd->err_word : nullptr;
@@ -58,9 +64,30 @@ int sm_count() {
     return pd ? pd->sm_count : 0;
 }
 
+namespace {
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    CUtensorMapSwizzle swizzle);
+}
+
 int make_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                         const uint64_t* strides_bytes, const uint32_t* box,
                         CUtensorMapSwizzle swizzle) {
+    return make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, rank, dims, strides_bytes,
+                           box, swizzle);
+}
+
+int make_tensor_map_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box,
+                        CUtensorMapSwizzle swizzle) {
+    return make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes,
+                           box, swizzle);
+}
+
+namespace {
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    CUtensorMapSwizzle swizzle) {
     if (!g_encode) {
         std::lock_guard<std::mutex> lock(g_mutex);
         if (!g_encode) {
@@ -87,12 +114,13 @@ int make_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint
         if (strides_bytes[i] % 16 != 0) return ET_ERR_ALIGNMENT;
         gstrides[i] = strides_bytes[i];
     }
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank),
+    CUresult r = g_encode(map, dtype, static_cast<cuuint32_t>(rank),
                           const_cast<void*>(base), gdims, gstrides, gbox, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? ET_OK : ET_ERR_CUDA;
 }
+}  // namespace
 
 }  // namespace et
 
@@ -112,6 +140,9 @@ const char* et_status_string(int status) {
         default: return "unknown status";
     }
 }
+
+// Test hook: 0 = plain launches, 1 = programmatic dependent launches (default).
+void et_debug_set_pdl(int on) { et::set_pdl_enabled(on != 0); }
 
 int et_version(void) { return 100; }
 int et_built_for_sm(void) { return 100; }
