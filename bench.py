@@ -172,6 +172,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch kernels directly")
+    ap.add_argument("--lanes", type=int, default=1,
+                    help="groups of sequences that run through the stack on their own streams")
     ap.add_argument("--skip-extras", action="store_true",
                     help="skip the pruned / per-kernel / CPU legs (used under profilers)")
     args = ap.parse_args()
@@ -212,7 +214,7 @@ def main():
 
     ws = build_weights(et)
     layers = [et.EncoderLayer(w, NHEAD, et.ACT_GELU, device=dev) for w in ws]
-    stack = et.EncoderStack(layers, BATCH, SEQ, device=dev)
+    stack = et.EncoderStack(layers, BATCH, SEQ, device=dev, lanes=args.lanes)
     x_host = torch.from_numpy(et.synth.normal(SEED, 7000 + rank, (BATCH * SEQ, HIDDEN), 1.0))
     x_pinned = x_host.pin_memory()
     y_pinned = torch.empty_like(x_pinned).pin_memory()

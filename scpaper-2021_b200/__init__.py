@@ -353,25 +353,58 @@ class EncoderLayer:
 
 
 class EncoderStack:
-    """N chained encoder layers sharing one workspace and two ping-pong activation buffers."""
+    """N chained encoder layers.  The batch can be cut into `lanes` groups of sequences that
+    run through the whole stack on streams of their own (sequences are independent), so that
+    the kernels of one group fill the SMs another group's kernels leave idle; each group has
+    its own workspace, all share two ping-pong activation buffers."""
 
-    def __init__(self, layers, batch: int, seq: int, device="cuda"):
+    def __init__(self, layers, batch: int, seq: int, device="cuda", lanes: int = 1):
         import torch
         self.layers = list(layers)
         self.batch, self.seq = batch, seq
-        ws = max(l.workspace_bytes(batch, seq) for l in self.layers)
-        if ws == 0:
-            raise EtError("invalid encoder layer description")
-        self.workspace = torch.empty(ws, dtype=torch.uint8, device=device)
+        lanes = max(1, min(lanes, batch))
+        base, extra = divmod(batch, lanes)
+        self.groups = []  # (first sequence, number of sequences)
+        first = 0
+        for i in range(lanes):
+            n = base + (1 if i < extra else 0)
+            self.groups.append((first, n))
+            first += n
         hidden = self.layers[0].hidden
+        self.workspaces = []
+        for _, n in self.groups:
+            ws = max(l.workspace_bytes(n, seq) for l in self.layers)
+            if ws == 0:
+                raise EtError("invalid encoder layer description")
+            self.workspaces.append(torch.empty(ws, dtype=torch.uint8, device=device))
+        self.workspace = self.workspaces[0]
         self.buf = [torch.empty((batch * seq, hidden), dtype=torch.float16, device=device)
                     for _ in range(2)]
+        self.streams = [torch.cuda.Stream(device=device) for _ in self.groups[1:]]
+        self.events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in self.groups[1:]]
+
+    def _run_group(self, g, x, mask_kind, mask, valid_len):
+        first, n = self.groups[g]
+        r0, r1 = first * self.seq, (first + n) * self.seq
+        cur = x[r0:r1]
+        vl = None if valid_len is None else valid_len[first:first + n]
+        for i, layer in enumerate(self.layers):
+            out = self.buf[i & 1][r0:r1]
+            layer.forward(cur, out, n, self.seq, self.workspaces[g], mask_kind, mask, vl)
+            cur = out
 
     def forward(self, x, mask_kind=MASK_NONE, mask=None, valid_len=None):
-        cur = x
-        for i, layer in enumerate(self.layers):
-            out = self.buf[i & 1]
-            layer.forward(cur, out, self.batch, self.seq, self.workspace, mask_kind, mask,
-                          valid_len)
-            cur = out
-        return cur
+        import torch
+        main = torch.cuda.current_stream()
+        for g in range(1, len(self.groups)):
+            start, _ = self.events[g - 1]
+            start.record(main)
+            self.streams[g - 1].wait_event(start)
+            with torch.cuda.stream(self.streams[g - 1]):
+                self._run_group(g, x, mask_kind, mask, valid_len)
+        self._run_group(0, x, mask_kind, mask, valid_len)
+        for g in range(1, len(self.groups)):
+            _, done = self.events[g - 1]
+            done.record(self.streams[g - 1])
+            main.wait_event(done)
+        return self.buf[(len(self.layers) - 1) & 1]

@@ -3,13 +3,17 @@
 // One CTA owns 128 queries of one (sequence, head).  Warp 0 streams Q once and then K / V
 // blocks of 128 keys with TMA (3-D tensor maps {feature, position, sequence}, so positions
 // past the end of a sequence are zero-filled and never read the next sequence).  One
-// thread of warp 1 issues S = Q.K^T (M=128, N=128) into tensor memory, the four softmax
-// warps (one query row per thread) read S back, apply scale and mask, keep a running
-// max / sum (online softmax, exp2 with log2(e)/sqrt(dh) folded into one FMA), write the
-// fp16 probabilities into 128-byte-swizzled shared memory as the A operand of the second
-// product, rescale the output accumulator when the running max moved, and the MMA thread
-// accumulates O += P.V with V consumed directly in its row-major (MN-major) layout.
-// After the last block each softmax thread divides its row by the sum and stores fp16.
+// thread of warp 1 issues S = Q.K^T (M=128, N=128) into tensor memory.  Eight softmax warps
+// share the 128 x 128 score block: two per tensor-memory lane quadrant, each thread owning
+// 64 keys of one query row, which it reads from tensor memory ONCE and keeps in registers.
+// The two halves of a row exchange their maxima through shared memory, then each thread
+// computes exp2 (with log2(e)/sqrt(dh) folded into one FMA), keeps a running max / partial
+// sum (online softmax across key blocks), writes its fp16 probabilities into the
+// 128-byte-swizzled shared-memory tile that is the A operand of the second product and
+// rescales its share of the output accumulator when the running max moved.  The MMA thread
+// accumulates O += P.V with V consumed directly in its row-major (MN-major) layout.  After
+// the last block the row sums are combined, each thread scales its share of the output
+// columns and the tile leaves through a swizzled staging buffer and TMA stores.
 // All waits are bounded.
 #include <math.h>
 
@@ -20,11 +24,24 @@ namespace et {
 
 namespace {
 
+// Optional per-CTA timestamps for bring-up builds (-DET_TIMELINE); compiled out otherwise.
+#ifdef ET_TIMELINE
+__device__ long long et_attn_timeline[65536];
+#define ET_TL(slot)                                                                       \
+    et_attn_timeline[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + \
+                     (slot)] = clock64()
+#else
+#define ET_TL(slot) ((void)0)
+#endif
+
 constexpr int BQ = 128;
 constexpr int BKV = 128;
-constexpr int ATT_THREADS = 192;
+constexpr int SM_WARPS = 8;                      // softmax / output warps
+constexpr int SM_THREADS = 32 * SM_WARPS;
+constexpr int ATT_THREADS = 64 + SM_THREADS;
 constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 fp16, one 128-byte-swizzled atom
-constexpr int TMEM_COLS_ATT = 256;     // S: columns [0,128), O: columns [128, 128 + dh_v)
+constexpr int TMEM_COLS_ATT = 256;     // S: columns [0,128), O: columns [128, 128 + v_n)
+constexpr int EXTRA_BYTES = 256 + 6 * 128 * 4;   // barriers + max / sum exchange arrays
 
 struct AttnArgs {
     __half* Z;
@@ -33,18 +50,20 @@ struct AttnArgs {
     int ldz;
     int batch, seq, nhead, dh_qk, dh_v;
     int mask_kind;
-    float scale_log2;  // scale * log2(e)
+    float scale_log2;  // scale * log2(e), > 0
     int* err_word;
     // column-compressed V (null for a dense V): feature list and per-head ranges into it
     const int* col_id;
     const int* head_ptr;
     int nva_max;    // 64-feature atoms reserved for a V block in shared memory
     int tmem_cols;  // tensor-memory columns to allocate (256 or 512)
+    int tma_out;    // 1: the output tile is written with TMA stores (dense V, dh_v % 64 == 0)
 };
 
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmZ,
+                 const AttnArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
     // shared-memory provenance (plain LDS / STS instead of generic accesses)
@@ -66,6 +85,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t* o_full = bars + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* s_xmax = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -99,14 +119,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
 
     if (threadIdx.x == 0) {
+        ET_TL(0);
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
         mbar_init(q_full, 1);
         mbar_init(k_full, 1);
         mbar_init(k_empty, 1);
         mbar_init(v_full, 1);
         mbar_init(v_empty, 1);
         mbar_init(s_full, 1);
-        mbar_init(s_free, 128);
-        mbar_init(p_full, 128);
+        mbar_init(s_free, SM_THREADS);
+        mbar_init(p_full, SM_THREADS);
         mbar_init(o_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -121,17 +145,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_S = tmem_base;
     const uint32_t tmem_O = tmem_base + 128;
+    if (threadIdx.x == 0) ET_TL(1);
     pdl_launch_dependents();
-    if (warp != 0) pdl_wait();  // Z may still be read by an earlier kernel until here
+    pdl_wait();  // Q, K, V come from the previous kernel; Z may still be read by an earlier one
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmQ);
-            tma_prefetch_desc(&tmK);
-            tma_prefetch_desc(&tmV);
-        }
-        pdl_wait();  // Q, K, V come from the previous kernel
         if (n_kv > 0 && elect_one()) {
             mbar_arrive_expect_tx(q_full, nqa * ATOM_BYTES);
             for (int t = 0; t < nqa; ++t)
@@ -155,6 +174,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 for (int t = 0; t < nva; ++t)
                     tma_load_3d(sV + t * ATOM_BYTES, &tmV, v_full, v_x0 + t * 64, j * BKV, b);
                 ++v_issued;
+                if (j == 0) ET_TL(2);
             }
             if (*abort_flag) {
                 // let copies in flight land before shared memory is released
@@ -195,6 +215,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 mma_commit(s_full);
                 mma_commit(k_empty);
+                if (j == 0) ET_TL(3);
 
                 ok = mbar_wait_bounded(p_full, ph, abort_flag) &&
                      mbar_wait_bounded(v_full, ph, abort_flag);
@@ -214,51 +235,85 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 mma_commit(o_full);
                 mma_commit(v_empty);
+                if (j == 0) ET_TL(7);
             }
         }
     } else {
-        // ---------------- softmax / output warps: one query row per thread ----------------
-        const int qd = warp & 3;
-        const int r = qd * 32 + lane;  // row inside the CTA tile
-        const int qrow = q0 + r;       // position inside the sequence
+        // ---------------- softmax / output warps ----------------
+        const int qd = warp & 3;          // tensor-memory lane quadrant
+        const int hf = (warp - 2) >> 2;   // which 64 keys of a block / which share of the output
+        const int r = qd * 32 + lane;     // row inside the CTA tile
+        const int qrow = q0 + r;          // position inside the sequence
         const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
         const float NINF = -INFINITY;
-        float m_run = NINF, l_run = 0.f;
+        // exchange buffers: maxima double-buffered by block parity, sums single
+        float* xmax = s_xmax;                 // [2 parities][2 halves][128 rows]
+        float* xsum = s_xmax + 2 * 2 * 128;   // [2 halves][128 rows]
+        const int nc16 = v_n >> 4;            // 16-column chunks of the output accumulator
+        const int csplit = (nc16 + 1) >> 1;
+        const int c_begin = hf * csplit;
+        const int c_end = (c_begin + csplit) < nc16 ? (c_begin + csplit) : nc16;
+        float m_run = NINF, l_part = 0.f;
         bool ok = true;
 
+        // Error handling: a warp whose bounded wait ran out keeps walking the loop (skipping the
+        // work) so that every warp executes the same sequence of named barriers.
         for (int j = 0; j < n_kv; ++j) {
             const uint32_t ph = j & 1;
-            ok = mbar_wait_bounded(s_full, ph, abort_flag);
-            if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after_sync();
-
-            const int kbase = j * BKV;
-            const bool need_mask = (kbase + BKV > kv_len) || (a.mask_kind == ET_MASK_ADDITIVE) ||
-                                   (a.mask_kind == ET_MASK_CAUSAL && kbase + BKV - 1 > q0);
-            const __half* mrow = (a.mask_kind == ET_MASK_ADDITIVE && qrow < a.seq)
-                                     ? a.mask + static_cast<size_t>(qrow) * a.seq
-                                     : nullptr;
-            auto score = [&](uint32_t raw, int kc) -> float {
-                float s = __uint_as_float(raw) * a.scale_log2;
-                if (need_mask) {
-                    if (kc >= kv_len || (a.mask_kind == ET_MASK_CAUSAL && kc > qrow)) return NINF;
-                    if (mrow) s += __half2float(__ldg(mrow + kc)) * 1.4426950408889634f;
-                }
-                return s;
-            };
-
-            // pass 1: row maximum of this block
-            float mx = NINF;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_S + lane_off + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(v[i], kbase + c * 32 + i));
+            if (ok) {
+                ok = mbar_wait_bounded(s_full, ph, abort_flag);
+                if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
+                ok = __all_sync(0xffffffffu, ok);
             }
+            if (!ok) {
+                asm volatile("bar.sync 1, %0;" ::"n"(SM_THREADS) : "memory");
+                continue;
+            }
+            tc_fence_after_sync();
+            if (threadIdx.x == 64 && j == 0) ET_TL(4);
+
+            // this thread's 64 scores, read once
+            uint32_t v0[32], v1[32];
+            tmem_ld32(tmem_S + lane_off + hf * 64, v0);
+            tmem_ld32(tmem_S + lane_off + hf * 64 + 32, v1);
+            tmem_ld_wait_regs(v0);
+            tmem_ld_wait_regs(v1);
+            tc_fence_before_sync();
+            mbar_arrive(s_free);  // S may be overwritten by the next Q.K^T
+
+            const int kbase = j * BKV + hf * 64;
+            const bool need_mask = (j * BKV + BKV > kv_len) || (a.mask_kind == ET_MASK_ADDITIVE) ||
+                                   (a.mask_kind == ET_MASK_CAUSAL && j * BKV + BKV - 1 > q0);
+            float mx = NINF;
+            if (need_mask) {
+                // general path: scores are scaled and masked in place (log2 domain)
+                const __half* mrow = (a.mask_kind == ET_MASK_ADDITIVE && qrow < a.seq)
+                                         ? a.mask + static_cast<size_t>(qrow) * a.seq
+                                         : nullptr;
+                auto fix = [&](uint32_t raw, int kc) -> uint32_t {
+                    float s = __uint_as_float(raw) * a.scale_log2;
+                    if (kc >= kv_len || (a.mask_kind == ET_MASK_CAUSAL && kc > qrow)) s = NINF;
+                    else if (mrow) s += __half2float(__ldg(mrow + kc)) * 1.4426950408889634f;
+                    mx = fmaxf(mx, s);
+                    return __float_as_uint(s);
+                };
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v0[i] = fix(v0[i], kbase + i);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v1[i] = fix(v1[i], kbase + 32 + i);
+            } else {
+                // fast path: max of the raw scores, the (positive) scale applied once
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+                mx *= a.scale_log2;
+            }
+            // combine with the other half of the row
+            xmax[(ph * 2 + hf) * 128 + r] = mx;
+            asm volatile("bar.sync 1, %0;" ::"n"(SM_THREADS) : "memory");
+            mx = fmaxf(mx, xmax[(ph * 2 + (hf ^ 1)) * 128 + r]);
+            if (threadIdx.x == 64 && j == 0) ET_TL(5);
+
             const float m_new = fmaxf(m_run, mx);
             const float m_use = (m_new == NINF) ? 0.f : m_new;
             const float alpha = exp2_approx(m_run - m_use);  // 0 when m_run = -inf
@@ -268,10 +323,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 ok = mbar_wait_bounded(o_full, ph ^ 1, abort_flag);
                 if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!ok) continue;
                 tc_fence_after_sync();
                 if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
-                    for (int c = 0; c < (v_n >> 4); ++c) {
+                    for (int c = c_begin; c < c_end; ++c) {
                         uint32_t o[16];
                         tmem_ld16(tmem_O + lane_off + c * 16, o);
                         tmem_ld_wait();
@@ -284,56 +339,64 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
 
-            // pass 2: probabilities -> shared memory (A operand of P.V), row sum
+            // probabilities -> shared memory (A operand of P.V, atom `hf`), partial row sum
             float rowsum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_S + lane_off + c * 32, v);
-                tmem_ld_wait();
-                float p[32];
+            uint8_t* prow = sP + hf * ATOM_BYTES + r * 128;
+            const float neg_m = -m_use;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    p[i] = exp2_approx(score(v[i], kbase + c * 32 + i) - m_use);
+            for (int g = 0; g < 8; ++g) {
+                float p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t raw = g < 4 ? v0[g * 8 + i] : v1[(g - 4) * 8 + i];
+                    const float arg = need_mask ? __uint_as_float(raw) + neg_m
+                                                : fmaf(__uint_as_float(raw), a.scale_log2, neg_m);
+                    p[i] = exp2_approx(arg);
                     rowsum += p[i];
                 }
-                uint8_t* prow = sP + (c >> 1) * ATOM_BYTES + r * 128;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 pk;
-                    pk.x = pack_half2(p[g * 8 + 0], p[g * 8 + 1]);
-                    pk.y = pack_half2(p[g * 8 + 2], p[g * 8 + 3]);
-                    pk.z = pack_half2(p[g * 8 + 4], p[g * 8 + 5]);
-                    pk.w = pack_half2(p[g * 8 + 6], p[g * 8 + 7]);
-                    const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + chunk * 16) = pk;
-                }
+                uint4 pk;
+                pk.x = pack_half2(p[0], p[1]);
+                pk.y = pack_half2(p[2], p[3]);
+                pk.z = pack_half2(p[4], p[5]);
+                pk.w = pack_half2(p[6], p[7]);
+                *reinterpret_cast<uint4*>(prow + ((g ^ (r & 7)) * 16)) = pk;
             }
-            l_run = l_run * alpha + rowsum;
+            l_part = l_part * alpha + rowsum;
             m_run = m_new;
 
             tc_fence_before_sync();
-            mbar_arrive(s_free);       // S may be overwritten by the next Q.K^T
             fence_proxy_async_smem();  // P visible to the tensor core's reads
             mbar_arrive(p_full);
+            if (threadIdx.x == 64 && j == 0) ET_TL(6);
         }
+
+        // total row sum = the two halves' partial sums
+        xsum[hf * 128 + r] = l_part;
+        asm volatile("bar.sync 1, %0;" ::"n"(SM_THREADS) : "memory");
+        const float l_run = l_part + xsum[(hf ^ 1) * 128 + r];
 
         if (ok && n_kv > 0) {
             ok = mbar_wait_bounded(o_full, (n_kv - 1) & 1, abort_flag);
             if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
             ok = __all_sync(0xffffffffu, ok);
         }
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        const bool staged = a.tma_out && n_kv > 0;
+        __half* zrow = a.Z + (static_cast<size_t>(b) * a.seq + (qrow < a.seq ? qrow : 0)) * a.ldz +
+                       static_cast<size_t>(h) * a.dh_v;
         if (ok) {
             tc_fence_after_sync();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            __half* zrow = a.Z + (static_cast<size_t>(b) * a.seq + (qrow < a.seq ? qrow : 0)) * a.ldz +
-                           static_cast<size_t>(h) * a.dh_v;
-            if (a.head_ptr != nullptr && qrow < a.seq) {
+            if (threadIdx.x == 64) ET_TL(8);
+            if (a.head_ptr != nullptr && qrow < a.seq && hf == 0) {
                 // pruned features of this head are zero; kept ones are scattered below
                 for (int c = 0; c < (a.dh_v >> 3); ++c)
                     *reinterpret_cast<uint4*>(zrow + c * 8) = make_uint4(0u, 0u, 0u, 0u);
             }
-            for (int c = 0; c < (v_n >> 4); ++c) {
+        }
+        // orders the zero fill (done by one warp of the quadrant's pair) before the scatter
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + qd) : "memory");
+        if (ok) {
+            for (int c = c_begin; c < c_end; ++c) {
                 uint32_t o[16];
                 if (n_kv > 0) {
                     tmem_ld16(tmem_O + lane_off + c * 16, o);
@@ -342,42 +405,60 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = 0u;
                 }
-                if (qrow < a.seq) {
+                uint4 w0, w1;
+                w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+                w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+                w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+                w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+                w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+                w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+                w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+                w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+                if (staged) {
+                    // P is dead once the last P.V product has completed: reuse it as the swizzled
+                    // staging tile of the output (64-column atoms, 128 bytes per row)
+                    uint8_t* srow = sP + (c >> 2) * ATOM_BYTES + r * 128;
+                    const int ch = (c & 3) * 2;
+                    *reinterpret_cast<uint4*>(srow + ((ch ^ (r & 7)) * 16)) = w0;
+                    *reinterpret_cast<uint4*>(srow + (((ch + 1) ^ (r & 7)) * 16)) = w1;
+                } else if (qrow < a.seq) {
                     if (a.head_ptr == nullptr) {
-                        uint4 w0, w1;
-                        w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
-                        w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
-                        w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
-                        w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
-                        w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
-                        w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
-                        w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
-                        w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
                         *reinterpret_cast<uint4*>(zrow + c * 16) = w0;
                         *reinterpret_cast<uint4*>(zrow + c * 16 + 8) = w1;
                     } else {
                         const int* ids = a.col_id + a.head_ptr[h];
+                        const __half* hv0 = reinterpret_cast<const __half*>(&w0);
+                        const __half* hv1 = reinterpret_cast<const __half*>(&w1);
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const int k = c * 16 + i - v_shift;  // index into this head's list
                             if (k >= 0 && k < v_cnt)
                                 a.Z[(static_cast<size_t>(b) * a.seq + qrow) * a.ldz + __ldg(ids + k)] =
-                                    __float2half_rn(__uint_as_float(o[i]) * inv);
+                                    i < 8 ? hv0[i] : hv1[i - 8];
                         }
                     }
                 }
             }
+            if (staged) fence_proxy_async_smem();
+        }
+        // both warps of the quadrant have filled their share of the 32 staged rows
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + qd) : "memory");
+        if (ok && staged && hf == 0 && lane == 0 && q0 + qd * 32 < a.seq) {
+            for (int t = 0; t < nva; ++t)
+                tma_store_3d(&tmZ, sP + t * ATOM_BYTES + qd * 32 * 128, h * a.dh_v + t * 64,
+                             q0 + qd * 32, b);
+            tma_store_commit();
+            tma_store_wait_read();
         }
     }
 
+    if (threadIdx.x == 64) ET_TL(9);
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) ET_TL(10);
     if (warp == 1) tmem_dealloc(tmem_base, a.tmem_cols);
 }
 
-}  // namespace
-
-namespace {
 int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
                           int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
                           int ldz, int mask_kind, const __half* mask, const int* valid_len,
@@ -388,6 +469,7 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     if (mask_kind < ET_MASK_NONE || mask_kind > ET_MASK_ADDITIVE) return ET_ERR_INVALID_ARG;
     if (mask_kind == ET_MASK_ADDITIVE && !mask) return ET_ERR_INVALID_ARG;
     if (mask_kind == ET_MASK_PADDING && !valid_len) return ET_ERR_INVALID_ARG;
+    if (!(scale > 0.f)) return ET_ERR_INVALID_ARG;
     if (dh_qk % 16 || dh_v % 16 || dh_qk > 128 || dh_v > 128) return ET_ERR_SHAPE;
     if (ldq % 8 || ldk % 8 || ldv % 8 || ldz % 8) return ET_ERR_SHAPE;
     const bool pruned = head_ptr != nullptr;
@@ -399,30 +481,34 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     int* err = device_error_word();
     if (!err) return ET_ERR_NO_DEVICE;
 
-    CUtensorMap tmQ, tmK, tmV;
-    const uint32_t box[3] = {64, 128, 1};
-    auto make = [&](CUtensorMap* m, const __half* p, int ld, int width) {
+    CUtensorMap tmQ, tmK, tmV, tmZ;
+    auto make = [&](CUtensorMap* m, const __half* p, int ld, int width, uint32_t box_rows) {
         const uint64_t dims[3] = {static_cast<uint64_t>(width), static_cast<uint64_t>(seq),
                                   static_cast<uint64_t>(batch)};
         const uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2,
                                      static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(seq)};
+        const uint32_t box[3] = {64, box_rows, 1};
         return make_tensor_map_f16(m, p, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     };
     int st;
-    if ((st = make(&tmQ, Q, ldq, nhead * dh_qk)) != ET_OK) return st;
-    if ((st = make(&tmK, K, ldk, nhead * dh_qk)) != ET_OK) return st;
-    if ((st = make(&tmV, V, ldv, pruned ? nnz_col : nhead * dh_v)) != ET_OK) return st;
+    if ((st = make(&tmQ, Q, ldq, nhead * dh_qk, 128)) != ET_OK) return st;
+    if ((st = make(&tmK, K, ldk, nhead * dh_qk, 128)) != ET_OK) return st;
+    if ((st = make(&tmV, V, ldv, pruned ? nnz_col : nhead * dh_v, 128)) != ET_OK) return st;
+    // the output leaves through 64-column x 32-row TMA boxes when heads are whole atoms wide
+    const bool tma_out = !pruned && (dh_v % 64 == 0);
+    tmZ = tmQ;
+    if (tma_out && (st = make(&tmZ, Z, ldz, nhead * dh_v, 32)) != ET_OK) return st;
 
     // a compressed V window may start up to 7 features before the head's first kept feature
     const int v_n_max = pruned ? ((7 + dh_v + 15) & ~15) : dh_v;
     const int nqa = (dh_qk + 63) / 64, nva = (v_n_max + 63) / 64;
-    const int smem_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + 256 + 1024;
+    const int smem_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + EXTRA_BYTES + 1024;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (2 * 2 + 3 + 2) * ATOM_BYTES + 256 + 1024) != cudaSuccess)
+                                 (2 * 2 + 3 + 2) * ATOM_BYTES + EXTRA_BYTES + 1024) != cudaSuccess)
             return ET_ERR_CUDA;
         attr_set[dev] = true;
     }
@@ -443,9 +529,10 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     a.head_ptr = head_ptr;
     a.nva_max = nva;
     a.tmem_cols = (128 + v_n_max > 256) ? 512 : TMEM_COLS_ATT;
+    a.tma_out = tma_out ? 1 : 0;
     dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
     return launch_kernel(attention_kernel, grid, dim3(ATT_THREADS), smem_bytes, stream, tmQ, tmK,
-                         tmV, a) == cudaSuccess
+                         tmV, tmZ, a) == cudaSuccess
                ? ET_OK
                : ET_ERR_CUDA;
 }
