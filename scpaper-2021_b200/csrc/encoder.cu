@@ -29,12 +29,18 @@ struct LayerBuffers {
 
 // Number of K slices for a dense [T, K] x [hidden, K]^T product feeding a LayerNorm: few
 // output tiles and a long K leave most SMs idle unless K is split.
+int g_force_splits = 0;  // test hook: 0 = automatic
+
 int pick_splits(int T, int hidden, int K) {
+    if (g_force_splits > 0) return g_force_splits > kMaxSplits ? kMaxSplits : g_force_splits;
     const int tiles = ((T + 127) / 128) * ((hidden + 127) / 128);
     const int slots = 2 * (sm_count() > 0 ? sm_count() : 148);
     int s = slots / (tiles > 0 ? tiles : 1);
     s = s < 1 ? 1 : (s > kMaxSplits ? kMaxSplits : s);
     while (s > 1 && (K / 64) / s < 8) --s;  // keep at least 8 K blocks per slice
+    // With persistent CTAs a half-filled machine already overlaps its epilogues; the extra
+    // fp32 traffic of the partial sums only pays when very few tiles exist.
+    if (2 * tiles > (sm_count() > 0 ? sm_count() : 148)) s = 1;
     return s;
 }
 
@@ -90,6 +96,9 @@ int check_layer(const et_encoder_layer_t* L) {
 }  // namespace et
 
 extern "C" {
+
+// Test hook: number of K slices of the FFN2 product (0 = automatic, 1 = no split).
+void et_debug_force_ffn2_splits(int n) { et::g_force_splits = n; }
 
 size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq) {
     if (et::check_layer(layer) != ET_OK || batch <= 0 || seq <= 0) return 0;

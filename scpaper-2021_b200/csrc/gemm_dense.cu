@@ -1,13 +1,15 @@
 // Dense fp16 GEMM  Y[M, N] = act(X[M, K] . W[N, K]^T + bias)  on tcgen05 tensor cores.
 //
-// One CTA computes a 128 x BN output tile.  Warp 0 streams 128x64 (X) and BNx64 (W)
-// K-major tiles into a ring of 128-byte-swizzled shared-memory stages with TMA; one
-// thread of warp 1 issues tcgen05.mma (M=128, N=BN, K=16) with the fp32 accumulator in
-// tensor memory; warps 2-9 (two per tensor-memory lane quadrant) read the accumulator back
-// with software-pipelined tcgen05.ld, add the bias (staged in shared memory while the main
-// loop runs), apply the activation and write the tile through a swizzled staging buffer and
-// TMA stores.  Rows / columns / K beyond the problem are zero-filled by TMA on the way in
-// and clipped on the way out.  Every mbarrier wait is bounded.
+// Each CTA walks a static list of 128 x BN output tiles (persistent form: one CTA per SM and
+// several tiles each; single-tile form: one tile per CTA, two CTAs per SM).  Warp 0
+// streams 128x64 (X) and BNx64 (W) K-major tiles into a ring of 128-byte-swizzled
+// shared-memory stages with TMA; one thread of warp 1 issues tcgen05.mma (M=128, N=BN, K=16)
+// into one of TWO fp32 accumulators in tensor memory, so that warps 2-9 (two per
+// tensor-memory lane quadrant) can drain the accumulator of tile i - software-pipelined
+// tcgen05.ld, bias staged in shared memory, activation, fp16, swizzled staging tile, TMA
+// store - while the tensor core already works on tile i + 1.  Rows / columns / K beyond the
+// problem are zero-filled by TMA on the way in and clipped on the way out.  Every mbarrier
+// wait is bounded.
 //
 // Output modes: fp16 tile store (Linear layers), index-list store (row-pruned Linear:
 // scattered or compressed columns), grouped rows (per-head V.O projection), and fp32
@@ -19,38 +21,40 @@ namespace et {
 
 namespace {
 
-// Optional per-CTA timestamps for bring-up builds (-DET_TIMELINE); compiled out otherwise.
-#ifdef ET_TIMELINE
-__device__ long long et_timeline[65536];
-#define ET_TL(slot)                                                                       \
-    et_timeline[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = \
-        clock64()
-#else
-#define ET_TL(slot) ((void)0)
-#endif
-
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int EPI_WARPS = 8;
-constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_THREADS = 32 * EPI_WARPS;
+constexpr int GEMM_THREADS = 64 + EPI_THREADS;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 
 enum : int { OUT_TILE_F16 = 0, OUT_INDEXED = 1, OUT_GROUPED = 2, OUT_PARTIAL_F32 = 3 };
 
-template <int BN, int STAGES>
+// PERSIST: several tiles per CTA, two accumulators, dedicated staging tiles (the ring keeps
+// running during the epilogue).  !PERSIST: exactly one tile per CTA, one accumulator, the
+// staging tiles reuse the then idle ring, small enough for two CTAs per SM.
+template <int BN, int STAGES, bool PERSIST>
 struct GemmCfg {
     static constexpr int B_STAGE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int BAR_BYTES = 256 + 8 * BN;  // barriers + staged bias (fp32) and column ids
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + align slack
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    // the epilogue's staging tiles live in the idle pipeline stages
-    static_assert(STAGES * STAGE_BYTES >= 4 * (BN / 32) * 4096, "staging does not fit");
+    // staging tiles of the epilogue: one 4 KB tile per (quadrant, 64 fp16 columns) or, for fp32
+    // partials (BN <= 128 only), per (quadrant, 32 fp32 columns)
+    static constexpr int STAGING_NEED = BN <= 128 ? BN * 512 : BN * 256;
+    static constexpr int STAGING_BYTES = PERSIST ? STAGING_NEED : 0;
+    static constexpr int MISC_BYTES = 256 + 2 * 8 * BN;  // barriers + 2 x (bias fp32 + column ids)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + MISC_BYTES + 1024;
+    static constexpr int NACC = PERSIST ? 2 : 1;
+    static constexpr int TMEM_COLS = NACC * BN < 32 ? 32 : NACC * BN;
+    static constexpr int MIN_CTAS = (!PERSIST && SMEM_BYTES <= 113 * 1024) ? 2 : 1;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
+    static_assert(TMEM_COLS <= 512, "tensor memory budget exceeded");
+    static_assert(PERSIST || STAGES * STAGE_BYTES >= STAGING_NEED, "staging does not fit the ring");
 };
 
-// blockIdx.z selects a group (B_MN: g-th weight matrix / bias, output rows interleaved: row m
-// of group g lands at (m / grp_rows) * grp_stride + g * grp_rows + m % grp_rows) or a K split
-// (OUT_PARTIAL_F32: K blocks [z * kb_per_split, (z + 1) * kb_per_split)).
+// Tiles are numbered t = (z * tiles_m + m) * tiles_n + n.  z selects a group (B_MN: z-th
+// weight matrix / bias, output rows interleaved: row m of group z lands at
+// (m / grp_rows) * grp_stride + z * grp_rows + m % grp_rows) or a K split (OUT_PARTIAL_F32:
+// K blocks [z * kb_per_split, (z + 1) * kb_per_split)).
 struct GemmArgs {
     void* Y;
     const __half* bias;
@@ -59,6 +63,7 @@ struct GemmArgs {
     int grp_rows, grp_stride;
     int out_mode;
     int kb_per_split;
+    int nz;  // groups or splits
     int* err_word;
 };
 
@@ -99,17 +104,18 @@ __device__ __forceinline__ void stage_f16_chunk(const uint32_t (&r)[32], const f
     }
 }
 
+struct TileCoord {
+    int n0, m0, z, kb_begin, num_kb;
+};
+
 // B_MN == false: W is [N, K] with K contiguous (the Linear weight layout).
 // B_MN == true : W is [groups][K, N] with N contiguous; its tiles are consumed in place
 //                as MN-major operands (64-column atoms of 64 K-rows, 8 KB each).
-template <int BN, int STAGES, int MIN_CTAS, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, MIN_CTAS)
+template <int BN, int STAGES, bool PERSIST, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, STAGES, PERSIST>::MIN_CTAS))
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmY, const GemmArgs g) {
-    using Cfg = GemmCfg<BN, STAGES>;
-    const int zidx = blockIdx.z;
-    const int grp = B_MN ? zidx : 0;
-    const __half* __restrict__ bias = g.bias ? g.bias + static_cast<size_t>(grp) * g.N : nullptr;
+    using Cfg = GemmCfg<BN, STAGES, PERSIST>;
     const int* __restrict__ col_map = g.col_map;
     const int M = g.M, N = g.N;
     int* err_word = g.err_word;
@@ -120,34 +126,53 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    // single-tile form: all MMAs of the tile have completed before the epilogue touches the ring
+    uint8_t* sStage = PERSIST ? smem + STAGES * Cfg::STAGE_BYTES : smem;
+    uint8_t* misc = smem + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    uint64_t* acc_full = empty_bar + STAGES;  // [2]
+    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* s_bias = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
-    int* s_col = reinterpret_cast<int*>(s_bias + BN);
+    float* s_bias = reinterpret_cast<float*>(misc + 256);  // [2][BN]
+    int* s_col = reinterpret_cast<int*>(s_bias + 2 * BN);  // [2][BN]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN;
-    const int m0 = blockIdx.y * BM;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int tiles_m = (M + BM - 1) / BM;
+    const int total_tiles = tiles_n * tiles_m * g.nz;
     const int kb_total = (g.K + BK - 1) / BK;
-    int kb_begin = 0, kb_end = kb_total;
-    if (g.out_mode == OUT_PARTIAL_F32) {
-        kb_begin = zidx * g.kb_per_split;
-        kb_end = kb_begin + g.kb_per_split < kb_total ? kb_begin + g.kb_per_split : kb_total;
-        if (kb_end < kb_begin) kb_end = kb_begin;
-    }
-    const int num_kb = kb_end - kb_begin;
+
+    auto decode = [&](int t) {
+        TileCoord c;
+        c.n0 = (t % tiles_n) * BN;
+        const int rest = t / tiles_n;
+        c.m0 = (rest % tiles_m) * BM;
+        c.z = rest / tiles_m;
+        c.kb_begin = 0;
+        int kb_end = kb_total;
+        if (g.out_mode == OUT_PARTIAL_F32) {
+            c.kb_begin = c.z * g.kb_per_split;
+            kb_end = c.kb_begin + g.kb_per_split < kb_total ? c.kb_begin + g.kb_per_split : kb_total;
+            if (kb_end < c.kb_begin) kb_end = c.kb_begin;
+        }
+        c.num_kb = kb_end - c.kb_begin;
+        return c;
+    };
 
     if (threadIdx.x == 0) {
-        ET_TL(0);
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(acc_bar, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], EPI_WARPS);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -159,56 +184,60 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) ET_TL(1);
     pdl_launch_dependents();  // the next kernel may begin its own set-up
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
-            tma_prefetch_desc(&tmA);
-            tma_prefetch_desc(&tmB);
-            int issued = 0;
-            auto load_b = [&](int kb, int s) {
+            int it = 0;  // K blocks issued so far (ring position)
+            bool ok = true;
+            auto load_b = [&](const TileCoord& c, int kb, int s) {
                 if (B_MN) {
 #pragma unroll
                     for (int t = 0; t < BN / 64; ++t)
                         tma_load_3d(sB + s * Cfg::B_STAGE_BYTES + t * (BK * 128), &tmB, &full_bar[s],
-                                    n0 + t * 64, kb * BK, grp);
+                                    c.n0 + t * 64, kb * BK, c.z);
                 } else {
-                    tma_load_2d(sB + s * Cfg::B_STAGE_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+                    tma_load_2d(sB + s * Cfg::B_STAGE_BYTES, &tmB, &full_bar[s], kb * BK, c.n0);
                 }
             };
-            // Weights do not depend on the previous kernel: fill the ring with weight tiles
-            // first, then wait for the producer of the activations, then fetch those.
-            const int pre = num_kb < STAGES ? num_kb : STAGES;
-            for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
-                load_b(kb_begin + i, i);
-            }
-            pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                tma_load_2d(sA + i * A_STAGE_BYTES, &tmA, &full_bar[i], (kb_begin + i) * BK, m0);
-                ++issued;
-                if (i == 0) ET_TL(2);
-            }
-            for (int i = pre; i < num_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) {
-                    report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_PRODUCER);
-                    break;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const TileCoord c = decode(t);
+                int i0 = 0;
+                if (t == static_cast<int>(blockIdx.x)) {
+                    // Weights do not depend on the previous kernel: fill the ring with weight
+                    // tiles first, then wait for the producer of the activations.
+                    const int pre = c.num_kb < STAGES ? c.num_kb : STAGES;
+                    for (int i = 0; i < pre; ++i) {
+                        mbar_arrive_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+                        load_b(c, c.kb_begin + i, i);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i)
+                        tma_load_2d(sA + i * A_STAGE_BYTES, &tmA, &full_bar[i], (c.kb_begin + i) * BK,
+                                    c.m0);
+                    it = pre;
+                    i0 = pre;
                 }
-                mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-                tma_load_2d(sA + s * A_STAGE_BYTES, &tmA, &full_bar[s], (kb_begin + i) * BK, m0);
-                load_b(kb_begin + i, s);
-                ++issued;
+                for (int i = i0; i < c.num_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) {
+                        report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                    tma_load_2d(sA + s * A_STAGE_BYTES, &tmA, &full_bar[s], (c.kb_begin + i) * BK,
+                                c.m0);
+                    load_b(c, c.kb_begin + i, s);
+                }
             }
-            ET_TL(3);
             if (*abort_flag) {
                 // Let copies already in flight land before the CTA's shared memory is released.
-                const int first = issued > STAGES ? issued - STAGES : 0;
-                for (int i = first; i < issued; ++i)
-                    for (uint32_t it = 0; it < ET_SPIN_LIMIT; ++it)
+                const int first = it > STAGES ? it - STAGES : 0;
+                for (int i = first; i < it; ++i)
+                    for (uint32_t sp = 0; sp < ET_SPIN_LIMIT; ++sp)
                         if (mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1)) break;
             }
         }
@@ -216,101 +245,120 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
             constexpr uint32_t idesc = make_idesc_f16(BM, BN, 0, B_MN ? 1 : 0);
+            int it = 0, tile_iter = 0;
             bool ok = true;
-            for (int i = 0; i < num_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_iter) {
+                const TileCoord c = decode(t);
+                const int buf = PERSIST ? (tile_iter & 1) : 0;
+                const uint32_t use_ph = PERSIST ? ((tile_iter >> 1) & 1) : (tile_iter & 1);
+                // (an empty K slice issues no MMA: the commit below then arrives at once and the
+                // epilogue writes zeros)
+                // the epilogue must have drained this accumulator's previous tile
+                if (!mbar_wait_bounded(&acc_empty[buf], use_ph ^ 1, abort_flag)) {
                     report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_MMA);
-                    ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                if (i == 0) ET_TL(4);
-                const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-                const uint32_t b_addr = smem_u32(sB + s * Cfg::B_STAGE_BYTES);
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int i = 0; i < c.num_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
+                        report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_MMA);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(sB + s * Cfg::B_STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024, SWZ_128B);
-                    // MN-major: 16 K-rows = two 8-row groups of 128 bytes (SBO 1024); the next
-                    // 64-column atom sits BK * 128 bytes further (LBO).
-                    const uint64_t bd =
-                        B_MN ? make_smem_desc(b_addr + k * 2048, BK * 128, 1024, SWZ_128B)
-                             : make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B);
-                    mma_f16_ss(tmem_base, ad, bd, idesc, (i | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024, SWZ_128B);
+                        // MN-major: 16 K-rows = two 8-row groups of 128 bytes (SBO 1024); the
+                        // next 64-column atom sits BK * 128 bytes further (LBO).
+                        const uint64_t bd =
+                            B_MN ? make_smem_desc(b_addr + k * 2048, BK * 128, 1024, SWZ_128B)
+                                 : make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B);
+                        mma_f16_ss(d_tmem, ad, bd, idesc, (i | k) != 0 ? 1u : 0u);
+                    }
+                    mma_commit(&empty_bar[s]);
                 }
-                mma_commit(&empty_bar[s]);
+                if (ok) mma_commit(&acc_full[buf]);
             }
-            if (ok) mma_commit(acc_bar);
-            ET_TL(5);
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> staging -> global ----------------
-        const int q = warp & 3;           // TMEM lane quadrant this warp may read
-        const int half = (warp - 2) >> 2; // which of the quadrant's two warps this is
-        const int row = m0 + q * 32 + lane;
-        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-
-        // While the main loop runs, stage this tile's bias (and output column ids) in shared
-        // memory: read per chunk from global they cost a cold L2 round trip each time.
-        for (int i = threadIdx.x - 64; i < BN; i += 32 * EPI_WARPS) {
-            const int n = n0 + i;
-            int feat = n;
-            if (col_map != nullptr && n < N) feat = __ldg(col_map + n);
-            s_col[i] = feat;
-            s_bias[i] = (bias != nullptr && n < N && g.out_mode != OUT_PARTIAL_F32)
+        const int q = warp & 3;            // TMEM lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;  // which of the quadrant's two warps this is
+        const int et = threadIdx.x - 64;   // 0 .. EPI_THREADS - 1
+        constexpr int NCHUNK = BN / 32;
+        bool ok = true;  // a warp whose wait ran out keeps walking so that named barriers match
+        int tile_iter = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
+            const TileCoord c = decode(t);
+            const int buf = PERSIST ? (tile_iter & 1) : 0;
+            const uint32_t use_ph = PERSIST ? ((tile_iter >> 1) & 1) : (tile_iter & 1);
+            const int grp = B_MN ? c.z : 0;
+            const __half* bias = g.bias ? g.bias + static_cast<size_t>(grp) * N : nullptr;
+            float* tb = s_bias + buf * BN;
+            int* tc = s_col + buf * BN;
+            // Stage this tile's bias (and output column ids) in shared memory while its main
+            // loop is still running: read per chunk from global they cost an L2 round trip.
+            for (int i = et; i < BN; i += EPI_THREADS) {
+                const int n = c.n0 + i;
+                int feat = n;
+                if (col_map != nullptr && n < N) feat = __ldg(col_map + n);
+                tc[i] = feat;
+                tb[i] = (bias != nullptr && n < N && g.out_mode != OUT_PARTIAL_F32)
                             ? __half2float(__ldg(bias + feat))
                             : 0.f;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
-        pdl_wait();  // output buffers may still be read by the previous kernel until here
-        bool ok = true;
-        if (num_kb > 0) {
-            ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
-            if (!ok) report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_EPILOGUE);
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            if (tile_iter == 0) pdl_wait();  // outputs may still be read by the previous kernel
+            if (ok) {
+                ok = mbar_wait_bounded(&acc_full[buf], use_ph, abort_flag);
+                if (!ok) report_error(err_word, abort_flag, DEV_TIMEOUT_GEMM_EPILOGUE);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) continue;
             tc_fence_after_sync();
-            if (threadIdx.x == 64) ET_TL(6);
+            // the TMA stores of this warp's previous tile must have read the staging tiles
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+
+            const int row = c.m0 + q * 32 + lane;
+            const uint32_t lane_addr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
             // This warp's share of the tile's 32-column chunks: for the fp16 tile store whole
             // 64-column groups alternate between the quadrant's two warps, otherwise chunks do.
             const bool by_group = g.out_mode == OUT_TILE_F16;
-            constexpr int NCHUNK = BN / 32;
             int my_chunks[NCHUNK];
             int n_my = 0;
 #pragma unroll
-            for (int c = 0; c < NCHUNK; ++c) {
-                int owner = by_group ? ((c >> 1) & 1) : (c & 1);
+            for (int ch = 0; ch < NCHUNK; ++ch) {
+                int owner = by_group ? ((ch >> 1) & 1) : (ch & 1);
                 if (by_group && BN == 64) owner = 0;
-                if (owner == half && n0 + c * 32 < N) my_chunks[n_my++] = c;
+                if (owner == half && c.n0 + ch * 32 < N) my_chunks[n_my++] = ch;
             }
 
-#ifdef ET_TL_SOLO
-            if (warp != 2) n_my = 0;  // bring-up experiment: one epilogue warp alone
-#endif
-            auto finish_chunk = [&](int c, const uint32_t (&r)[32]) {
+            auto finish_chunk = [&](int ch, const uint32_t (&r)[32]) {
                 if (g.out_mode == OUT_TILE_F16) {
-                    uint8_t* tile = smem + (q * (BN / 64) + (c >> 1)) * 4096;
+                    uint8_t* tile = sStage + (q * (BN / 64) + (ch >> 1)) * 4096;
                     uint8_t* srow = tile + lane * 128;
-                    const float* b32 = s_bias + c * 32;
+                    const float* b32 = tb + ch * 32;
                     if (g.act == ET_ACT_GELU)
-                        stage_f16_chunk<ET_ACT_GELU>(r, b32, srow, c & 1, lane);
+                        stage_f16_chunk<ET_ACT_GELU>(r, b32, srow, ch & 1, lane);
                     else if (g.act == ET_ACT_RELU)
-                        stage_f16_chunk<ET_ACT_RELU>(r, b32, srow, c & 1, lane);
+                        stage_f16_chunk<ET_ACT_RELU>(r, b32, srow, ch & 1, lane);
                     else
-                        stage_f16_chunk<ET_ACT_NONE>(r, b32, srow, c & 1, lane);
-                    if (threadIdx.x == 64 && c < 2) ET_TL(10 + 3 * c);
-                    if ((c & 1) || n0 + c * 32 + 32 >= N) {  // the 64-column group is complete
+                        stage_f16_chunk<ET_ACT_NONE>(r, b32, srow, ch & 1, lane);
+                    if ((ch & 1) || c.n0 + ch * 32 + 32 >= N) {  // the 64-column group is complete
                         fence_proxy_async_smem();
                         __syncwarp();
-                        if (threadIdx.x == 64 && c < 2) ET_TL(14);
-                        if (lane == 0 && m0 + q * 32 < M)
-                            tma_store_2d(&tmY, tile, n0 + (c >> 1) * 64, m0 + q * 32);
-                        if (threadIdx.x == 64 && c < 2) ET_TL(15);
+                        if (lane == 0 && c.m0 + q * 32 < M)
+                            tma_store_2d(&tmY, tile, c.n0 + (ch >> 1) * 64, c.m0 + q * 32);
                     }
                 } else if (g.out_mode == OUT_PARTIAL_F32) {
-                    uint8_t* tile = smem + (q * NCHUNK + c) * 4096;
+                    uint8_t* tile = sStage + (q * NCHUNK + ch) * 4096;
                     uint8_t* srow = tile + lane * 128;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -319,8 +367,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && m0 + q * 32 < M)
-                        tma_store_3d(&tmY, tile, n0 + c * 32, m0 + q * 32, zidx);
+                    if (lane == 0 && c.m0 + q * 32 < M)
+                        tma_store_3d(&tmY, tile, c.n0 + ch * 32, c.m0 + q * 32, c.z);
                 } else if (row < M) {
                     // index-list / grouped-row epilogues: direct stores (small problems only)
                     __half* Y = static_cast<__half*>(g.Y);
@@ -330,11 +378,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                   static_cast<size_t>(grp) * g.grp_rows + row % g.grp_rows;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int n = n0 + c * 32 + j;
+                        const int n = c.n0 + ch * 32 + j;
                         if (n < N) {
-                            const float v =
-                                apply_act(__uint_as_float(r[j]) + s_bias[c * 32 + j], g.act);
-                            const int col = (col_map != nullptr && !g.scatter) ? n : s_col[c * 32 + j];
+                            const float v = apply_act(__uint_as_float(r[j]) + tb[ch * 32 + j], g.act);
+                            const int col = (col_map != nullptr && !g.scatter) ? n : tc[ch * 32 + j];
                             Y[out_row * g.ldy + col] = __float2half_rn(v);
                         }
                     }
@@ -344,7 +391,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // software pipeline: the load of the next chunk is in flight while this one is
             // converted and staged
             uint32_t ra[32], rb[32];
-            if (num_kb == 0) {
+            if (c.num_kb == 0) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) ra[j] = 0u;
                 for (int i = 0; i < n_my; ++i) finish_chunk(my_chunks[i], ra);
@@ -353,31 +400,29 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
                 for (int i = 0; i < n_my; i += 2) {
                     tmem_ld_wait_regs(ra);
-                    if (threadIdx.x == 64 && i == 0) ET_TL(9);
                     if (i + 1 < n_my) tmem_ld32(lane_addr + my_chunks[i + 1] * 32, rb);
                     finish_chunk(my_chunks[i], ra);
                     if (i + 1 < n_my) {
                         tmem_ld_wait_regs(rb);
-                        if (threadIdx.x == 64 && i == 0) ET_TL(12);
                         if (i + 2 < n_my) tmem_ld32(lane_addr + my_chunks[i + 2] * 32, ra);
                         finish_chunk(my_chunks[i + 1], rb);
                     }
                 }
             }
-            if (g.out_mode == OUT_TILE_F16 || g.out_mode == OUT_PARTIAL_F32) {
-                if (lane == 0) {
-                    tma_store_commit();
-                    tma_store_wait_read();
-                }
+            // this warp no longer needs the accumulator: hand it back to the MMA thread
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&acc_empty[buf]);
+                tma_store_commit();
             }
         }
+        if (lane == 0) tma_store_wait_read();
     }
 
-    if (threadIdx.x == 64) ET_TL(7);
     pdl_wait();  // no CTA may retire before the kernels it depends on have completed
     tc_fence_before_sync();
     __syncthreads();
-    if (threadIdx.x == 0) ET_TL(8);
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
@@ -427,11 +472,13 @@ __global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __re
     }
 }
 
-template <int BN, int STAGES, int MIN_CTAS, bool B_MN>
+int g_max_ctas = 0;  // test hook: cap on the persistent grid (0 = one CTA per SM)
+
+template <int BN, int STAGES, bool PERSIST, bool B_MN>
 int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
-               const GemmArgs& args, int zdim, cudaStream_t stream) {
-    using Cfg = GemmCfg<BN, STAGES>;
-    auto kern = gemm_f16_kernel<BN, STAGES, MIN_CTAS, B_MN>;
+               GemmArgs args, int zdim, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN, STAGES, PERSIST>;
+    auto kern = gemm_f16_kernel<BN, STAGES, PERSIST, B_MN>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -441,32 +488,72 @@ int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap
             return ET_ERR_CUDA;
         attr_set[dev] = true;
     }
-    dim3 grid((args.N + BN - 1) / BN, (args.M + BM - 1) / BM, zdim);
+    args.nz = zdim;
+    const long tiles = static_cast<long>((args.N + BN - 1) / BN) * ((args.M + BM - 1) / BM) * zdim;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const long cap = (PERSIST && g_max_ctas > 0 && g_max_ctas < sms) ? g_max_ctas : sms;
+    dim3 grid(static_cast<unsigned>((PERSIST && tiles > cap) ? cap : tiles));
     return launch_kernel(kern, grid, dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, tmA, tmB, tmY,
                          args) == cudaSuccess
                ? ET_OK
                : ET_ERR_CUDA;
 }
 
-int g_force_bn = 0;
+int g_force_bn = 0;       // test hook: 0 = automatic, else 64 / 128 / 256
+int g_force_persist = -1;  // test hook: -1 = automatic, 0 = single-tile CTAs, 1 = persistent
 
-int pick_bn(int M, int N, int groups = 1) {
-    if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) return g_force_bn;
+struct TilePlan {
+    int bn;
+    bool persist;
+};
+
+// Single-tile CTAs (two per SM) win while every tile is resident at once; beyond that the
+// persistent form overlaps each tile's epilogue with the next tile's main loop.
+TilePlan pick_plan(int M, int N, int zdim) {
     const int sms = sm_count() > 0 ? sm_count() : 148;
-    const int mt = (M + BM - 1) / BM;
-    int best_bn = 128;
-    long best_cost = -1;
-    const int cands[3] = {256, 128, 64};
-    for (int bn : cands) {
-        const long tiles = static_cast<long>(mt) * ((N + bn - 1) / bn) * groups;
-        const long waves = (tiles + sms - 1) / sms;
-        const long cost = waves * (bn + 48);
-        if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            best_bn = bn;
-        }
+    const long mt = (M + BM - 1) / BM;
+    auto tiles = [&](int bn) { return mt * ((N + bn - 1) / bn) * zdim; };
+    TilePlan p;
+    if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) {
+        p.bn = g_force_bn;
+        p.persist = g_force_persist >= 0 ? g_force_persist != 0 : tiles(p.bn) > (p.bn == 256 ? sms : 2 * sms);
+        return p;
     }
-    return best_bn;
+    // Measured on B200 (K = 768 .. 8192): up to one tile per SM the one-CTA-per-SM form wins
+    // (deeper ring, no register cap); up to two tiles per SM two co-resident single-tile CTAs
+    // win; beyond that persistent CTAs overlap every epilogue with the next main loop; very
+    // long runs prefer the widest tile (least operand traffic per FLOP).
+    if (tiles(128) <= sms) {
+        p.persist = true;
+        p.bn = 128;
+    } else if (tiles(128) <= 2L * sms) {
+        p.persist = false;
+        p.bn = 128;
+    } else if (tiles(256) >= 4L * sms) {
+        p.persist = false;
+        p.bn = 256;
+    } else {
+        p.persist = true;
+        const long r128 = (tiles(128) + sms - 1) / sms, r256 = (tiles(256) + sms - 1) / sms;
+        p.bn = (r256 * 256 < r128 * 128) ? 256 : 128;
+    }
+    if (g_force_persist >= 0) p.persist = g_force_persist != 0;
+    return p;
+}
+
+template <bool B_MN>
+int dispatch(const TilePlan& p, const CUtensorMap& tmA, const CUtensorMap& tmB,
+             const CUtensorMap& tmY, const GemmArgs& args, int zdim, cudaStream_t stream) {
+    if (p.persist) {
+        if (p.bn == 256 && args.out_mode != OUT_PARTIAL_F32)
+            return launch_cfg<256, 3, true, B_MN>(tmA, tmB, tmY, args, zdim, stream);
+        if (p.bn == 64) return launch_cfg<64, 6, true, B_MN>(tmA, tmB, tmY, args, zdim, stream);
+        return launch_cfg<128, 4, true, B_MN>(tmA, tmB, tmY, args, zdim, stream);
+    }
+    if (p.bn == 256 && args.out_mode != OUT_PARTIAL_F32)
+        return launch_cfg<256, 4, false, B_MN>(tmA, tmB, tmY, args, zdim, stream);
+    if (p.bn == 64) return launch_cfg<64, 4, false, B_MN>(tmA, tmB, tmY, args, zdim, stream);
+    return launch_cfg<128, 3, false, B_MN>(tmA, tmB, tmY, args, zdim, stream);
 }
 
 int encode_operand(CUtensorMap* tm, const __half* p, int ld, int rows, int K, int box_rows) {
@@ -491,6 +578,7 @@ GemmArgs base_args(void* Y, const __half* bias, int ldy, int M, int N, int K, in
     a.grp_stride = 0;
     a.out_mode = OUT_TILE_F16;
     a.kb_per_split = 0;
+    a.nz = 1;
     a.err_word = device_error_word();
     return a;
 }
@@ -498,6 +586,8 @@ GemmArgs base_args(void* Y, const __half* bias, int ldy, int M, int N, int K, in
 }  // namespace
 
 void gemm_force_bn(int bn) { g_force_bn = bn; }
+void gemm_force_persist(int mode) { g_force_persist = mode; }
+void gemm_set_max_ctas(int n) { g_max_ctas = n; }
 
 // ---- built-in gather scratch of et_linear_col_noalloc_fwd -------------------------------
 // Callers that cannot allocate device memory (see the entry point) use this array instead of
@@ -531,7 +621,8 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
     if (col_map == nullptr && (N % 8 || ldy % 8)) return ET_ERR_SHAPE;
     if (!device_error_word()) return ET_ERR_NO_DEVICE;
 
-    const int bn = pick_bn(M, N);
+    const TilePlan plan = pick_plan(M, N, 1);
+    const int bn = plan.bn;
     CUtensorMap tmA, tmB;
     int st;
     if ((st = encode_operand(&tmA, X, ldx, M, K, BM)) != ET_OK) return st;
@@ -548,11 +639,7 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
     args.col_map = col_map;
     args.scatter = scatter;
     args.out_mode = col_map == nullptr ? OUT_TILE_F16 : OUT_INDEXED;
-    switch (bn) {
-        case 256: return launch_cfg<256, 4, 1, false>(tmA, tmB, tmY, args, 1, stream);
-        case 64: return launch_cfg<64, 4, 2, false>(tmA, tmB, tmY, args, 1, stream);
-        default: return launch_cfg<128, 3, 2, false>(tmA, tmB, tmY, args, 1, stream);
-    }
+    return dispatch<false>(plan, tmA, tmB, tmY, args, 1, stream);
 }
 
 // P[s][m, n] = sum over the s-th slice of K of X[m, k] W[n, k]  (fp32, no bias): split-K
@@ -581,7 +668,12 @@ int launch_gemm_f16_splitk(const __half* X, int ldx, const __half* W, int ldw, f
     GemmArgs args = base_args(P, nullptr, N, M, N, K, ET_ACT_NONE);
     args.out_mode = OUT_PARTIAL_F32;
     args.kb_per_split = kb_per;
-    return launch_cfg<128, 3, 2, false>(tmA, tmB, tmY, args, splits, stream);
+    TilePlan plan;
+    plan.bn = 128;
+    plan.persist = static_cast<long>((M + BM - 1) / BM) * ((N + 127) / 128) * splits >
+                   2L * (sm_count() > 0 ? sm_count() : 148);
+    if (g_force_persist >= 0) plan.persist = g_force_persist != 0;
+    return dispatch<false>(plan, tmA, tmB, tmY, args, splits, stream);
 }
 
 // Y[(m / grp_rows) * groups * grp_rows + g * grp_rows + m % grp_rows, :] = X[m, :] . W[g] + bias[g]
@@ -595,7 +687,9 @@ int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const 
         return ET_ERR_ALIGNMENT;
     if (ldx % 8 || K % 8 || N % 8 || groups > 65535) return ET_ERR_SHAPE;
     if (!device_error_word()) return ET_ERR_NO_DEVICE;
-    const int bn = pick_bn(M, N, groups) == 64 ? 64 : 128;
+    TilePlan plan = pick_plan(M, N, groups);
+    if (plan.bn == 256) plan.bn = 128;
+    const int bn = plan.bn;
     CUtensorMap tmA, tmB;
     int st;
     if ((st = encode_operand(&tmA, X, ldx, M, K, BM)) != ET_OK) return st;
@@ -612,8 +706,8 @@ int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const 
     args.out_mode = OUT_GROUPED;
     args.grp_rows = grp_rows;
     args.grp_stride = groups * grp_rows;
-    if (bn == 64) return launch_cfg<64, 4, 2, true>(tmA, tmB, tmA, args, groups, stream);
-    return launch_cfg<128, 3, 2, true>(tmA, tmB, tmA, args, groups, stream);
+    (void)bn;
+    return dispatch<true>(plan, tmA, tmB, tmA, args, groups, stream);
 }
 
 }  // namespace et
@@ -624,6 +718,10 @@ extern "C" {
 
 // Test hook: 0 = automatic tile width, else 64 / 128 / 256.
 void et_debug_force_gemm_bn(int bn) { et::gemm_force_bn(bn); }
+// Test hook: cap on the number of persistent CTAs (0 = one per SM).
+void et_debug_set_gemm_max_ctas(int n) { et::gemm_set_max_ctas(n); }
+// Test hook: -1 = automatic, 0 = one tile per CTA, 1 = persistent CTAs.
+void et_debug_force_gemm_persist(int mode) { et::gemm_force_persist(mode); }
 
 int et_linear_dense_fwd(const et_half* X, const et_half* W, const et_half* bias, et_half* Y,
                         int T, int in, int out, int act, et_stream stream) {
