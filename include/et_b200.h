@@ -85,6 +85,27 @@ int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_
                        int nnz_tiles, const et_half* bias, const et_half* X, et_half* Y, int T,
                        int in, int out, int act, et_stream stream);
 
+/* The same tile-pruned Linear on RE-PACKED weights.  Weights are static, so the operator
+ * may reorder its tiles once into the order the kernel consumes them - (panel of 8 block
+ * rows, chunk of 4 block columns, row, column) - with one presence mask and one tile offset
+ * per (panel, chunk); a chunk's tiles then arrive with a single bulk copy.  The re-packing
+ * is a pure permutation of the tile-CSR arrays:
+ *   et_tile_pack_dims   sizes of the mask / offset arrays (npanel * nchunk entries each);
+ *   et_tile_pack_plan   HOST index arrays in, masks / offsets / permutation out (host);
+ *   et_tile_pack_tiles  packed_tiles[i] = tiles[perm[i]] on the GPU (perm: device array);
+ *   et_linear_tile_packed_fwd  the forward pass; row_ptr as in et_linear_tile_fwd.
+ * Stands in for the same reference call as et_linear_tile_fwd (Linear/SPMM_tile.cu:312-324);
+ * the reference keeps its tiles in file order. */
+int et_tile_pack_dims(int in, int out, int* npanel, int* nchunk);
+int et_tile_pack_plan(const int32_t* row_ptr, const int32_t* row_off, int nnz_tiles, int in, int out,
+                      uint32_t* pk_mask, int32_t* pk_off, int32_t* perm);
+int et_tile_pack_tiles(const et_half* tiles, const int32_t* perm, int nnz_tiles,
+                       et_half* packed_tiles, et_stream stream);
+int et_linear_tile_packed_fwd(const int32_t* row_ptr, const uint32_t* pk_mask, const int32_t* pk_off,
+                              const et_half* pk_tiles, int nnz_tiles, const et_half* bias,
+                              const et_half* X, et_half* Y, int T, int in, int out, int act,
+                              et_stream stream);
+
 /* Row-pruned weights: rows[nn_row, in] are the weights of output features
  * row_id[0..nn_row) (ascending); every other output column receives the bias alone.
  * Stands in for Linear<row_mat>::forward(half*, half*) (Linear/SPMM_row.cu:62-75:
@@ -233,16 +254,20 @@ int et_linear_vo_fwd(const et_half* X, const et_half* Wvo_t, const et_half* bias
  *   a = O(attention(QKV(x)));  y = LN1(a + x);  out = LN2(W2 act(W1 y + b1) + b2 + y)
  * ================================================================================= */
 #define ET_FMT_DENSE 0
-#define ET_FMT_TILE 1
+#define ET_FMT_TILE 1        /* tile-CSR as the reference stores it                        */
+#define ET_FMT_TILE_PACKED 2 /* re-packed tile-CSR (et_tile_pack_plan / et_tile_pack_tiles) */
 
 typedef struct {
-    int format;             /* ET_FMT_DENSE or ET_FMT_TILE                              */
+    int format;             /* ET_FMT_DENSE, ET_FMT_TILE or ET_FMT_TILE_PACKED          */
     int in, out;
-    const et_half* weight;  /* dense: W[out, in]; tile: tiles[nnz][256]                 */
-    const int32_t* row_ptr; /* tile only                                                */
-    const int32_t* row_off; /* tile only                                                */
-    int nnz_tiles;          /* tile only                                                */
+    const et_half* weight;  /* dense: W[out, in]; tile: tiles[nnz][256] (packed order for
+                               ET_FMT_TILE_PACKED)                                       */
+    const int32_t* row_ptr; /* tile formats                                             */
+    const int32_t* row_off; /* ET_FMT_TILE only                                         */
+    int nnz_tiles;          /* tile formats                                             */
     const et_half* bias;    /* [out] or NULL                                            */
+    const uint32_t* pk_mask; /* ET_FMT_TILE_PACKED only                                 */
+    const int32_t* pk_off;   /* ET_FMT_TILE_PACKED only                                 */
 } et_linear_t;
 
 typedef struct {

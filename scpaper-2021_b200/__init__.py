@@ -17,12 +17,13 @@ LIB_PATH = os.path.join(_HERE, "libet_b200.so")
 
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_PADDING, MASK_ADDITIVE = 0, 1, 2, 3
-FMT_DENSE, FMT_TILE = 0, 1
+FMT_DENSE, FMT_TILE, FMT_TILE_PACKED = 0, 1, 2
 
 # Every symbol include/et_b200.h declares (checked by the CPU test-suite against the header).
 ABI_SYMBOLS = [
     "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
-    "et_linear_dense_fwd", "et_linear_tile_fwd", "et_linear_row_fwd",
+    "et_linear_dense_fwd", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
+    "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_linear_row_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
     "et_linear_1x16_fwd",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
@@ -41,7 +42,7 @@ class LinearDesc(ctypes.Structure):
     """et_linear_t"""
     _fields_ = [("format", c_int), ("in_", c_int), ("out", c_int), ("weight", c_void_p),
                 ("row_ptr", c_void_p), ("row_off", c_void_p), ("nnz_tiles", c_int),
-                ("bias", c_void_p)]
+                ("bias", c_void_p), ("pk_mask", c_void_p), ("pk_off", c_void_p)]
 
 
 class EncoderLayerDesc(ctypes.Structure):
@@ -116,6 +117,52 @@ def linear_tile(x, row_ptr, row_off, tiles, out, bias=None, act=ACT_NONE):
                                    _p(tiles) if nnz else None, c_int(nnz), _p(bias), _p(x), _p(y),
                                    c_int(T), c_int(inn), c_int(out), c_int(act), _stream()),
           "et_linear_tile_fwd")
+    return y
+
+
+class PackedTiles:
+    """Tile-CSR weights re-packed for et_linear_tile_packed_fwd.  Built from host arrays
+    (row_ptr, row_off, tiles[nnz, 256] fp16): the plan runs on the host, the tiles are
+    permuted on the GPU."""
+
+    def __init__(self, row_ptr, row_off, tiles, inn: int, out: int, device="cuda"):
+        import numpy as np
+        import torch
+        nnz = int(tiles.shape[0])
+        npanel, nchunk = c_int(0), c_int(0)
+        check(lib().et_tile_pack_dims(c_int(inn), c_int(out), ctypes.byref(npanel),
+                                      ctypes.byref(nchunk)), "et_tile_pack_dims")
+        n = npanel.value * nchunk.value
+        rp = np.ascontiguousarray(row_ptr, np.int32)
+        ro = np.ascontiguousarray(row_off, np.int32)
+        mask = np.zeros(n, np.uint32)
+        off = np.zeros(n, np.int32)
+        perm = np.zeros(max(nnz, 1), np.int32)
+        vp = lambda a: a.ctypes.data_as(c_void_p)
+        check(lib().et_tile_pack_plan(vp(rp), vp(ro) if nnz else None, c_int(nnz), c_int(inn),
+                                      c_int(out), vp(mask), vp(off), vp(perm)), "et_tile_pack_plan")
+        self.inn, self.out, self.nnz = inn, out, nnz
+        self.perm_host = perm[:nnz].copy()
+        self.row_ptr = torch.from_numpy(rp).to(device)
+        self.pk_mask = torch.from_numpy(mask.view(np.int32)).to(device)
+        self.pk_off = torch.from_numpy(off).to(device)
+        self.tiles = torch.empty((max(nnz, 1), 256), dtype=torch.float16, device=device)
+        if nnz:
+            src = torch.from_numpy(np.ascontiguousarray(tiles)).to(device)
+            dperm = torch.from_numpy(self.perm_host).to(device)
+            check(lib().et_tile_pack_tiles(_p(src), _p(dperm), c_int(nnz), _p(self.tiles),
+                                           _stream()), "et_tile_pack_tiles")
+            torch.cuda.current_stream().synchronize()
+
+
+def linear_tile_packed(x, pk: "PackedTiles", bias=None, act=ACT_NONE):
+    T, inn = x.shape
+    y = _empty((T, pk.out), x)
+    check(lib().et_linear_tile_packed_fwd(_p(pk.row_ptr), _p(pk.pk_mask), _p(pk.pk_off),
+                                          _p(pk.tiles) if pk.nnz else None, c_int(pk.nnz),
+                                          _p(bias), _p(x), _p(y), c_int(T), c_int(inn),
+                                          c_int(pk.out), c_int(act), _stream()),
+          "et_linear_tile_packed_fwd")
     return y
 
 
@@ -289,7 +336,8 @@ def fused_vo_attention(q, k, vo, bias_o, batch, seq, nhead, dh_qk, emdim, mask_k
 class EncoderLayer:
     """Device-resident weights of one encoder layer plus the et_encoder_layer_t that
     describes them.  `weights` is the dict of numpy fp16 arrays synth.encoder_layer_weights
-    returns; tile_sparse=True stores the four Linear layers in tile-CSR form."""
+    returns; tile_sparse=True stores the four Linear layers in re-packed tile-CSR form,
+    tile_sparse="unpacked" in the reference's tile-CSR order."""
 
     def __init__(self, weights: dict, nhead: int, act_kind: int = ACT_GELU, device="cuda",
                  tile_sparse: bool = False):
@@ -309,12 +357,22 @@ class EncoderLayer:
             d.bias = weights[bname] is not None and dev(weights[bname]).data_ptr() or None
             if tile_sparse:
                 rp, ro, tiles = synth.dense_to_tile(W)
-                d.format = FMT_TILE
-                d.row_ptr = dev(rp).data_ptr()
                 d.nnz_tiles = int(tiles.shape[0])
-                if d.nnz_tiles:
-                    d.row_off = dev(ro).data_ptr()
-                    d.weight = dev(tiles).data_ptr()
+                if tile_sparse == "unpacked":
+                    d.format = FMT_TILE
+                    d.row_ptr = dev(rp).data_ptr()
+                    if d.nnz_tiles:
+                        d.row_off = dev(ro).data_ptr()
+                        d.weight = dev(tiles).data_ptr()
+                else:
+                    pk = PackedTiles(rp, ro, tiles, d.in_, d.out, device)
+                    self._keep.append(pk)
+                    d.format = FMT_TILE_PACKED
+                    d.row_ptr = pk.row_ptr.data_ptr()
+                    d.pk_mask = pk.pk_mask.data_ptr()
+                    d.pk_off = pk.pk_off.data_ptr()
+                    if d.nnz_tiles:
+                        d.weight = pk.tiles.data_ptr()
             else:
                 d.format = FMT_DENSE
                 d.weight = dev(W).data_ptr()

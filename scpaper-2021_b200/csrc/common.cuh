@@ -156,6 +156,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Same contract for waits that are expected to last long (an epilogue waiting for a whole
+// main loop): the warp sleeps between polls so that it does not compete for issue slots
+// with the producer and MMA-issuing threads that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t* bar, uint32_t parity,
+                                                          volatile int* abort_flag) {
+    for (uint32_t it = 0; it < (ET_SPIN_LIMIT >> 2); ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(128);
+        if ((it & 63u) == 63u && *abort_flag) return false;
+    }
+    return false;
+}
+
 __device__ __forceinline__ void report_error(int* err_word, volatile int* abort_flag, int code) {
     *abort_flag = 1;
     __threadfence_block();

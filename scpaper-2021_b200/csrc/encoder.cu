@@ -75,6 +75,11 @@ int run_linear(const et_linear_t& lin, const __half* X, __half* Y, int T, int ac
                                   reinterpret_cast<const __half*>(lin.weight), lin.nnz_tiles,
                                   reinterpret_cast<const __half*>(lin.bias), X, Y, T, lin.in,
                                   lin.out, act, stream);
+    if (lin.format == ET_FMT_TILE_PACKED)
+        return launch_linear_tile_packed(lin.row_ptr, lin.pk_mask, lin.pk_off,
+                                         reinterpret_cast<const __half*>(lin.weight), lin.nnz_tiles,
+                                         reinterpret_cast<const __half*>(lin.bias), X, Y, T, lin.in,
+                                         lin.out, act, stream);
     return ET_ERR_INVALID_ARG;
 }
 

@@ -32,6 +32,11 @@ int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* til
                        const __half* bias, const __half* X, __half* Y, int T, int in, int out,
                        int act, cudaStream_t stream);
 
+int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const int* pk_off,
+                              const __half* pk_tiles, int nnz_tiles, const __half* bias,
+                              const __half* X, __half* Y, int T, int in, int out, int act,
+                              cudaStream_t stream);
+
 // Fused attention (see attention.cu).  Vc_col_id / head_ptr are null for an uncompressed V.
 int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
                      int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,

@@ -14,6 +14,16 @@
 // and the accumulator columns by block row; warps 2-9 run the bias / activation / fp16
 // epilogue through a swizzled staging tile and TMA stores, writing bias alone for block
 // rows that hold no tile.
+//
+// Packed form.  Issuing one TMA per 512-byte tile makes the producer the bottleneck at high
+// sparsity, so the operator can re-pack its (static) weights once: tiles are reordered into
+// (panel, chunk, row, column) order - the order in which the kernel consumes them - and
+// stored pre-swizzled, with one presence mask and one tile offset per (panel, chunk).  A
+// chunk's tiles are then one contiguous run fetched by a single bulk copy, and the prologue
+// reads ready-made masks instead of building them.  The re-packing is a pure permutation of
+// the tile-CSR arrays (et_tile_pack_plan on the host indices, et_tile_pack_tiles on the GPU).
+#include <vector>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -42,11 +52,15 @@ constexpr int RING_BYTES = 96 * 1024;           // two CTAs per SM
 constexpr int MAX_STAGES = 4;
 constexpr int MAX_IN = 8192;
 
+// PACKED: pk_mask / pk_off / tiles describe the re-packed weights (row_off unused).
+template <bool PACKED>
 __global__ void __launch_bounds__(TILE_THREADS, 2)
 linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmY, const int* __restrict__ row_ptr,
-                   const int* __restrict__ row_off, const __half* __restrict__ bias, int T, int in,
-                   int out, int act, int* err_word) {
+                   const int* __restrict__ row_off, const uint32_t* __restrict__ pk_mask,
+                   const int* __restrict__ pk_off, const __half* __restrict__ pk_tiles,
+                   const __half* __restrict__ bias, int T, int in, int out, int act,
+                   int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
     // shared-memory provenance (plain LDS / STS instead of generic accesses)
@@ -64,7 +78,8 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     int* rp = reinterpret_cast<int*>(tmem_slot + 4);                  // [PANEL_ROWS + 1]
     float* s_bias = reinterpret_cast<float*>(misc + 256);             // [TBN]
     uint32_t* chunk_mask = reinterpret_cast<uint32_t*>(s_bias + TBN);  // [nchunk]
-    int* tile_at = reinterpret_cast<int*>(chunk_mask + ((nchunk + 3) & ~3));  // [8][nbc]
+    // unpacked: tile_at[8][nbc]; packed: chunk_off[nchunk] (first tile of each chunk)
+    int* tile_at = reinterpret_cast<int*>(chunk_mask + ((nchunk + 3) & ~3));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -80,7 +95,14 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         br = br < nbr ? br : nbr;
         rp[threadIdx.x] = __ldg(row_ptr + br);
     }
-    for (int i = threadIdx.x; i < nchunk; i += TILE_THREADS) chunk_mask[i] = 0u;
+    for (int i = threadIdx.x; i < nchunk; i += TILE_THREADS) {
+        if (PACKED) {
+            chunk_mask[i] = __ldg(pk_mask + static_cast<size_t>(panel) * nchunk + i);
+            tile_at[i] = __ldg(pk_off + static_cast<size_t>(panel) * nchunk + i);
+        } else {
+            chunk_mask[i] = 0u;
+        }
+    }
     for (int i = threadIdx.x; i < TBN; i += TILE_THREADS)
         s_bias[i] = (bias != nullptr && n0 + i < out) ? __half2float(__ldg(bias + n0 + i)) : 0.f;
     if (threadIdx.x == 0) {
@@ -88,9 +110,9 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         tma_prefetch_desc(&tmW);
         for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
+            mbar_init(&empty_bar[s], T_EPI_WARPS);
         }
-        mbar_init(acc_bar, 1);
+        mbar_init(acc_bar, T_EPI_WARPS);
         *abort_flag = 0;
         *max_cnt = 0;
         fence_barrier_init();
@@ -100,16 +122,18 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         tmem_relinquish();
     }
     __syncthreads();
-    for (int i = rp[0] + threadIdx.x; i < rp[PANEL_ROWS]; i += TILE_THREADS) {
-        int r = 0;
-        while (r < PANEL_ROWS - 1 && i >= rp[r + 1]) ++r;
-        const int off = __ldg(row_off + i);
-        if (off >= 0 && off < nbc) {
-            tile_at[r * nbc + off] = i;
-            atomicOr(&chunk_mask[off >> 2], 1u << (r * 4 + (off & 3)));
+    if (!PACKED) {
+        for (int i = rp[0] + threadIdx.x; i < rp[PANEL_ROWS]; i += TILE_THREADS) {
+            int r = 0;
+            while (r < PANEL_ROWS - 1 && i >= rp[r + 1]) ++r;
+            const int off = __ldg(row_off + i);
+            if (off >= 0 && off < nbc) {
+                tile_at[r * nbc + off] = i;
+                atomicOr(&chunk_mask[off >> 2], 1u << (r * 4 + (off & 3)));
+            }
         }
+        __syncthreads();
     }
-    __syncthreads();
     {
         int mc = 0;
         for (int i = threadIdx.x; i < nchunk; i += TILE_THREADS) {
@@ -131,88 +155,145 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     pdl_launch_dependents();
     pdl_wait();  // the tables above are weights; activations and Y need the wait
 
-    if (warp == 0) {
-        // ---------------- producer (whole warp: lane = row * 4 + column in chunk) ----------------
-        const int r = lane >> 2, kb = lane & 3;
-        int stage_it = 0;
-        bool ok = true;
-        for (int kc = 0; kc < nchunk && ok; ++kc) {
-            const uint32_t mask = chunk_mask[kc];
-            if (mask == 0u) continue;
-            const int s = stage_it % nstages;
-            const uint32_t ph = (stage_it / nstages) & 1;
-            uint8_t* stage = ring + s * stage_bytes;
+    if (warp < 2) {
+        // ---------------- producers ----------------
+        // packed: lane 0 of warps 0 and 1 take alternate chunks, each fetching the activation
+        // slab and the chunk's tiles (one bulk copy); tile-CSR: warp 0 alone, lane = row * 4 + column in chunk fetches
+        // its own tile.  Stage index and phase advance incrementally (no divisions on the path).
+        int s = 0, issued = 0;
+        uint32_t ph = 0;
+        if (PACKED) {
             if (lane == 0) {
-                ok = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag);
-                if (!ok) report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_PRODUCER);
-                else
-                    mbar_arrive_expect_tx(&full_bar[s], X_STAGE_BYTES + 512u * __popc(mask));
-                if (stage_it < 12) ET_TL(16 + stage_it * 4);
+                // the two producer threads take alternate chunks
+                for (int kc = 0; kc < nchunk; ++kc) {
+                    const uint32_t mask = chunk_mask[kc];
+                    if (mask == 0u) continue;
+                    if ((issued & 1) == warp) {
+                        uint8_t* stage = ring + s * stage_bytes;
+                        if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) {
+                            report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_PRODUCER);
+                            break;
+                        }
+                        const uint32_t bytes = 512u * __popc(mask);
+                        mbar_arrive_expect_tx(&full_bar[s], X_STAGE_BYTES + bytes);
+                        if (issued < 12) ET_TL(16 + issued * 4);
+                        tma_load_2d(stage, &tmX, &full_bar[s], kc * CHUNK, m0);
+                        // the chunk's tiles are one contiguous, pre-swizzled run
+                        bulk_load(stage + X_STAGE_BYTES,
+                                  pk_tiles + static_cast<size_t>(tile_at[kc]) * 256, bytes,
+                                  &full_bar[s]);
+                        if (issued < 12) ET_TL(17 + issued * 4);
+                    }
+                    ++issued;
+                    if (++s == nstages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
             }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
-            if (lane == 0) tma_load_2d(stage, &tmX, &full_bar[s], kc * CHUNK, m0);
-            if (mask & (1u << lane)) {
-                const int t = tile_at[r * nbc + kc * 4 + kb];
-                const int slot = __popc(mask & ((1u << lane) - 1u));
-                tma_load_2d(stage + X_STAGE_BYTES + slot * 512, &tmW, &full_bar[s], 0, t * 16);
+        } else if (warp == 0) {
+            const int r = lane >> 2, kb = lane & 3;
+            bool ok = true;
+            for (int kc = 0; kc < nchunk && ok; ++kc) {
+                const uint32_t mask = chunk_mask[kc];
+                if (mask == 0u) continue;
+                uint8_t* stage = ring + s * stage_bytes;
+                if (lane == 0) {
+                    ok = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag);
+                    if (!ok) report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_PRODUCER);
+                    else
+                        mbar_arrive_expect_tx(&full_bar[s], X_STAGE_BYTES + 512u * __popc(mask));
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                if (lane == 0) tma_load_2d(stage, &tmX, &full_bar[s], kc * CHUNK, m0);
+                if (mask & (1u << lane)) {
+                    const int t = tile_at[r * nbc + kc * 4 + kb];
+                    const int slot = __popc(mask & ((1u << lane) - 1u));
+                    tma_load_2d(stage + X_STAGE_BYTES + slot * 512, &tmW, &full_bar[s], 0, t * 16);
+                }
+                ++issued;
+                if (++s == nstages) {
+                    s = 0;
+                    ph ^= 1u;
+                }
             }
-            __syncwarp();
-            if (lane == 0 && stage_it < 12) ET_TL(17 + stage_it * 4);
-            ++stage_it;
         }
         if (*abort_flag && lane == 0) {
-            const int first = stage_it > nstages ? stage_it - nstages : 0;
-            for (int it2 = first; it2 < stage_it; ++it2)
+            // let copies in flight land: the last min(issued, nstages) stages
+            int ss = s;
+            uint32_t pp = ph;
+            const int pending = issued < nstages ? issued : nstages;
+            for (int i = 0; i < pending; ++i) {
+                if (--ss < 0) {
+                    ss = nstages - 1;
+                    pp ^= 1u;
+                }
                 for (uint32_t it = 0; it < ET_SPIN_LIMIT; ++it)
-                    if (mbar_try_wait(&full_bar[it2 % nstages], (it2 / nstages) & 1)) break;
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (panel_tiles > 0 && elect_one()) {
-            constexpr uint32_t idesc = make_idesc_f16(TBM, 16, 0, 0);
-            uint32_t started = 0;  // bit r: block row r already has a partial sum
-            int stage_it = 0;
-            bool ok = true;
-            for (int kc = 0; kc < nchunk; ++kc) {
-                uint32_t mask = chunk_mask[kc];
-                if (mask == 0u) continue;
-                const int s = stage_it % nstages;
-                const uint32_t ph = (stage_it / nstages) & 1;
-                if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
-                    report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_MMA);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                if (stage_it < 12) ET_TL(18 + stage_it * 4);
-                const uint32_t x_addr = smem_u32(ring + s * stage_bytes);
-                uint32_t w_addr = x_addr + X_STAGE_BYTES;
-                while (mask) {
-                    const int bit = __ffs(mask) - 1;
-                    mask &= mask - 1;
-                    const int r = bit >> 2, kb = bit & 3;
-                    const uint64_t ad = make_smem_desc(x_addr + kb * 32, 16, 1024, SWZ_128B);
-                    const uint64_t bd = make_smem_desc(w_addr, 16, 256, SWZ_32B);
-                    mma_f16_ss(tmem_base + r * 16, ad, bd, idesc, (started >> r) & 1u);
-                    started |= 1u << r;
-                    w_addr += 512;
-                }
-                mma_commit(&empty_bar[s]);
-                if (stage_it < 12) ET_TL(19 + stage_it * 4);
-                ++stage_it;
+                    if (mbar_try_wait(&full_bar[ss], pp)) break;
             }
-            if (ok) mma_commit(acc_bar);
-            ET_TL(2);
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> staging -> global ----------------
-        const int q = warp & 3;            // TMEM lane quadrant
+        // ------- warps 2..9: MMA issue for one block row each, then the epilogue -------
+        // Issuing a 128 x 16 x 16 product costs far more issue time than tensor time, so the
+        // eight block rows of the panel are issued by eight threads in parallel; every warp
+        // commits its own products to the stage's empty barrier and to the accumulator barrier.
+        const int e = warp - 2;            // block row issued by this warp
+        const int q = warp & 3;            // TMEM lane quadrant read in the epilogue
         const int half = (warp - 2) >> 2;  // which 64 output columns of the panel
         bool ok = true;
         if (panel_tiles > 0) {
+            if (lane == 0) {
+                constexpr uint32_t idesc = make_idesc_f16(TBM, 16, 0, 0);
+                uint32_t started = 0;
+                int s = 0, stage_it = 0;
+                uint32_t ph = 0;
+                const uint32_t below_mask = (1u << (4 * e)) - 1u;
+                for (int kc = 0; kc < nchunk; ++kc) {
+                    const uint32_t mask = chunk_mask[kc];
+                    if (mask == 0u) continue;
+                    // a warp without a tile in this chunk still waits: its arrival must not
+                    // run ahead into the stage's next use
+                    if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
+                        report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_MMA);
+                        ok = false;
+                        break;
+                    }
+                    if (e == 0 && stage_it < 12) ET_TL(18 + stage_it * 4);
+                    uint32_t nib = (mask >> (4 * e)) & 0xFu;
+                    if (nib) {
+                        tc_fence_after_sync();
+                        const uint32_t x_addr = smem_u32(ring + s * stage_bytes);
+                        // descriptors differ from tile to tile only in their start address
+                        const uint64_t a_base = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
+                        uint64_t bd = make_smem_desc(
+                            x_addr + X_STAGE_BYTES + 512u * __popc(mask & below_mask), 16, 256,
+                            SWZ_32B);
+                        while (nib) {
+                            const int kb = __ffs(nib) - 1;
+                            nib &= nib - 1;
+                            mma_f16_ss(tmem_base + e * 16, a_base + static_cast<uint64_t>(kb * 2),
+                                       bd, idesc, started);
+                            started = 1u;
+                            bd += 32;  // next 512-byte slot
+                        }
+                        mma_commit(&empty_bar[s]);
+                    } else {
+                        mbar_arrive(&empty_bar[s]);
+                    }
+                    if (e == 0 && stage_it < 12) ET_TL(19 + stage_it * 4);
+                    ++stage_it;
+                    if (++s == nstages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (ok) mma_commit(acc_bar);
+                if (e == 0) ET_TL(2);
+            }
+            __syncwarp();
             ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
-            if (!ok) report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_EPILOGUE);
+            if (!ok && lane == 0) report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_EPILOGUE);
         }
         ok = __all_sync(0xffffffffu, ok);
         if (threadIdx.x == 64) ET_TL(3);
@@ -282,12 +363,30 @@ __global__ void tile_fill_bias_kernel(__half* __restrict__ Y, const __half* __re
 
 }  // namespace
 
-int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
-                       const __half* bias, const __half* X, __half* Y, int T, int in, int out,
-                       int act, cudaStream_t stream) {
+// dst[i] = tile perm[i] of src, stored with the 32-byte swizzle the tensor core expects
+// (16-byte half j of row r lands at half j ^ ((r >> 2) & 1)).
+__global__ void pack_tiles_kernel(const uint4* __restrict__ src, const int* __restrict__ perm,
+                                  uint4* __restrict__ dst, int nnz) {
+    const size_t total = static_cast<size_t>(nnz) * 32;  // 32 x 16 bytes per tile
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = i >> 5;
+        const int c = static_cast<int>(i & 31);  // 16-byte unit inside the tile: row = c / 2
+        const int row = c >> 1, hf = c & 1;
+        const int dc = (row << 1) | (hf ^ ((row >> 2) & 1));
+        dst[t * 32 + dc] = __ldg(src + static_cast<size_t>(__ldg(perm + t)) * 32 + c);
+    }
+}
+
+namespace {
+int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, const uint32_t* pk_mask,
+                       const int* pk_off, const __half* tiles, int nnz_tiles, const __half* bias,
+                       const __half* X, __half* Y, int T, int in, int out, int act,
+                       cudaStream_t stream) {
     if (!row_ptr || !X || !Y || T <= 0 || in <= 0 || out <= 0 || nnz_tiles < 0)
         return ET_ERR_INVALID_ARG;
-    if (nnz_tiles > 0 && (!row_off || !tiles)) return ET_ERR_INVALID_ARG;
+    if (nnz_tiles > 0 && !tiles) return ET_ERR_INVALID_ARG;
+    if (nnz_tiles > 0 && (packed ? (!pk_mask || !pk_off) : !row_off)) return ET_ERR_INVALID_ARG;
     if (act < ET_ACT_NONE || act > ET_ACT_GELU) return ET_ERR_INVALID_ARG;
     if (in % 16 || out % 16 || in > MAX_IN) return ET_ERR_SHAPE;
     if (!aligned16(X) || !aligned16(Y) || (tiles && !aligned16(tiles)) || (bias && !aligned16(bias)))
@@ -330,20 +429,43 @@ int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* til
     const int nbc = in / 16, nchunk = (in + CHUNK - 1) / CHUNK;
     const int smem_bytes = RING_BYTES + 256 + TBN * 4 + ((nchunk + 3) & ~3) * 4 +
                            PANEL_ROWS * nbc * 4 + 1024;
-    static int attr_bytes[64] = {};
+    static int attr_bytes[2][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && attr_bytes[dev] < smem_bytes) {
-        if (cudaFuncSetAttribute(linear_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_bytes) != cudaSuccess)
-            return ET_ERR_CUDA;
-        attr_bytes[dev] = smem_bytes;
+    if (dev >= 0 && dev < 64 && attr_bytes[packed][dev] < smem_bytes) {
+        const cudaError_t e =
+            packed ? cudaFuncSetAttribute(linear_tile_kernel<true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)
+                   : cudaFuncSetAttribute(linear_tile_kernel<false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return ET_ERR_CUDA;
+        attr_bytes[packed][dev] = smem_bytes;
     }
     dim3 grid((out + TBN - 1) / TBN, (T + TBM - 1) / TBM);
-    return launch_kernel(linear_tile_kernel, grid, dim3(TILE_THREADS), smem_bytes, stream, tmX, tmW,
-                         tmY, row_ptr, row_off, bias, T, in, out, act, err) == cudaSuccess
-               ? ET_OK
-               : ET_ERR_CUDA;
+    const cudaError_t e =
+        packed ? launch_kernel(linear_tile_kernel<true>, grid, dim3(TILE_THREADS), smem_bytes, stream,
+                               tmX, tmW, tmY, row_ptr, row_off, pk_mask, pk_off, tiles, bias, T, in,
+                               out, act, err)
+               : launch_kernel(linear_tile_kernel<false>, grid, dim3(TILE_THREADS), smem_bytes,
+                               stream, tmX, tmW, tmY, row_ptr, row_off, pk_mask, pk_off, tiles, bias,
+                               T, in, out, act, err);
+    return e == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+}
+}  // namespace
+
+int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
+                       const __half* bias, const __half* X, __half* Y, int T, int in, int out,
+                       int act, cudaStream_t stream) {
+    return launch_tile_common(false, row_ptr, row_off, nullptr, nullptr, tiles, nnz_tiles, bias, X, Y,
+                              T, in, out, act, stream);
+}
+
+int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const int* pk_off,
+                              const __half* pk_tiles, int nnz_tiles, const __half* bias,
+                              const __half* X, __half* Y, int T, int in, int out, int act,
+                              cudaStream_t stream) {
+    return launch_tile_common(true, row_ptr, nullptr, pk_mask, pk_off, pk_tiles, nnz_tiles, bias, X, Y,
+                              T, in, out, act, stream);
 }
 
 }  // namespace et
@@ -357,6 +479,76 @@ int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_
                                   nnz_tiles, reinterpret_cast<const __half*>(bias),
                                   reinterpret_cast<const __half*>(X), reinterpret_cast<__half*>(Y),
                                   T, in, out, act, static_cast<cudaStream_t>(stream));
+}
+
+// ---- re-packing of tile-CSR weights for the packed forward ---------------------------------
+// Sizes: the packed layout has ceil(out / 128) panels x ceil(in / 64) chunks.
+int et_tile_pack_dims(int in, int out, int* npanel, int* nchunk) {
+    if (in <= 0 || out <= 0 || !npanel || !nchunk) return ET_ERR_INVALID_ARG;
+    if (in % 16 || out % 16) return ET_ERR_SHAPE;
+    *npanel = (out + et::TBN - 1) / et::TBN;
+    *nchunk = (in + et::CHUNK - 1) / et::CHUNK;
+    return ET_OK;
+}
+
+// Host side (index arrays in host memory): computes, for every (panel, chunk), the presence
+// mask (bit = row_in_panel * 4 + column_in_chunk) and the first packed tile, and the
+// permutation perm[i] = tile-CSR index of the i-th packed tile.
+int et_tile_pack_plan(const int32_t* row_ptr, const int32_t* row_off, int nnz_tiles, int in, int out,
+                      uint32_t* pk_mask, int32_t* pk_off, int32_t* perm) {
+    int st = et_validate_tile_mat(row_ptr, row_off, nnz_tiles, in, out);
+    if (st != ET_OK) return st;
+    if (!pk_mask || !pk_off || (nnz_tiles > 0 && !perm)) return ET_ERR_INVALID_ARG;
+    const int npanel = (out + et::TBN - 1) / et::TBN, nchunk = (in + et::CHUNK - 1) / et::CHUNK;
+    const int nbr = out / 16;
+    int next = 0;
+    for (int p = 0; p < npanel; ++p) {
+        // cursor per block row of the panel (columns ascend inside a row)
+        int cur[et::PANEL_ROWS], end[et::PANEL_ROWS];
+        for (int r = 0; r < et::PANEL_ROWS; ++r) {
+            const int br = p * et::PANEL_ROWS + r;
+            cur[r] = br < nbr ? row_ptr[br] : 0;
+            end[r] = br < nbr ? row_ptr[br + 1] : 0;
+        }
+        for (int c = 0; c < nchunk; ++c) {
+            uint32_t mask = 0;
+            pk_off[p * nchunk + c] = next;
+            for (int r = 0; r < et::PANEL_ROWS; ++r)
+                while (cur[r] < end[r] && row_off[cur[r]] < (c + 1) * 4) {
+                    mask |= 1u << (r * 4 + (row_off[cur[r]] & 3));
+                    perm[next++] = cur[r]++;
+                }
+            pk_mask[p * nchunk + c] = mask;
+        }
+    }
+    return next == nnz_tiles ? ET_OK : ET_ERR_INDEX;
+}
+
+// Device side: packed_tiles[i] = tiles[perm[i]], pre-swizzled.  perm is a device array.
+int et_tile_pack_tiles(const et_half* tiles, const int32_t* perm, int nnz_tiles,
+                       et_half* packed_tiles, et_stream stream) {
+    if (nnz_tiles < 0 || (nnz_tiles > 0 && (!tiles || !perm || !packed_tiles)))
+        return ET_ERR_INVALID_ARG;
+    if (nnz_tiles == 0) return ET_OK;
+    if (!et::aligned16(tiles) || !et::aligned16(packed_tiles)) return ET_ERR_ALIGNMENT;
+    const size_t total = static_cast<size_t>(nnz_tiles) * 32;
+    const int blocks = static_cast<int>((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    et::pack_tiles_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(tiles), perm, reinterpret_cast<uint4*>(packed_tiles),
+        nnz_tiles);
+    return cudaGetLastError() == cudaSuccess ? ET_OK : ET_ERR_CUDA;
+}
+
+int et_linear_tile_packed_fwd(const int32_t* row_ptr, const uint32_t* pk_mask, const int32_t* pk_off,
+                              const et_half* pk_tiles, int nnz_tiles, const et_half* bias,
+                              const et_half* X, et_half* Y, int T, int in, int out, int act,
+                              et_stream stream) {
+    return et::launch_linear_tile_packed(row_ptr, pk_mask, pk_off,
+                                         reinterpret_cast<const __half*>(pk_tiles), nnz_tiles,
+                                         reinterpret_cast<const __half*>(bias),
+                                         reinterpret_cast<const __half*>(X),
+                                         reinterpret_cast<__half*>(Y), T, in, out, act,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -81,6 +81,19 @@ def test_tile(et, orc, cuda, T, inn, out, act, sparsity):
                  dump=f"tile_{T}_{inn}_{out}_{sparsity}")
     # format-native loop agrees with the dense evaluation of the densified weights
     assert_close(ref, orc.linear_dense(x, w, b, act), "oracle tile vs dense", 1e-5, 1e-4)
+    # re-packed weights: same result bit for bit, and the packing is a pure permutation
+    if len(ro):
+        pk = et.PackedTiles(rp, ro, tiles, inn, out, cuda)
+        yp = et.linear_tile_packed(_dev(x, cuda), pk, _dev(b, cuda), act)
+        assert et.device_error() == 0
+        import torch
+        assert torch.equal(yp, y), "packed and tile-CSR forward differ"
+        assert np.array_equal(np.sort(pk.perm_host), np.arange(len(ro)))
+        packed = pk.tiles.cpu().numpy().reshape(-1, 16, 2, 8)
+        unsw = packed.copy()
+        flip = ((np.arange(16) >> 2) & 1).astype(bool)
+        unsw[:, flip] = packed[:, flip][:, :, ::-1]
+        assert np.array_equal(unsw.reshape(-1, 256), tiles[pk.perm_host])
 
 
 def test_tile_empty_block_rows(et, orc, cuda):
