@@ -106,6 +106,17 @@ int et_linear_tile_packed_fwd(const int32_t* row_ptr, const uint32_t* pk_mask, c
                               const et_half* X, et_half* Y, int T, int in, int out, int act,
                               et_stream stream);
 
+/* Plan-time choice for a tile-pruned weight.  On B200 one 128 x 16 x 16 tensor-core product
+ * occupies the tensor pipe about as long as a product eight times wider, so the tile kernel
+ * only pays for very sparse weights.  et_tile_prefer_dense returns 1 when the dense GEMM on
+ * the expanded weight is expected to be faster (more than 8 % of the tiles stored);
+ * et_tile_densify expands tile-CSR (device arrays) into dense[out, in], pruned tiles zero, for
+ * et_linear_dense_fwd.  The result equals et_linear_tile_fwd's up to fp32 summation order.
+ * Same reference call as et_linear_tile_fwd (Linear/SPMM_tile.cu:312-324). */
+int et_tile_prefer_dense(int in, int out, int nnz_tiles);
+int et_tile_densify(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,
+                    int nnz_tiles, int in, int out, et_half* dense, et_stream stream);
+
 /* Row-pruned weights: rows[nn_row, in] are the weights of output features
  * row_id[0..nn_row) (ascending); every other output column receives the bias alone.
  * Stands in for Linear<row_mat>::forward(half*, half*) (Linear/SPMM_row.cu:62-75:

@@ -10,7 +10,7 @@ import ctypes
 import os
 from ctypes import c_float, c_int, c_size_t, c_void_p
 
-from . import synth  # noqa: F401
+from . import sharding, synth  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libet_b200.so")
@@ -23,7 +23,8 @@ FMT_DENSE, FMT_TILE, FMT_TILE_PACKED = 0, 1, 2
 ABI_SYMBOLS = [
     "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
     "et_linear_dense_fwd", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
-    "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_linear_row_fwd",
+    "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_tile_prefer_dense", "et_tile_densify",
+    "et_linear_row_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
     "et_linear_1x16_fwd",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
@@ -100,10 +101,11 @@ def _empty(shape, like):
 
 # ---- Linear layers ------------------------------------------------------------------------
 
-def linear_dense(x, w, bias=None, act=ACT_NONE):
+def linear_dense(x, w, bias=None, act=ACT_NONE, out=None):
+    """`out`: optional preallocated [T, out] result (no allocation inside the call)."""
     T, inn = x.shape
+    y = _empty((T, w.shape[0]), x) if out is None else out
     out = w.shape[0]
-    y = _empty((T, out), x)
     check(lib().et_linear_dense_fwd(_p(x), _p(w), _p(bias), _p(y), c_int(T), c_int(inn),
                                     c_int(out), c_int(act), _stream()), "et_linear_dense_fwd")
     return y
@@ -153,6 +155,23 @@ class PackedTiles:
             check(lib().et_tile_pack_tiles(_p(src), _p(dperm), c_int(nnz), _p(self.tiles),
                                            _stream()), "et_tile_pack_tiles")
             torch.cuda.current_stream().synchronize()
+
+
+def tile_prefer_dense(inn: int, out: int, nnz_tiles: int) -> bool:
+    """Plan-time choice: True when the dense GEMM on the expanded weight is expected to beat
+    the tile kernel on B200."""
+    return bool(lib().et_tile_prefer_dense(c_int(inn), c_int(out), c_int(nnz_tiles)))
+
+
+def tile_densify(row_ptr, row_off, tiles, inn: int, out: int):
+    """dense[out, in] fp16 from device tile-CSR arrays (pruned tiles zero)."""
+    import torch
+    dense = torch.empty((out, inn), dtype=torch.float16, device=row_ptr.device)
+    nnz = 0 if tiles is None else int(tiles.shape[0])
+    check(lib().et_tile_densify(_p(row_ptr), _p(row_off) if nnz else None,
+                                _p(tiles) if nnz else None, c_int(nnz), c_int(inn), c_int(out),
+                                _p(dense), _stream()), "et_tile_densify")
+    return dense
 
 
 def linear_tile_packed(x, pk: "PackedTiles", bias=None, act=ACT_NONE):
@@ -233,9 +252,9 @@ def linear_csr(x, indptr, indices, data, out, bias=None, act=ACT_NONE):
 
 # ---- normalisation / element-wise ---------------------------------------------------------
 
-def skip_layernorm(src, skip, gamma, beta):
+def skip_layernorm(src, skip, gamma, beta, out=None):
     rows, size = src.shape
-    out = _empty((rows, size), src)
+    out = _empty((rows, size), src) if out is None else out
     check(lib().et_skip_layernorm_fwd(_p(src), _p(skip), _p(gamma), _p(beta), _p(out), c_int(rows),
                                       c_int(size), _stream()), "et_skip_layernorm_fwd")
     return out
@@ -266,13 +285,13 @@ def bias_add_(data, bias):
 # ---- attention ----------------------------------------------------------------------------
 
 def attention(q, k, v, batch, seq, nhead, dh_qk, dh_v, mask_kind=MASK_NONE, mask=None,
-              valid_len=None, scale=None, ldq=None, ldk=None, ldv=None):
+              valid_len=None, scale=None, ldq=None, ldk=None, ldv=None, out=None):
     """q/k/v: fp16 tensors (possibly views into one fused buffer); ld* default to the row
-    stride of each tensor."""
+    stride of each tensor; `out`: optional preallocated result."""
     ldq = q.stride(0) if ldq is None else ldq
     ldk = k.stride(0) if ldk is None else ldk
     ldv = v.stride(0) if ldv is None else ldv
-    z = _empty((batch * seq, nhead * dh_v), q)
+    z = _empty((batch * seq, nhead * dh_v), q) if out is None else out
     scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
     check(lib().et_attention_fwd(_p(q), _p(k), _p(v), _p(z), c_int(batch), c_int(seq),
                                  c_int(nhead), c_int(dh_qk), c_int(dh_v), c_int(ldq), c_int(ldk),
@@ -337,7 +356,9 @@ class EncoderLayer:
     """Device-resident weights of one encoder layer plus the et_encoder_layer_t that
     describes them.  `weights` is the dict of numpy fp16 arrays synth.encoder_layer_weights
     returns; tile_sparse=True stores the four Linear layers in re-packed tile-CSR form,
-    tile_sparse="unpacked" in the reference's tile-CSR order."""
+    tile_sparse="unpacked" in the reference's tile-CSR order, and tile_sparse="auto" lets
+    et_tile_prefer_dense choose per weight between the packed tile kernel and the dense GEMM
+    on the expanded weight."""
 
     def __init__(self, weights: dict, nhead: int, act_kind: int = ACT_GELU, device="cuda",
                  tile_sparse: bool = False):
@@ -358,7 +379,14 @@ class EncoderLayer:
             if tile_sparse:
                 rp, ro, tiles = synth.dense_to_tile(W)
                 d.nnz_tiles = int(tiles.shape[0])
-                if tile_sparse == "unpacked":
+                if tile_sparse == "auto" and tile_prefer_dense(d.in_, d.out, d.nnz_tiles):
+                    dense = tile_densify(dev(rp), dev(ro) if d.nnz_tiles else None,
+                                         dev(tiles) if d.nnz_tiles else None, d.in_, d.out)
+                    self._keep.append(dense)
+                    d.format = FMT_DENSE
+                    d.nnz_tiles = 0
+                    d.weight = dense.data_ptr()
+                elif tile_sparse == "unpacked":
                     d.format = FMT_TILE
                     d.row_ptr = dev(rp).data_ptr()
                     if d.nnz_tiles:

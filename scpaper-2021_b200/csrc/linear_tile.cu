@@ -363,6 +363,20 @@ __global__ void tile_fill_bias_kernel(__half* __restrict__ Y, const __half* __re
 
 }  // namespace
 
+// One CTA per block row: dense[br * 16 + i][off * 16 + j] = tile[i][j] for every stored tile.
+__global__ void densify_tiles_kernel(const int* __restrict__ row_ptr, const int* __restrict__ row_off,
+                                     const __half* __restrict__ tiles, int nbc, int in,
+                                     __half* __restrict__ dense) {
+    const int br = blockIdx.x;
+    const int i = threadIdx.x >> 4, j = threadIdx.x & 15;
+    for (int t = __ldg(row_ptr + br); t < __ldg(row_ptr + br + 1); ++t) {
+        const int off = __ldg(row_off + t);
+        if (off < 0 || off >= nbc) continue;
+        dense[(static_cast<size_t>(br) * 16 + i) * in + off * 16 + j] =
+            tiles[static_cast<size_t>(t) * 256 + threadIdx.x];
+    }
+}
+
 // dst[i] = tile perm[i] of src, stored with the 32-byte swizzle the tensor core expects
 // (16-byte half j of row r lands at half j ^ ((r >> 2) & 1)).
 __global__ void pack_tiles_kernel(const uint4* __restrict__ src, const int* __restrict__ perm,
@@ -549,6 +563,36 @@ int et_linear_tile_packed_fwd(const int32_t* row_ptr, const uint32_t* pk_mask, c
                                          reinterpret_cast<const __half*>(X),
                                          reinterpret_cast<__half*>(Y), T, in, out, act,
                                          static_cast<cudaStream_t>(stream));
+}
+
+// ---- plan-time choice between the tile kernel and dense math -------------------------------
+// A 128 x 16 x 16 tensor-core product occupies the tensor pipe for about 45 cycles on B200
+// whatever its operands' source, against 8 cycles of arithmetic: per stored tile the tile
+// kernel is about five times less efficient than a dense product, and it only wins when fewer
+// than roughly one tile in twelve is stored.  Denser weights are expanded once and served by
+// the dense GEMM.
+int et_tile_prefer_dense(int in, int out, int nnz_tiles) {
+    if (in <= 0 || out <= 0 || (in & 15) || (out & 15)) return 0;
+    const double total = static_cast<double>(in >> 4) * (out >> 4);
+    return nnz_tiles > 0.08 * total ? 1 : 0;
+}
+
+int et_tile_densify(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,
+                    int nnz_tiles, int in, int out, et_half* dense, et_stream stream) {
+    if (!row_ptr || !dense || in <= 0 || out <= 0 || nnz_tiles < 0) return ET_ERR_INVALID_ARG;
+    if ((in & 15) || (out & 15)) return ET_ERR_SHAPE;
+    if (nnz_tiles > 0 && (!row_off || !tiles)) return ET_ERR_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(dense, 0, static_cast<size_t>(in) * out * sizeof(__half), s) != cudaSuccess)
+        return ET_ERR_CUDA;
+    if (nnz_tiles > 0) {
+        et::densify_tiles_kernel<<<out >> 4, 256, 0, s>>>(row_ptr, row_off,
+                                                           reinterpret_cast<const __half*>(tiles),
+                                                           in >> 4, in,
+                                                           reinterpret_cast<__half*>(dense));
+        if (cudaGetLastError() != cudaSuccess) return ET_ERR_CUDA;
+    }
+    return ET_OK;
 }
 
 }  // extern "C"

@@ -1,0 +1,84 @@
+"""Data-parallel sharding of the encoder workload: one process per GPU, whole sequences per rank.
+
+The encoder layer couples tokens only inside one sequence (attention is per batch entry,
+reference Attention/Attention.cu:53 indexes blockIdx.y = batch entry; Linear and LayerNorm are
+per token), so sequences are independent units: ranks take contiguous blocks of sequences and
+no data-path collective is needed.  The only communication is the timing protocol (barrier,
+max over ranks) and an optional gather of results for checking.
+
+Everything here is host logic over torch.distributed; it runs on `gloo` (CPU) and `nccl`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+def shard_range(n_units: int, world: int, rank: int) -> tuple[int, int]:
+    """[start, stop) of the units rank owns: contiguous blocks, the first n_units % world
+    ranks one unit longer.  Covers 0..n_units exactly once over all ranks."""
+    if world <= 0 or not (0 <= rank < world) or n_units < 0:
+        raise ValueError(f"bad shard request: n_units={n_units} world={world} rank={rank}")
+    base, extra = divmod(n_units, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def shard_rows(n_sequences: int, seq_len: int, world: int, rank: int) -> tuple[int, int]:
+    """Token-row range [start, stop) of the rank's sequences in a [n_sequences * seq_len, h]
+    activation matrix."""
+    a, b = shard_range(n_sequences, world, rank)
+    return a * seq_len, b * seq_len
+
+
+@dataclass
+class Job:
+    """Rank / world of this process and the torch.distributed plumbing of the timing protocol."""
+    rank: int = 0
+    world: int = 1
+    device: object = None  # torch.device of the tensors used for the collectives
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def max_over_ranks(self, value: float) -> float:
+        """The slowest rank's time: the figure a multi-GPU measurement reports."""
+        if self.world == 1:
+            return float(value)
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, value: float) -> float:
+        if self.world == 1:
+            return float(value)
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def throughput(self, units_this_rank: int, seconds_this_rank: float) -> float:
+        """Whole-job units per second: all ranks' units over the slowest rank's time."""
+        total = self.sum_over_ranks(float(units_this_rank))
+        return total / self.max_over_ranks(seconds_this_rank)
+
+    def gather_rows(self, local, n_sequences: int, seq_len: int):
+        """All ranks' result rows in sequence order on every rank (checking aid, not part of
+        the timed path).  `local` is this rank's [rows, h] tensor."""
+        if self.world == 1:
+            return local
+        import torch
+        import torch.distributed as dist
+        sizes = [shard_rows(n_sequences, seq_len, self.world, r) for r in range(self.world)]
+        most = max(b - a for a, b in sizes)
+        # equal-sized pieces (uneven all_gather is not portable across backends): pad, then trim
+        padded = torch.zeros((most,) + tuple(local.shape[1:]), dtype=local.dtype,
+                             device=local.device)
+        padded[:local.shape[0]] = local
+        parts = [torch.empty_like(padded) for _ in range(self.world)]
+        dist.all_gather(parts, padded)
+        return torch.cat([p[:b - a] for p, (a, b) in zip(parts, sizes)], dim=0)

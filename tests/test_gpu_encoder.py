@@ -47,6 +47,10 @@ def test_bert_base_layer_dense_and_tile(et, orc, cuda):
     refp = _oracle_stack(orc, [wp], x, batch, seq, nhead)
     assert_close(_run(et, cuda, [wp], x, batch, seq, nhead, tile_sparse=True), refp,
                  "bert-base tile 80%", dump="enc_bb_tile")
+    assert_close(_run(et, cuda, [wp], x, batch, seq, nhead, tile_sparse="unpacked"), refp,
+                 "bert-base tile 80%, tile-CSR order")
+    assert_close(_run(et, cuda, [wp], x, batch, seq, nhead, tile_sparse="auto"), refp,
+                 "bert-base tile 80%, plan-time choice")
 
 
 def test_stack_of_three_layers_with_padding(et, orc, cuda):

@@ -94,6 +94,11 @@ def test_tile(et, orc, cuda, T, inn, out, act, sparsity):
         flip = ((np.arange(16) >> 2) & 1).astype(bool)
         unsw[:, flip] = packed[:, flip][:, :, ::-1]
         assert np.array_equal(unsw.reshape(-1, 256), tiles[pk.perm_host])
+    # expansion to dense restores the pruned matrix exactly
+    dense = et.tile_densify(_dev(rp, cuda), _dev(ro, cuda) if len(ro) else None,
+                            _dev(tiles, cuda) if len(ro) else None, inn, out)
+    assert np.array_equal(_host(dense), w)
+    assert et.tile_prefer_dense(inn, out, len(ro)) == (len(ro) > 0.08 * (inn // 16) * (out // 16))
 
 
 def test_tile_empty_block_rows(et, orc, cuda):

@@ -1,0 +1,92 @@
+"""Multi-process path on CPU: two gloo ranks shard whole sequences, run the encoder layer on
+their own shard (here with the CPU oracle standing in for the GPU kernels: the sharding logic
+under test is host code), and the gathered result must equal the unsharded evaluation bit for
+bit.  Also covers the timing protocol (max over ranks, whole-job throughput)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+
+def test_shard_range_covers_every_unit_once():
+    et = entry.load_package()
+    for n in (0, 1, 5, 16, 17, 1000):
+        for world in (1, 2, 3, 8):
+            got = []
+            for r in range(world):
+                a, b = et.sharding.shard_range(n, world, r)
+                assert 0 <= a <= b <= n
+                got += list(range(a, b))
+            assert got == list(range(n))
+            sizes = [np.diff(et.sharding.shard_range(n, world, r))[0] for r in range(world)]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        et.sharding.shard_range(4, 2, 2)
+    assert et.sharding.shard_rows(5, 128, 2, 1) == (3 * 128, 5 * 128)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, n_seq: int, seq: int, out_q):
+    try:
+        import torch
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        et = entry.load_package()
+        orc = entry.load_oracle()
+        orc.build()
+        hidden, nhead, ff = 64, 4, 128
+        w = et.synth.encoder_layer_weights(11, 0, hidden, ff, std=0.05, bias_std=0.02, ln_noise=0.1)
+        x = et.synth.normal(11, 5, (n_seq * seq, hidden), 1.0)
+        vl = np.array([(7 * i) % seq + 1 for i in range(n_seq)], dtype=np.int32)
+        job = et.sharding.Job(rank=rank, world=world, device=torch.device("cpu"))
+        a, b = et.sharding.shard_range(n_seq, world, rank)
+        ra, rb = et.sharding.shard_rows(n_seq, seq, world, rank)
+        local = orc.encoder_layer(x[ra:rb], w, b - a, seq, nhead, et.ACT_GELU, 2, None, vl[a:b]) \
+            if b > a else np.zeros((0, hidden), np.float32)
+        full = job.gather_rows(torch.from_numpy(np.ascontiguousarray(local)), n_seq, seq).numpy()
+        job.barrier()
+        slow = job.max_over_ranks(1.0 + rank)          # rank r "took" 1 + r seconds
+        thr = job.throughput(b - a, 1.0 + rank)
+        if rank == 0:
+            ref = orc.encoder_layer(x, w, n_seq, seq, nhead, et.ACT_GELU, 2, None, vl)
+            out_q.put(("ok", bool(np.array_equal(full, ref)), slow, thr))
+        dist.destroy_process_group()
+    except Exception as e:  # surfaced by the parent
+        out_q.put(("error", repr(e), 0.0, 0.0))
+        raise
+
+
+@pytest.mark.parametrize("n_seq", [4, 5])
+def test_two_gloo_ranks_shard_sequences_exactly(n_seq):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world, port = 2, _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_seq, 32, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("a gloo rank did not finish")
+        assert p.exitcode == 0
+    kind, same, slow, thr = q.get(timeout=10)
+    assert kind == "ok", same
+    assert same, "sharded and unsharded results differ"
+    assert slow == 2.0
+    assert thr == n_seq / 2.0
