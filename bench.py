@@ -27,6 +27,8 @@ import __graft_entry__ as entry  # noqa: E402
 
 METRIC = "BERT-base seq128 sequences/s"
 UNIT = "sequences/s"
+WORKLOAD = ("BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, seq 128, dense weights, "
+            "all-ones mask")
 HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
 SEED = 2021
 KERNELS_PER_LAYER = 7  # QKV, attention, O, skip-LN, FFN1(+GELU), FFN2, skip-LN
@@ -124,6 +126,8 @@ def run_reference(args, rank: int):
     et = entry.load_package()
     orc = entry.load_oracle()
     orc.build()
+    # process launchers export OMP_NUM_THREADS=1: use every core this process may run on
+    orc.set_num_threads(len(os.sched_getaffinity(0)))
     ws = [et.synth.encoder_layer_weights(SEED, 0, HIDDEN, FF)]
     batch = 16
     import numpy as np
@@ -142,8 +146,9 @@ def run_reference(args, rank: int):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * LAYERS * BATCH / batch,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "BERT-base 12L h768 12 heads FFN3072 GELU, batch 16, seq 128, dense",
-                   "note": "CPU evaluation (oracle port, OpenMP) of the same encoder math"},
+        "config": {"workload": WORKLOAD, "global_batch": BATCH, "seq_len": SEQ,
+                   "note": "CPU evaluation (oracle port, OpenMP, fp32) of the same encoder math on "
+                           "rank 0's host cores"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -289,8 +294,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
         "data": "synthetic",
-        "config": {"workload": "BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, "
-                               "seq 128, dense weights, all-ones mask",
+        "config": {"workload": WORKLOAD,
                    "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"dp{world}",
                    "l2": "weights (170 MB fp16) exceed the 126 MB L2 and are streamed every step",
                    "cuda_graph": graph is not None},
@@ -369,6 +373,7 @@ def main():
         if world == 1:
             orc = entry.load_oracle()
             orc.build()
+            orc.set_num_threads(len(os.sched_getaffinity(0)))
             cpu_value, best = cpu_sample(et, orc, ws, 128, 3)
             line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": orc.num_threads(),
                                     "kind": "port",

@@ -77,6 +77,15 @@ int orc_num_threads() {
 #endif
 }
 
+// Overrides OMP_NUM_THREADS (process launchers set it to 1); n <= 0 leaves it unchanged.
+void orc_set_num_threads(int n) {
+#if defined(_OPENMP)
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 void orc_round_fp16(float* x, long n) {
 #pragma omp parallel for schedule(static)
     for (long i = 0; i < n; ++i) x[i] = round_half(x[i]);

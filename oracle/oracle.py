@@ -42,6 +42,11 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Number of OpenMP threads of the following calls (overrides OMP_NUM_THREADS)."""
+    lib().orc_set_num_threads(c_int(int(n)))
+
+
 def _f(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
