@@ -15,20 +15,14 @@
 // scattered or compressed columns), grouped rows (per-head V.O projection), and fp32
 // split-K partials (consumed by the partial-sum LayerNorm kernel).
 #include "common.cuh"
+#include "gemm_common.cuh"
 #include "kernels.h"
 
 namespace et {
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int EPI_WARPS = 8;
-constexpr int EPI_THREADS = 32 * EPI_WARPS;
-constexpr int GEMM_THREADS = 64 + EPI_THREADS;
-constexpr int A_STAGE_BYTES = BM * BK * 2;
-
-enum : int { OUT_TILE_F16 = 0, OUT_INDEXED = 1, OUT_GROUPED = 2, OUT_PARTIAL_F32 = 3 };
+using namespace gemm;
 
 // PERSIST: several tiles per CTA, two accumulators, dedicated staging tiles (the ring keeps
 // running during the epilogue).  !PERSIST: exactly one tile per CTA, one accumulator, the
@@ -50,59 +44,6 @@ struct GemmCfg {
     static_assert(TMEM_COLS <= 512, "tensor memory budget exceeded");
     static_assert(PERSIST || STAGES * STAGE_BYTES >= STAGING_NEED, "staging does not fit the ring");
 };
-
-// Tiles are numbered t = (z * tiles_m + m) * tiles_n + n.  z selects a group (B_MN: z-th
-// weight matrix / bias, output rows interleaved: row m of group z lands at
-// (m / grp_rows) * grp_stride + z * grp_rows + m % grp_rows) or a K split (OUT_PARTIAL_F32:
-// K blocks [z * kb_per_split, (z + 1) * kb_per_split)).
-struct GemmArgs {
-    void* Y;
-    const __half* bias;
-    const int* col_map;
-    int ldy, scatter, M, N, K, act;
-    int grp_rows, grp_stride;
-    int out_mode;
-    int kb_per_split;
-    int nz;  // groups or splits
-    int* err_word;
-};
-
-template <int ACT>
-__device__ __forceinline__ float act_fn(float x) {
-    if (ACT == ET_ACT_RELU) return fmaxf(x, 0.f);
-    if (ACT == ET_ACT_GELU) return gelu_tanh(x);
-    return x;
-}
-
-// 32 accumulator columns of one row -> bias, activation, fp16 -> four swizzled 16-byte
-// chunks of the row's 128-byte staging line (half 0 or 1 of a 64-column group).
-template <int ACT>
-__device__ __forceinline__ void stage_f16_chunk(const uint32_t (&r)[32], const float* bias32,
-                                                uint8_t* srow, int half, int lane) {
-#pragma unroll
-    for (int gq = 0; gq < 4; ++gq) {
-        const float4 b0 = *reinterpret_cast<const float4*>(bias32 + gq * 8);
-        const float4 b1 = *reinterpret_cast<const float4*>(bias32 + gq * 8 + 4);
-        float v[8];
-        v[0] = __uint_as_float(r[gq * 8 + 0]) + b0.x;
-        v[1] = __uint_as_float(r[gq * 8 + 1]) + b0.y;
-        v[2] = __uint_as_float(r[gq * 8 + 2]) + b0.z;
-        v[3] = __uint_as_float(r[gq * 8 + 3]) + b0.w;
-        v[4] = __uint_as_float(r[gq * 8 + 4]) + b1.x;
-        v[5] = __uint_as_float(r[gq * 8 + 5]) + b1.y;
-        v[6] = __uint_as_float(r[gq * 8 + 6]) + b1.z;
-        v[7] = __uint_as_float(r[gq * 8 + 7]) + b1.w;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = act_fn<ACT>(v[j]);
-        uint4 o;
-        o.x = pack_half2(v[0], v[1]);
-        o.y = pack_half2(v[2], v[3]);
-        o.z = pack_half2(v[4], v[5]);
-        o.w = pack_half2(v[6], v[7]);
-        const int chunk = ((half << 2) + gq) ^ (lane & 7);
-        *reinterpret_cast<uint4*>(srow + chunk * 16) = o;
-    }
-}
 
 struct TileCoord {
     int n0, m0, z, kb_begin, num_kb;
@@ -541,6 +482,26 @@ TilePlan pick_plan(int M, int N, int zdim) {
     return p;
 }
 
+int g_force_pair = -1;  // test hook: -1 = automatic, 0 = never, 128 / 256 = always that width
+
+// Width of the CTA-pair tile to use for a plain [M, K] x [N, K]^T product, or 0 for the
+// single-CTA kernels.
+int pick_pair(int M, int N, int K) {
+    if (g_force_pair == 0) return 0;
+    if (g_force_pair == 128 || g_force_pair == 256) return g_force_pair;
+    if (M < 2 * BM) return 0;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const long mt2 = (M + 2 * BM - 1) / (2 * BM);
+    // Measured on B200: 256 x 256 pair tiles win once they fill the machine more than about
+    // 1.6 times over (operand traffic per FLOP is what bounds those runs); 256 x 128 pair tiles
+    // win for few output tiles with a long K (every CTA streams weights for a long time and
+    // halving that stream pays); otherwise fill and drain dominate and the single-CTA forms win.
+    if (mt2 * ((N + 255) / 256) >= (sms / 2) * 8 / 5) return 256;
+    const long single = static_cast<long>((M + BM - 1) / BM) * ((N + 127) / 128);
+    if (K >= 2048 && single <= sms) return 128;
+    return 0;
+}
+
 template <bool B_MN>
 int dispatch(const TilePlan& p, const CUtensorMap& tmA, const CUtensorMap& tmB,
              const CUtensorMap& tmY, const GemmArgs& args, int zdim, cudaStream_t stream) {
@@ -554,13 +515,6 @@ int dispatch(const TilePlan& p, const CUtensorMap& tmA, const CUtensorMap& tmB,
         return launch_cfg<256, 4, false, B_MN>(tmA, tmB, tmY, args, zdim, stream);
     if (p.bn == 64) return launch_cfg<64, 4, false, B_MN>(tmA, tmB, tmY, args, zdim, stream);
     return launch_cfg<128, 3, false, B_MN>(tmA, tmB, tmY, args, zdim, stream);
-}
-
-int encode_operand(CUtensorMap* tm, const __half* p, int ld, int rows, int K, int box_rows) {
-    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(rows)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(ld) * 2};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(box_rows)};
-    return make_tensor_map_f16(tm, p, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 GemmArgs base_args(void* Y, const __half* bias, int ldy, int M, int N, int K, int act) {
@@ -588,6 +542,7 @@ GemmArgs base_args(void* Y, const __half* bias, int ldy, int M, int N, int K, in
 void gemm_force_bn(int bn) { g_force_bn = bn; }
 void gemm_force_persist(int mode) { g_force_persist = mode; }
 void gemm_set_max_ctas(int n) { g_max_ctas = n; }
+void gemm_force_pair(int mode) { g_force_pair = mode; }
 
 // ---- built-in gather scratch of et_linear_col_noalloc_fwd -------------------------------
 // Callers that cannot allocate device memory (see the entry point) use this array instead of
@@ -621,6 +576,11 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
     if (col_map == nullptr && (N % 8 || ldy % 8)) return ET_ERR_SHAPE;
     if (!device_error_word()) return ET_ERR_NO_DEVICE;
 
+    if (col_map == nullptr) {
+        const int pair_bn = pick_pair(M, N, K);
+        if (pair_bn != 0)
+            return launch_gemm_pair_f16(X, ldx, W, ldw, bias, Y, ldy, M, N, K, act, pair_bn, stream);
+    }
     const TilePlan plan = pick_plan(M, N, 1);
     const int bn = plan.bn;
     CUtensorMap tmA, tmB;
@@ -720,6 +680,8 @@ extern "C" {
 void et_debug_force_gemm_bn(int bn) { et::gemm_force_bn(bn); }
 // Test hook: cap on the number of persistent CTAs (0 = one per SM).
 void et_debug_set_gemm_max_ctas(int n) { et::gemm_set_max_ctas(n); }
+// Test hook: -1 = automatic, 0 = single-CTA kernels only, 128 / 256 = CTA-pair tiles of that width.
+void et_debug_force_gemm_pair(int mode) { et::gemm_force_pair(mode); }
 // Test hook: -1 = automatic, 0 = one tile per CTA, 1 = persistent CTAs.
 void et_debug_force_gemm_persist(int mode) { et::gemm_force_persist(mode); }
 

@@ -13,6 +13,11 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
                     __half* Y, int ldy, const int* col_map, int scatter, int M, int N, int K,
                     int act, cudaStream_t stream);
 
+// The same product on CTA pairs (256 x bn tiles, bn = 128 or 256); see gemm_pair.cu.
+int launch_gemm_pair_f16(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
+                         __half* Y, int ldy, int M, int N, int K, int act, int bn,
+                         cudaStream_t stream);
+
 // Grouped GEMM over weights stored [groups][K, N] (N contiguous); see gemm_dense.cu.
 int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const __half* bias,
                                __half* Y, int M, int N, int K, int groups, int grp_rows,
