@@ -38,10 +38,15 @@ struct GemmCfg {
     static constexpr int MISC_BYTES = 256 + 2 * 8 * BN;  // barriers + 2 x (bias fp32 + column ids)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + MISC_BYTES + 1024;
     static constexpr int NACC = PERSIST ? 2 : 1;
-    static constexpr int TMEM_COLS = NACC * BN < 32 ? 32 : NACC * BN;
+    static constexpr int TMEM_NEED = NACC * BN;  // allocations are powers of two, at least 32
+    static constexpr int TMEM_COLS = TMEM_NEED <= 32    ? 32
+                                     : TMEM_NEED <= 64  ? 64
+                                     : TMEM_NEED <= 128 ? 128
+                                     : TMEM_NEED <= 256 ? 256
+                                                        : 512;
     static constexpr int MIN_CTAS = (!PERSIST && SMEM_BYTES <= 113 * 1024) ? 2 : 1;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
-    static_assert(TMEM_COLS <= 512, "tensor memory budget exceeded");
+    static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
     static_assert(PERSIST || STAGES * STAGE_BYTES >= STAGING_NEED, "staging does not fit the ring");
 };
 
@@ -450,12 +455,12 @@ struct TilePlan {
 
 // Single-tile CTAs (two per SM) win while every tile is resident at once; beyond that the
 // persistent form overlaps each tile's epilogue with the next tile's main loop.
-TilePlan pick_plan(int M, int N, int zdim) {
+TilePlan pick_plan(int M, int N, int K, int zdim) {
     const int sms = sm_count() > 0 ? sm_count() : 148;
     const long mt = (M + BM - 1) / BM;
     auto tiles = [&](int bn) { return mt * ((N + bn - 1) / bn) * zdim; };
     TilePlan p;
-    if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) {
+    if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 192 || g_force_bn == 256) {
         p.bn = g_force_bn;
         p.persist = g_force_persist >= 0 ? g_force_persist != 0 : tiles(p.bn) > (p.bn == 256 ? sms : 2 * sms);
         return p;
@@ -467,16 +472,28 @@ TilePlan pick_plan(int M, int N, int zdim) {
     if (tiles(128) <= sms) {
         p.persist = true;
         p.bn = 128;
-    } else if (tiles(128) <= 2L * sms) {
+    } else if (tiles(128) <= 2L * sms && K <= 1024) {
+        // (with a long K the two co-resident CTAs only share the SM's operand bandwidth)
         p.persist = false;
         p.bn = 128;
     } else if (tiles(256) >= 4L * sms) {
         p.persist = false;
         p.bn = 256;
     } else {
+        // a few rounds of tiles per CTA: the width whose rounds x time per K block is least,
+        // a K block costing the larger of its tensor time (2 * bn cycles) and its operand
+        // bytes at the 75 B/clk an SM gets from L2 when all SMs pull
         p.persist = true;
-        const long r128 = (tiles(128) + sms - 1) / sms, r256 = (tiles(256) + sms - 1) / sms;
-        p.bn = (r256 * 256 < r128 * 128) ? 256 : 128;
+        long best = -1;
+        for (int bn : {128, 192, 256}) {
+            const long rounds = (tiles(bn) + sms - 1) / sms;
+            const long tensor = 2L * bn, bytes = (128L + bn) * 128 / 75;
+            const long cost = rounds * (tensor > bytes ? tensor : bytes);
+            if (best < 0 || cost < best) {
+                best = cost;
+                p.bn = bn;
+            }
+        }
     }
     if (g_force_persist >= 0) p.persist = g_force_persist != 0;
     return p;
@@ -505,6 +522,8 @@ int pick_pair(int M, int N, int K) {
 template <bool B_MN>
 int dispatch(const TilePlan& p, const CUtensorMap& tmA, const CUtensorMap& tmB,
              const CUtensorMap& tmY, const GemmArgs& args, int zdim, cudaStream_t stream) {
+    if (p.bn == 192 && args.out_mode == OUT_TILE_F16 && !B_MN)
+        return launch_cfg<192, 4, true, false>(tmA, tmB, tmY, args, zdim, stream);
     if (p.persist) {
         if (p.bn == 256 && args.out_mode != OUT_PARTIAL_F32)
             return launch_cfg<256, 3, true, B_MN>(tmA, tmB, tmY, args, zdim, stream);
@@ -581,7 +600,8 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
         if (pair_bn != 0)
             return launch_gemm_pair_f16(X, ldx, W, ldw, bias, Y, ldy, M, N, K, act, pair_bn, stream);
     }
-    const TilePlan plan = pick_plan(M, N, 1);
+    TilePlan plan = pick_plan(M, N, K, 1);
+    if (plan.bn == 192 && col_map != nullptr) plan.bn = 128;  // 192 exists for the tile store only
     const int bn = plan.bn;
     CUtensorMap tmA, tmB;
     int st;
@@ -647,8 +667,8 @@ int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const 
         return ET_ERR_ALIGNMENT;
     if (ldx % 8 || K % 8 || N % 8 || groups > 65535) return ET_ERR_SHAPE;
     if (!device_error_word()) return ET_ERR_NO_DEVICE;
-    TilePlan plan = pick_plan(M, N, groups);
-    if (plan.bn == 256) plan.bn = 128;
+    TilePlan plan = pick_plan(M, N, K, groups);
+    if (plan.bn == 256 || plan.bn == 192) plan.bn = 128;
     const int bn = plan.bn;
     CUtensorMap tmA, tmB;
     int st;

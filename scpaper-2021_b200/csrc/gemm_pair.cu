@@ -397,9 +397,10 @@ int launch_gemm_pair_f16(const __half* X, int ldx, const __half* W, int ldw, con
     a.kb_per_split = 0;
     a.nz = 1;
     a.err_word = device_error_word();
-    // Measured on B200: the wide tiles run best as single-tile pairs (two CTAs per SM overlap
-    // one tile's epilogue with another's main loop), the narrow ones as persistent pairs.
-    const bool persist = g_pair_persist >= 0 ? g_pair_persist != 0 : bn == 128;
+    // Measured on B200: persistent pairs (a tile's epilogue overlaps the next tile's main loop)
+    // win except for wide tiles with a very long K, where two co-resident single-tile CTAs per
+    // SM do.
+    const bool persist = g_pair_persist >= 0 ? g_pair_persist != 0 : !(bn == 256 && K >= 4096);
     if (bn == 256)
         return persist ? launch_pair_cfg<256, 4, true>(tmA, tmB, tmY, a, stream)
                        : launch_pair_cfg<256, 3, false>(tmA, tmB, tmY, a, stream);

@@ -28,30 +28,47 @@ __device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
 }
 
 // size % 8 == 0.  Variance as E[x^2] - E[x]^2 in fp32, clamped at zero.
-template <bool CACHED>
+// NCH: chunks of 8 halves per lane kept in registers (rows up to NCH * 256), 0 = any size,
+// the row is read twice.
+template <int NCH>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__ skip,
                       const __half* __restrict__ gamma, const __half* __restrict__ beta,
                       __half* __restrict__ out, int rows, int size, float eps) {
+    constexpr bool CACHED = NCH > 0;
+    constexpr int LN_CH = CACHED ? NCH : 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * LN_WARPS + warp;
+    const int nchunk = size >> 3;
+    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+    const uint4* b4 = reinterpret_cast<const uint4*>(beta);
+    // gamma / beta are weights: fetch them before waiting for the kernel that produces src,
+    // so that their L2 round trip is off the critical path
+    uint4 gq[LN_CH], bq[LN_CH];
+    if (CACHED) {
+#pragma unroll
+        for (int it = 0; it < LN_CH; ++it) {
+            const int c = lane + it * 32;
+            if (c < nchunk) {
+                gq[it] = __ldg(g4 + c);
+                bq[it] = __ldg(b4 + c);
+            }
+        }
+    }
     pdl_launch_dependents();
     pdl_wait();
     if (row >= rows) return;
-    const int nchunk = size >> 3;
     const uint4* s4 = reinterpret_cast<const uint4*>(src + static_cast<size_t>(row) * size);
     const uint4* k4 =
         skip ? reinterpret_cast<const uint4*>(skip + static_cast<size_t>(row) * size) : nullptr;
     uint4* o4 = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * size);
-    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
-    const uint4* b4 = reinterpret_cast<const uint4*>(beta);
 
-    float cache[CACHED ? LN_MAX_CHUNKS : 1][8];
+    float cache[LN_CH][8];
     float sum = 0.f, sq = 0.f;
     // CACHED: static trip count so the row stays in registers; otherwise a plain strided loop.
-    const int trips = CACHED ? LN_MAX_CHUNKS : (nchunk + 31) / 32;
+    const int trips = CACHED ? LN_CH : (nchunk + 31) / 32;
 #pragma unroll
-    for (int it = 0; it < (CACHED ? LN_MAX_CHUNKS : trips); ++it) {
+    for (int it = 0; it < (CACHED ? LN_CH : trips); ++it) {
         const int c = lane + it * 32;
         if (c < nchunk) {
             float v[8];
@@ -77,7 +94,7 @@ skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__
     const float rstd = rsqrtf(var + eps);
 
 #pragma unroll
-    for (int it = 0; it < (CACHED ? LN_MAX_CHUNKS : trips); ++it) {
+    for (int it = 0; it < (CACHED ? LN_CH : trips); ++it) {
         const int c = lane + it * 32;
         if (c < nchunk) {
             float v[8];
@@ -94,8 +111,8 @@ skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__
                 }
             }
             float g[8], b[8];
-            unpack8(__ldg(g4 + c), g);
-            unpack8(__ldg(b4 + c), b);
+            unpack8(CACHED ? gq[it] : __ldg(g4 + c), g);
+            unpack8(CACHED ? bq[it] : __ldg(b4 + c), b);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = (v[j] - mean) * rstd * g[j] + b[j];
             uint4 o;
@@ -243,12 +260,18 @@ int launch_skip_layernorm(const __half* src, const __half* skip, const __half* g
         return ET_ERR_ALIGNMENT;
     const int blocks = (rows + LN_WARPS - 1) / LN_WARPS;
     cudaError_t e;
-    if (size <= LN_MAX_CHUNKS * 8 * 32)
-        e = launch_kernel(skip_layernorm_kernel<true>, dim3(blocks), dim3(LN_WARPS * 32), 0, stream,
-                          src, skip, gamma, beta, out, rows, size, 1e-5f);
+    auto go = [&](auto kern) {
+        return launch_kernel(kern, dim3(blocks), dim3(LN_WARPS * 32), 0, stream, src, skip, gamma,
+                             beta, out, rows, size, 1e-5f);
+    };
+    if (size <= 3 * 256)
+        e = go(skip_layernorm_kernel<3>);
+    else if (size <= 4 * 256)
+        e = go(skip_layernorm_kernel<4>);
+    else if (size <= LN_MAX_CHUNKS * 256)
+        e = go(skip_layernorm_kernel<LN_MAX_CHUNKS>);
     else
-        e = launch_kernel(skip_layernorm_kernel<false>, dim3(blocks), dim3(LN_WARPS * 32), 0,
-                          stream, src, skip, gamma, beta, out, rows, size, 1e-5f);
+        e = go(skip_layernorm_kernel<0>);
     return e == cudaSuccess ? ET_OK : ET_ERR_CUDA;
 }
 
