@@ -25,7 +25,7 @@ def _qkv(et, seed, batch, seq, nhead, dh_qk, dh_v, std=1.0):
 @pytest.mark.parametrize("batch,seq,nhead,dh_qk,dh_v", [
     (1, 128, 1, 64, 64), (2, 128, 12, 64, 64), (1, 16, 2, 16, 16), (3, 48, 2, 32, 64),
     (2, 256, 4, 64, 64), (1, 384, 2, 64, 64), (1, 512, 3, 64, 64), (2, 200, 2, 48, 64),
-    (1, 1000, 1, 64, 64), (1, 128, 2, 128, 128), (1, 300, 1, 96, 112),
+    (1, 1000, 1, 64, 64), (1, 128, 2, 128, 128), (1, 300, 1, 96, 112), (1, 4096, 2, 64, 64),
 ])
 @pytest.mark.parametrize("mask_kind", [0, 1])
 def test_attention(et, orc, cuda, batch, seq, nhead, dh_qk, dh_v, mask_kind):

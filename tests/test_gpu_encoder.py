@@ -71,3 +71,57 @@ def test_pruned_qk_head_width(et, orc, cuda):
     x = et.synth.normal(11, 96, (batch * seq, hidden), 1.0)
     assert_close(_run(et, cuda, [w], x, batch, seq, nhead),
                  _oracle_stack(orc, [w], x, batch, seq, nhead), "dh_qk 48")
+
+
+def test_mixed_format_layer_bert_large_shapes(et, orc, cuda):
+    """The BERT-large case of the paper's Table-2 style sweeps, composed from the per-operator
+    entry points the C++ Encoder<config> template would bind: 1x16-pruned Q/K/V and O
+    projections (90 %), row-pruned FFN-in and column-pruned FFN-out (50 %), padding mask,
+    seq 384.  The oracle runs the format-native loops of the same operators."""
+    import torch
+    batch, seq, hidden, nhead, ff = 2, 384, 1024, 16, 4096
+    T, dh = batch * seq, hidden // nhead
+    w = et.synth.encoder_layer_weights(31, 0, hidden, ff, std=0.05, bias_std=0.02, ln_noise=0.1)
+    x = et.synth.normal(31, 95, (T, hidden), 1.0)
+    vl = np.array([384, 150], dtype=np.int32)
+    wqkv = et.synth.prune_1x16(w["wqkv"], 31, 60, 0.9)
+    wo = et.synth.prune_1x16(w["wo"], 31, 61, 0.9)
+    rid = et.synth.choose_ids(31, 62, ff, 0.5)       # FFN-in keeps these output rows
+    cid = rid                                        # FFN-out reads exactly those features
+    q16, o16 = et.synth.dense_to_1x16(wqkv), et.synth.dense_to_1x16(wo)
+    r_id, r_rows = et.synth.dense_to_row(w["w1"], rid)
+    c_id, c_cols = et.synth.dense_to_col(w["w2"], cid)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+    # ---- GPU ----
+    xd = d(x)
+    qkv = et.linear_1x16(xd, d(q16[0]), d(q16[1]), d(q16[2]), 3 * hidden, d(w["bqkv"]))
+    z = et.attention(qkv[:, :hidden], qkv[:, hidden:2 * hidden], qkv[:, 2 * hidden:], batch, seq,
+                     nhead, dh, dh, et.MASK_PADDING, None, d(vl))
+    a = et.linear_1x16(z, d(o16[0]), d(o16[1]), d(o16[2]), hidden, d(w["bo"]))
+    y = et.skip_layernorm(a, xd, d(w["ln1_g"]), d(w["ln1_b"]))
+    f = et.linear_row_compressed(y, d(r_id), d(r_rows), d(w["b1"]))   # [T, nn_row], bias of kept rows
+    f = et.act(f, et.ACT_GELU)
+    a2 = et.linear_dense(f, d(c_cols), d(w["b2"]))                     # cols[out, nn_col] on the compressed input
+    out = et.skip_layernorm(a2, y, d(w["ln2_g"]), d(w["ln2_b"]))
+    assert et.device_error() == 0
+
+    # ---- oracle, same operators (activations rounded to fp16 between operators as on the GPU) ----
+    r16 = orc.round_fp16
+    oq = r16(orc.linear_1x16(x, q16[0], q16[1], q16[2].astype(np.float32), 3 * hidden, w["bqkv"]))
+    oz = r16(orc.attention(oq[:, :hidden], oq[:, hidden:2 * hidden], oq[:, 2 * hidden:], batch, seq,
+                           nhead, dh, dh, 2, None, vl))
+    oa = r16(orc.linear_1x16(oz, o16[0], o16[1], o16[2].astype(np.float32), hidden, w["bo"]))
+    oy = r16(orc.skip_layernorm(oa, x, w["ln1_g"], w["ln1_b"]))
+    of = r16(orc.act(r16(orc.linear_row_compressed(oy, r_id, r_rows.astype(np.float32), w["b1"])), 2))
+    oa2 = r16(orc.linear_dense(of, c_cols.astype(np.float32), w["b2"]))
+    ref = orc.skip_layernorm(oa2, oy, w["ln2_g"], w["ln2_b"])
+    assert_close(out.float().cpu().numpy(), ref, "mixed-format BERT-large layer",
+                 rel_tol=8e-3, abs_tol=4e-2)
+
+    # the same FFN through the scatter / gather forms of the row- and column-pruned Linear
+    f_full = et.linear_row(y, d(r_id), d(r_rows), ff, d(w["b1"]), et.ACT_GELU)
+    a3 = et.linear_col(f_full, d(c_id), d(c_cols), d(w["b2"]))
+    assert et.device_error() == 0
+    assert_close(a3.float().cpu().numpy(), a2.float().cpu().numpy(), "row scatter + col gather FFN",
+                 rel_tol=2e-3, abs_tol=1e-2)
