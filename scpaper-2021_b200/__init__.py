@@ -438,6 +438,45 @@ class EncoderLayer:
         return out
 
 
+class HeadParallelLayer:
+    """One encoder layer over `job.world` GPUs for a batch that cannot be sharded (one long
+    sequence): every rank projects and attends over its own heads and multiplies by its heads'
+    columns of the output projection; one all-reduce adds the partial [T, hidden] sums; the
+    LayerNorms and the FFN run replicated.  `weights` is the full layer (numpy fp16)."""
+
+    def __init__(self, weights: dict, nhead: int, job, act_kind: int = ACT_GELU, device="cuda"):
+        import numpy as np
+        import torch
+        self.job, self.act = job, act_kind
+        sl = sharding.head_shard_weights(weights, nhead, job.world, job.rank)
+        self.nh, self.dqk, self.dv = sl["nhead_local"], sl["dh_qk"], sl["dh_v"]
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        self.wqkv, self.bqkv = dev(sl["wqkv"]), dev(sl["bqkv"])
+        self.wo, self.bo = dev(sl["wo"]), dev(sl["bo"])
+        self.w1, self.b1, self.w2, self.b2 = (dev(weights[k]) for k in ("w1", "b1", "w2", "b2"))
+        self.ln = [dev(weights[k]) for k in ("ln1_g", "ln1_b", "ln2_g", "ln2_b")]
+
+    def forward(self, x, batch: int, seq: int, mask_kind=MASK_NONE, mask=None, valid_len=None):
+        kq, kv = self.nh * self.dqk, self.nh * self.dv
+        a = None
+        if self.nh > 0:
+            qkv = linear_dense(x, self.wqkv, self.bqkv)
+            z = attention(qkv[:, :kq], qkv[:, kq:2 * kq], qkv[:, 2 * kq:], batch, seq, self.nh,
+                          self.dqk, self.dv, mask_kind, mask, valid_len)
+            a = linear_dense(z, self.wo, self.bo)
+        else:  # more ranks than heads: this rank only contributes the bias (rank 0) or zeros
+            import torch
+            a = self.bo.expand(x.shape[0], -1).contiguous() if self.job.rank == 0 else \
+                torch.zeros((x.shape[0], self.wo.shape[0]), dtype=x.dtype, device=x.device)
+        if self.job.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(a)  # the layer's one exchange step
+        y = skip_layernorm(a, x, self.ln[0], self.ln[1])
+        f = linear_dense(y, self.w1, self.b1, self.act)
+        a2 = linear_dense(f, self.w2, self.b2)
+        return skip_layernorm(a2, y, self.ln[2], self.ln[3])
+
+
 class EncoderStack:
     """N chained encoder layers.  The batch can be cut into `lanes` groups of sequences that
     run through the whole stack on streams of their own (sequences are independent), so that

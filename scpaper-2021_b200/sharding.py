@@ -82,3 +82,39 @@ class Job:
         parts = [torch.empty_like(padded) for _ in range(self.world)]
         dist.all_gather(parts, padded)
         return torch.cat([p[:b - a] for p, (a, b) in zip(parts, sizes)], dim=0)
+
+
+# ---- head-parallel mode: one long sequence over several GPUs --------------------------------
+# The attention block is split by head: rank r projects only its heads' Q, K, V (rows of the
+# fused weight), attends over them and multiplies by its heads' columns of the output projection,
+# which yields a partial [seq, hidden] sum; ONE all-reduce per layer adds the partial sums (the
+# reference has no multi-GPU code; this is the tensor-parallel form of Attention/Attention.h:58-142
+# for a batch that cannot be sharded).  LayerNorm and the FFN run replicated.
+
+def head_slice(nhead: int, world: int, rank: int) -> tuple[int, int]:
+    """[first, last) head of the rank: contiguous blocks, as shard_range."""
+    return shard_range(nhead, world, rank)
+
+
+def head_shard_weights(w: dict, nhead: int, world: int, rank: int) -> dict:
+    """The rank's slice of one layer's attention weights (numpy arrays in, numpy arrays out):
+    wqkv rows of its heads (kept in Q | K | V order), the matching bias entries, wo columns of
+    its heads.  The output bias is kept on rank 0 only (it must be added once)."""
+    import numpy as np
+    hidden, vdim = w["wo"].shape
+    kdim = (w["wqkv"].shape[0] - vdim) // 2
+    if kdim % nhead or vdim % nhead:
+        raise ValueError("kdim and vdim must be multiples of nhead")
+    dqk, dv = kdim // nhead, vdim // nhead
+    h0, h1 = head_slice(nhead, world, rank)
+    rows = np.concatenate([np.arange(h0 * dqk, h1 * dqk),
+                           kdim + np.arange(h0 * dqk, h1 * dqk),
+                           2 * kdim + np.arange(h0 * dv, h1 * dv)])
+    out = {
+        "wqkv": np.ascontiguousarray(w["wqkv"][rows]),
+        "bqkv": np.ascontiguousarray(w["bqkv"][rows]),
+        "wo": np.ascontiguousarray(w["wo"][:, h0 * dv:h1 * dv]),
+        "bo": w["bo"] if rank == 0 else np.zeros_like(w["bo"]),
+        "nhead_local": h1 - h0, "dh_qk": dqk, "dh_v": dv,
+    }
+    return out

@@ -1,0 +1,75 @@
+"""Head-parallel encoder layer on two GPUs (one long sequence, one all-reduce per layer)
+against the unsharded oracle layer.  Needs two visible GPUs; skipped otherwise."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out_q):
+    try:
+        import torch
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        et = entry.load_package()
+        hidden, nhead, ff, seq = 768, 12, 3072, 1024
+        w = et.synth.encoder_layer_weights(41, 0, hidden, ff, std=0.03, bias_std=0.02, ln_noise=0.1)
+        x = et.synth.normal(41, 3, (seq, hidden), 1.0)
+        job = et.sharding.Job(rank=rank, world=world, device=dev)
+        layer = et.HeadParallelLayer(w, nhead, job, et.ACT_GELU, device=dev)
+        y = layer.forward(torch.from_numpy(x).to(dev), 1, seq)
+        torch.cuda.synchronize()
+        err = et.device_error()
+        if rank == 0:
+            out_q.put(("ok", y.float().cpu().numpy(), err))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        out_q.put(("error", repr(e), -1))
+        raise
+
+
+def test_head_parallel_layer_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    et = entry.load_package()
+    orc = entry.load_oracle()
+    orc.build()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world, port = 2, _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    kind, y, err = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert kind == "ok", y
+    assert err == 0
+    hidden, nhead, ff, seq = 768, 12, 3072, 1024
+    w = et.synth.encoder_layer_weights(41, 0, hidden, ff, std=0.03, bias_std=0.02, ln_noise=0.1)
+    x = et.synth.normal(41, 3, (seq, hidden), 1.0)
+    ref = orc.encoder_layer(x, w, 1, seq, nhead, 2, 0)
+    from conftest import assert_close
+    assert_close(y, ref, "head-parallel layer on 2 GPUs", rel_tol=8e-3, abs_tol=4e-2)

@@ -90,3 +90,75 @@ def test_two_gloo_ranks_shard_sequences_exactly(n_seq):
     assert same, "sharded and unsharded results differ"
     assert slow == 2.0
     assert thr == n_seq / 2.0
+
+
+def _hp_worker(rank: int, world: int, port: int, out_q):
+    """Head-parallel attention block with the oracle standing in for the kernels: the partial
+    sums of the ranks, all-reduced, must equal the unsharded block."""
+    try:
+        import torch
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        et = entry.load_package()
+        orc = entry.load_oracle()
+        orc.build()
+        hidden, nhead, ff, seq = 96, 6, 128, 80
+        kdim, vdim = 6 * 16, 6 * 32          # dh_qk 16, dh_v 32: Q/K narrower than V
+        w = et.synth.encoder_layer_weights(5, 0, hidden, ff, kdim=kdim, vdim=vdim, std=0.1,
+                                           bias_std=0.05)
+        x = et.synth.normal(5, 9, (seq, hidden), 1.0).astype(np.float32)
+        sl = et.sharding.head_shard_weights(w, nhead, world, rank)
+        nh, dqk, dv = sl["nhead_local"], sl["dh_qk"], sl["dh_v"]
+        qkv = orc.linear_dense(x, sl["wqkv"], sl["bqkv"], 0)
+        z = orc.attention(qkv[:, :nh * dqk], qkv[:, nh * dqk:2 * nh * dqk], qkv[:, 2 * nh * dqk:],
+                          1, seq, nh, dqk, dv, 1)
+        part = torch.from_numpy(orc.linear_dense(z, sl["wo"], sl["bo"], 0))
+        dist.all_reduce(part)
+        if rank == 0:
+            fq = orc.linear_dense(x, w["wqkv"], w["bqkv"], 0)
+            fz = orc.attention(fq[:, :kdim], fq[:, kdim:2 * kdim], fq[:, 2 * kdim:], 1, seq, nhead,
+                               kdim // nhead, vdim // nhead, 1)
+            full = orc.linear_dense(fz, w["wo"], w["bo"], 0)
+            err = float(np.abs(part.numpy() - full).max())
+            out_q.put(("ok", err))
+        dist.destroy_process_group()
+    except Exception as e:
+        out_q.put(("error", repr(e)))
+        raise
+
+
+def test_head_shards_cover_every_head_and_bias_once():
+    et = entry.load_package()
+    w = et.synth.encoder_layer_weights(5, 0, 64, 128, kdim=48, vdim=64)
+    for world in (1, 2, 3, 4, 8):
+        rows, cols, bias = [], [], np.zeros(64, np.float32)
+        for r in range(world):
+            sl = et.sharding.head_shard_weights(w, 4, world, r)
+            assert sl["wqkv"].shape[0] == sl["nhead_local"] * (2 * 12 + 16)
+            rows.append(sl["wqkv"].shape[0])
+            cols.append(sl["wo"].shape[1])
+            bias += sl["bo"].astype(np.float32)
+        assert sum(rows) == w["wqkv"].shape[0] and sum(cols) == w["wo"].shape[1]
+        assert np.array_equal(bias, w["bo"].astype(np.float32))
+
+
+def test_two_gloo_ranks_head_parallel_attention_block():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world, port = 2, _free_port()
+    procs = [ctx.Process(target=_hp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("a gloo rank did not finish")
+        assert p.exitcode == 0
+    kind, err = q.get(timeout=10)
+    assert kind == "ok", err
+    assert err < 1e-4, f"head-parallel partial sums differ from the full block by {err}"
