@@ -31,6 +31,21 @@ struct LayerBuffers {
 // output tiles and a long K leave most SMs idle unless K is split.
 int g_force_splits = 0;  // test hook: 0 = automatic
 
+// Split-K on CTA pairs: 256 x 256 pair tiles, as many K slices as SM pairs allow.  Returns 0
+// when the pair form does not apply.  Measured on B200 at BERT-base sizes the fp32 partial
+// sums (written by the GEMM, re-read by the LayerNorm) cost more than the better machine fill
+// gains, so this form only runs when the test hook asks for it (-2).
+int pick_pair_splits(int T, int hidden, int K) {
+    if (g_force_splits != -2) return 0;
+    if (T < 256 || hidden < 256) return 0;
+    const int pairs = (sm_count() > 0 ? sm_count() : 148) / 2;
+    const int tiles = ((T + 255) / 256) * ((hidden + 255) / 256);
+    int s = pairs / tiles;
+    s = s > kMaxSplits ? kMaxSplits : s;
+    while (s > 1 && (K / 64) / s < 8) --s;  // keep at least 8 K blocks per slice
+    return s >= 2 ? s : 0;
+}
+
 int pick_splits(int T, int hidden, int K) {
     if (g_force_splits > 0) return g_force_splits > kMaxSplits ? kMaxSplits : g_force_splits;
     const int tiles = ((T + 127) / 128) * ((hidden + 127) / 128);
@@ -102,7 +117,8 @@ int check_layer(const et_encoder_layer_t* L) {
 
 extern "C" {
 
-// Test hook: number of K slices of the FFN2 product (0 = automatic, 1 = no split).
+// Test hook: number of K slices of the FFN2 product (0 = automatic, 1 = no split, n > 1 = n
+// slices on single-CTA tiles, -2 = K slices on 256 x 256 CTA-pair tiles).
 void et_debug_force_ffn2_splits(int n) { et::g_force_splits = n; }
 
 size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq) {
@@ -140,9 +156,25 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                                         layer->hidden, s)) != ET_OK)
         return st;
     if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, s)) != ET_OK) return st;
-    const int splits = (layer->ffn2.format == ET_FMT_DENSE && layer->hidden <= 2048)
-                           ? et::pick_splits(T, layer->hidden, layer->ff)
-                           : 1;
+    const bool ffn2_splittable = layer->ffn2.format == ET_FMT_DENSE && layer->hidden <= 2048;
+    const int pair_splits =
+        ffn2_splittable ? et::pick_pair_splits(T, layer->hidden, layer->ff) : 0;
+    if (pair_splits > 1) {
+        // FFN2 as split-K partial sums on CTA pairs, reduced (with bias and residual) inside
+        // the LayerNorm
+        if ((st = et::launch_gemm_pair_splitk(b.f, layer->ff,
+                                              reinterpret_cast<const __half*>(layer->ffn2.weight),
+                                              layer->ff, b.part, T, layer->hidden, layer->ff,
+                                              pair_splits, s)) != ET_OK)
+            return st;
+        return et::launch_skip_layernorm_partials(
+            b.part, pair_splits, static_cast<size_t>(T) * layer->hidden,
+            reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
+            reinterpret_cast<const __half*>(layer->ln2_gamma),
+            reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
+            layer->hidden, s);
+    }
+    const int splits = ffn2_splittable ? et::pick_splits(T, layer->hidden, layer->ff) : 1;
     if (splits > 1) {
         // FFN2 as split-K partial sums, reduced (with bias and residual) inside the LayerNorm
         if ((st = et::launch_gemm_f16_splitk(b.f, layer->ff,

@@ -37,21 +37,25 @@ using namespace gemm;
 // accumulator, the staging tiles reuse the then idle ring; small enough (shared memory and
 // tensor memory) for two CTAs per SM, so that the next kernel's CTAs can start (programmatic
 // dependent launch) while this kernel's epilogues drain.
-template <int BN, int STAGES, bool PERSIST>
+// PARTIAL (single-tile form only): the tile index carries a K split; the epilogue writes
+// the fp32 partial sums of its K slice (no bias) through fp32 staging tiles in the idle ring.
+template <int BN, int STAGES, bool PERSIST, bool PARTIAL = false>
 struct PairCfg {
     static constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_HALF_BYTES;  // per CTA
     static constexpr int STAGING_NEED = BN * 256;  // 4 quadrants x BN/64 groups x 4 KB
-    static constexpr int STAGING_BYTES = PERSIST ? STAGING_NEED : 0;
+    static constexpr int STAGING_BYTES = (PERSIST && !PARTIAL) ? STAGING_NEED : 0;
     static constexpr int MISC_BYTES = 256 + 2 * 4 * BN;  // barriers + 2 x bias fp32
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + MISC_BYTES + 1024;
     static constexpr int NACC = PERSIST ? 2 : 1;
     static constexpr int TMEM_COLS = NACC * BN;
-    static constexpr int MIN_CTAS = PERSIST ? 1 : 2;
+    static constexpr int MIN_CTAS = (PERSIST || PARTIAL) ? 1 : 2;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
     static_assert(!PERSIST || SMEM_BYTES > 114 * 1024, "persistent form: one CTA per SM is assumed");
-    static_assert(PERSIST || SMEM_BYTES <= 113 * 1024, "single-tile form: two CTAs per SM");
-    static_assert(PERSIST || STAGES * STAGE_BYTES >= STAGING_NEED, "staging does not fit the ring");
+    static_assert(!PARTIAL || !PERSIST, "partial sums exist in the single-tile form only");
+    static_assert(PERSIST || PARTIAL || SMEM_BYTES <= 113 * 1024, "single-tile form: two CTAs per SM");
+    static_assert(PERSIST || STAGES * STAGE_BYTES >= (PARTIAL ? 2 : 1) * STAGING_NEED,
+                  "staging does not fit the ring");
     static_assert(TMEM_COLS * MIN_CTAS <= 512 && STAGES <= 8, "budget exceeded");
 };
 
@@ -59,12 +63,12 @@ struct PairTile {
     int n0, m0;
 };
 
-template <int BN, int STAGES, bool PERSIST>
+template <int BN, int STAGES, bool PERSIST, bool PARTIAL>
 __global__ void __cluster_dims__(2, 1, 1)
-__launch_bounds__(GEMM_THREADS, (PairCfg<BN, STAGES, PERSIST>::MIN_CTAS))
+__launch_bounds__(GEMM_THREADS, (PairCfg<BN, STAGES, PERSIST, PARTIAL>::MIN_CTAS))
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmY, const GemmArgs g) {
-    using Cfg = PairCfg<BN, STAGES, PERSIST>;
+    using Cfg = PairCfg<BN, STAGES, PERSIST, PARTIAL>;
     const int M = g.M, N = g.N;
     int* err_word = g.err_word;
 
@@ -89,13 +93,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int tiles_n = (N + BN - 1) / BN;
     const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
-    const int total_tiles = tiles_n * tiles_m;
-    const int num_kb = (g.K + BK - 1) / BK;
+    const int tiles_mn = tiles_n * tiles_m;
+    const int total_tiles = tiles_mn * (PARTIAL ? g.nz : 1);
+    const int kb_total = (g.K + BK - 1) / BK;
+    // K blocks of this CTA's tile(s): everything, or (PARTIAL: one tile per pair) the split's slice
+    int kb_begin = 0, num_kb = kb_total;
+    const int split = PARTIAL ? pair / tiles_mn : 0;
+    if (PARTIAL) {
+        kb_begin = split * g.kb_per_split;
+        int kb_end = kb_begin + g.kb_per_split < kb_total ? kb_begin + g.kb_per_split : kb_total;
+        if (kb_end < kb_begin) kb_end = kb_begin;
+        num_kb = kb_end - kb_begin;
+    }
 
     auto decode = [&](int t) {
         PairTile c;
-        c.n0 = (t % tiles_n) * BN;
-        c.m0 = (t / tiles_n) * 2 * BM + static_cast<int>(rank) * BM;  // this CTA's rows
+        const int tt = PARTIAL ? t % tiles_mn : t;
+        c.n0 = (tt % tiles_n) * BN;
+        c.m0 = (tt / tiles_n) * 2 * BM + static_cast<int>(rank) * BM;  // this CTA's rows
         return c;
     };
 
@@ -146,14 +161,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     for (int i = 0; i < pre; ++i) {
                         if (rank == 0) mbar_arrive_expect_tx(&full_bar[i], 2 * Cfg::STAGE_BYTES);
                         tma_load_2d_pair(sB + i * Cfg::B_HALF_BYTES, &tmB,
-                                         map_to_cta(smem_u32(&full_bar[i]), 0), i * BK, nb0);
+                                         map_to_cta(smem_u32(&full_bar[i]), 0), (kb_begin + i) * BK,
+                                         nb0);
                     }
                     ET_TL(3);
                     pdl_wait();
                     ET_TL(4);
                     for (int i = 0; i < pre; ++i)
                         tma_load_2d_pair(sA + i * A_STAGE_BYTES, &tmA,
-                                         map_to_cta(smem_u32(&full_bar[i]), 0), i * BK, c.m0);
+                                         map_to_cta(smem_u32(&full_bar[i]), 0), (kb_begin + i) * BK,
+                                         c.m0);
                     issued = pre;
                     s = pre % STAGES;
                     ph = (pre / STAGES) & 1;
@@ -167,8 +184,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
                     const uint32_t lb = map_to_cta(smem_u32(&full_bar[s]), 0);
-                    tma_load_2d_pair(sA + s * A_STAGE_BYTES, &tmA, lb, i * BK, c.m0);
-                    tma_load_2d_pair(sB + s * Cfg::B_HALF_BYTES, &tmB, lb, i * BK, nb0);
+                    tma_load_2d_pair(sA + s * A_STAGE_BYTES, &tmA, lb, (kb_begin + i) * BK, c.m0);
+                    tma_load_2d_pair(sB + s * Cfg::B_HALF_BYTES, &tmB, lb, (kb_begin + i) * BK, nb0);
                     ++issued;
                     if (++s == STAGES) {
                         s = 0;
@@ -244,7 +261,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             float* tb = s_bias + buf * BN;
             for (int i = et; i < BN; i += EPI_THREADS) {
                 const int n = c.n0 + i;
-                tb[i] = (g.bias != nullptr && n < N) ? __half2float(__ldg(g.bias + n)) : 0.f;
+                tb[i] = (!PARTIAL && g.bias != nullptr && n < N) ? __half2float(__ldg(g.bias + n)) : 0.f;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             if (tile_iter == 0) pdl_wait();  // outputs may still be read by the previous kernel
@@ -267,6 +284,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (((ch >> 1) & 1) == half && c.n0 + ch * 32 < N) my_chunks[n_my++] = ch;
 
             auto finish_chunk = [&](int ch, const uint32_t (&r)[32]) {
+                if (PARTIAL) {
+                    // 32 rows x 32 fp32 columns: one swizzled 4 KB staging tile, one TMA store
+                    uint8_t* tile = sStage + (q * NCHUNK + ch) * 4096;
+                    uint8_t* srow = tile + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(srow + ((j ^ (lane & 7)) * 16)) =
+                            make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && c.m0 + q * 32 < M)
+                        tma_store_3d(&tmY, tile, c.n0 + ch * 32, c.m0 + q * 32, split);
+                    return;
+                }
                 uint8_t* tile = sStage + (q * (BN / 64) + (ch >> 1)) * 4096;
                 uint8_t* srow = tile + lane * 128;
                 const float* b32 = tb + ch * 32;
@@ -285,7 +316,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             };
 
             uint32_t ra[32], rb[32];
-            if (n_my > 0) {
+            if (num_kb == 0) {  // an empty K slice: no product ran, the partial sum is zero
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ra[j] = 0u;
+                for (int i = 0; i < n_my; ++i) finish_chunk(my_chunks[i], ra);
+            } else if (n_my > 0) {
                 tmem_ld32(lane_addr + my_chunks[0] * 32, ra);
 #pragma unroll 1
                 for (int i = 0; i < n_my; i += 2) {
@@ -329,11 +364,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 32) ET_TL(12);
 }
 
-template <int BN, int STAGES, bool PERSIST>
+template <int BN, int STAGES, bool PERSIST, bool PARTIAL = false>
 int launch_pair_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
                     const GemmArgs& args, cudaStream_t stream) {
-    using Cfg = PairCfg<BN, STAGES, PERSIST>;
-    auto kern = gemm_pair_kernel<BN, STAGES, PERSIST>;
+    using Cfg = PairCfg<BN, STAGES, PERSIST, PARTIAL>;
+    auto kern = gemm_pair_kernel<BN, STAGES, PERSIST, PARTIAL>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -343,7 +378,8 @@ int launch_pair_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtens
             return ET_ERR_CUDA;
         attr_set[dev] = true;
     }
-    const long tiles = static_cast<long>((args.N + BN - 1) / BN) * ((args.M + 2 * BM - 1) / (2 * BM));
+    const long tiles = static_cast<long>((args.N + BN - 1) / BN) *
+                       ((args.M + 2 * BM - 1) / (2 * BM)) * (PARTIAL ? args.nz : 1);
     const int sms = sm_count() > 0 ? sm_count() : 148;
     const long pairs = (!PERSIST || tiles < sms / 2) ? tiles : sms / 2;
     return launch_kernel(kern, dim3(static_cast<unsigned>(2 * pairs)), dim3(GEMM_THREADS),
@@ -406,6 +442,52 @@ int launch_gemm_pair_f16(const __half* X, int ldx, const __half* W, int ldw, con
                        : launch_pair_cfg<256, 3, false>(tmA, tmB, tmY, a, stream);
     return persist ? launch_pair_cfg<128, 6, true>(tmA, tmB, tmY, a, stream)
                    : launch_pair_cfg<128, 4, false>(tmA, tmB, tmY, a, stream);
+}
+
+}  // namespace et
+
+namespace et {
+
+// P[s][m, n] = sum over the s-th slice of K of X[m, k] W[n, k] (fp32, no bias) on 256 x 256
+// pair tiles, one tile and slice per CTA pair: for products with few output tiles and a long K,
+// where splitting K is what fills the machine.
+int launch_gemm_pair_splitk(const __half* X, int ldx, const __half* W, int ldw, float* P, int M,
+                            int N, int K, int splits, cudaStream_t stream) {
+    if (!X || !W || !P || M <= 0 || N <= 0 || K <= 0 || splits <= 0) return ET_ERR_INVALID_ARG;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(P)) return ET_ERR_ALIGNMENT;
+    if (ldx % 8 || ldw % 8 || K % 8 || N % 8) return ET_ERR_SHAPE;
+    if (!device_error_word()) return ET_ERR_NO_DEVICE;
+    CUtensorMap tmA, tmB, tmY;
+    int st;
+    if ((st = gemm::encode_operand(&tmA, X, ldx, M, K, gemm::BM)) != ET_OK) return st;
+    if ((st = gemm::encode_operand(&tmB, W, ldw, N, K, 128)) != ET_OK) return st;
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                                  static_cast<uint64_t>(splits)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(N) * 4,
+                                     static_cast<uint64_t>(N) * 4 * static_cast<uint64_t>(M)};
+        const uint32_t box[3] = {32, 32, 1};
+        st = make_tensor_map_f32(&tmY, P, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
+    }
+    const int kb_total = (K + gemm::BK - 1) / gemm::BK;
+    gemm::GemmArgs a;
+    a.Y = P;
+    a.bias = nullptr;
+    a.col_map = nullptr;
+    a.ldy = N;
+    a.scatter = 0;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.act = ET_ACT_NONE;
+    a.grp_rows = 0;
+    a.grp_stride = 0;
+    a.out_mode = gemm::OUT_PARTIAL_F32;
+    a.kb_per_split = (kb_total + splits - 1) / splits;
+    a.nz = splits;
+    a.err_word = device_error_word();
+    return launch_pair_cfg<256, 6, false, true>(tmA, tmB, tmY, a, stream);
 }
 
 }  // namespace et

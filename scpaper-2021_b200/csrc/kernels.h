@@ -18,6 +18,10 @@ int launch_gemm_pair_f16(const __half* X, int ldx, const __half* W, int ldw, con
                          __half* Y, int ldy, int M, int N, int K, int act, int bn,
                          cudaStream_t stream);
 
+// fp32 split-K partial sums on 256 x 256 pair tiles; see gemm_pair.cu.
+int launch_gemm_pair_splitk(const __half* X, int ldx, const __half* W, int ldw, float* P, int M,
+                            int N, int K, int splits, cudaStream_t stream);
+
 // Grouped GEMM over weights stored [groups][K, N] (N contiguous); see gemm_dense.cu.
 int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const __half* bias,
                                __half* Y, int M, int N, int K, int groups, int grp_rows,

@@ -53,6 +53,22 @@ def test_bert_base_layer_dense_and_tile(et, orc, cuda):
                  "bert-base tile 80%, plan-time choice")
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, -2])
+def test_ffn2_split_k_forms(et, orc, cuda, splits):
+    """FFN2 as split-K partial sums reduced inside the LayerNorm: single-CTA slices (2, 3) and
+    CTA-pair slices (-2) against the unsplit layer (1) and the oracle."""
+    import ctypes
+    batch, seq, hidden, nhead, ff = 4, 128, 768, 12, 3072
+    w = et.synth.encoder_layer_weights(2021, 2, hidden, ff, bias_std=0.02, ln_noise=0.05)
+    x = et.synth.normal(2021, 94, (batch * seq, hidden), 1.0)
+    try:
+        et.lib().et_debug_force_ffn2_splits(ctypes.c_int(splits))
+        y = _run(et, cuda, [w], x, batch, seq, nhead)
+    finally:
+        et.lib().et_debug_force_ffn2_splits(ctypes.c_int(0))
+    assert_close(y, _oracle_stack(orc, [w], x, batch, seq, nhead), f"ffn2 splits {splits}")
+
+
 def test_stack_of_three_layers_with_padding(et, orc, cuda):
     batch, seq, hidden, nhead, ff = 3, 96, 256, 4, 512
     ws = [et.synth.encoder_layer_weights(7, l, hidden, ff, std=0.05, bias_std=0.02, ln_noise=0.1)
