@@ -533,3 +533,71 @@ class EncoderStack:
             done.record(self.streams[g - 1])
             main.wait_event(done)
         return self.buf[(len(self.layers) - 1) & 1]
+
+
+class HostPipeline:
+    """Serving loop over an EncoderStack for callers whose batches live in (pinned) host memory:
+    `submit(x_host, y_host)` queues host-to-device copy, the stack (replayed from a CUDA graph)
+    and device-to-host copy of one batch on three streams; with `depth` >= 2 input / output
+    slots the copies of neighbouring batches overlap the compute of the current one.  `drain()`
+    waits for everything queued.  Results land in the caller's `y_host` of each submit."""
+
+    def __init__(self, stack: "EncoderStack", depth: int = 2, mask_kind=MASK_NONE, mask=None,
+                 valid_len=None, use_graph: bool = True):
+        import torch
+        dev = stack.buf[0].device
+        self.stack, self.depth = stack, max(1, depth)
+        shape = tuple(stack.buf[0].shape)
+        self.x_dev = [torch.empty(shape, dtype=torch.float16, device=dev) for _ in range(self.depth)]
+        self.y_dev = [torch.empty(shape, dtype=torch.float16, device=dev) for _ in range(self.depth)]
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        mk = lambda: [torch.cuda.Event() for _ in range(self.depth)]
+        self.ev_in, self.ev_run, self.ev_out = mk(), mk(), mk()
+        self.count = 0
+        self.kernels_per_step = 0
+        self.graphs = []
+
+        def run(slot):
+            out = stack.forward(self.x_dev[slot], mask_kind, mask, valid_len)
+            self.y_dev[slot].copy_(out)  # frees the stack's own buffer for the next batch
+
+        with torch.cuda.stream(self.s_run):
+            for slot in range(self.depth):
+                run(slot)  # warm: sets kernel attributes before capture
+            self.s_run.synchronize()
+            for slot in range(self.depth):
+                if use_graph:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.s_run):
+                        run(slot)
+                    self.graphs.append(g.replay)
+                else:
+                    self.graphs.append(lambda slot=slot: run(slot))
+        torch.cuda.synchronize(dev)
+
+    def submit(self, x_host, y_host) -> None:
+        import torch
+        slot = self.count % self.depth
+        reuse = self.count >= self.depth
+        with torch.cuda.stream(self.s_in):
+            if reuse:
+                self.s_in.wait_event(self.ev_run[slot])   # the stack has consumed this input slot
+            self.x_dev[slot].copy_(x_host, non_blocking=True)
+            self.ev_in[slot].record(self.s_in)
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(self.ev_in[slot])
+            if reuse:
+                self.s_run.wait_event(self.ev_out[slot])  # its previous result has left the device
+            self.graphs[slot]()
+            self.ev_run[slot].record(self.s_run)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_run[slot])
+            y_host.copy_(self.y_dev[slot], non_blocking=True)
+            self.ev_out[slot].record(self.s_out)
+        self.count += 1
+
+    def drain(self) -> None:
+        self.s_out.synchronize()
+        self.s_run.synchronize()
+        self.s_in.synchronize()
+

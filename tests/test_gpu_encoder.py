@@ -141,3 +141,25 @@ def test_mixed_format_layer_bert_large_shapes(et, orc, cuda):
     assert et.device_error() == 0
     assert_close(a3.float().cpu().numpy(), a2.float().cpu().numpy(), "row scatter + col gather FFN",
                  rel_tol=2e-3, abs_tol=1e-2)
+
+
+def test_host_pipeline_matches_resident_forward(et, cuda):
+    """The serving loop (pinned host batches in and out, copies overlapped with compute over
+    two slots) returns, for every batch of a stream of different batches, exactly what the
+    resident forward returns."""
+    import torch
+    batch, seq, hidden, nhead, ff = 2, 64, 256, 4, 512
+    ws = [et.synth.encoder_layer_weights(9, l, hidden, ff, std=0.05) for l in range(2)]
+    layers = [et.EncoderLayer(w, nhead, et.ACT_GELU, device=cuda) for w in ws]
+    stack = et.EncoderStack(layers, batch, seq, device=cuda)
+    xs = [torch.from_numpy(et.synth.normal(9, 200 + i, (batch * seq, hidden), 1.0)).pin_memory()
+          for i in range(5)]
+    want = [stack.forward(x.to(cuda)).clone().cpu() for x in xs]
+    pipe = et.HostPipeline(stack, depth=2)
+    ys = [torch.empty_like(x).pin_memory() for x in xs]
+    for x, y in zip(xs, ys):
+        pipe.submit(x, y)
+    pipe.drain()
+    assert et.device_error() == 0
+    for i, (y, w) in enumerate(zip(ys, want)):
+        assert torch.equal(y, w), f"batch {i} differs"
