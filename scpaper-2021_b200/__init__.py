@@ -10,7 +10,7 @@ import ctypes
 import os
 from ctypes import c_float, c_int, c_size_t, c_void_p
 
-from . import sharding, synth  # noqa: F401
+from . import sharding, synth, weights  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libet_b200.so")
