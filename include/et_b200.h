@@ -221,6 +221,19 @@ int et_attention_fwd(const et_half* Q, const et_half* K, const et_half* V, et_ha
                      int mask_kind, const et_half* mask, const int32_t* valid_len, float scale,
                      et_stream stream);
 
+/* Fused Q/K/V projection + self-attention for short sequences: Z[b, :, head h] =
+ * softmax(Q_h K_h^T * scale + mask) V_h with [Q | K | V] = X Wqkv^T + bqkv computed inside the
+ * same kernel (one CTA per sequence and head; the projected activations never reach memory).
+ * Wqkv: [2 * kdim + vdim, hidden] with output features ordered Q | K | V, bqkv may be null, Z:
+ * [batch * seq, vdim].  Requires seq <= 128 and kdim = vdim = 64 * nhead (ET_ERR_SHAPE
+ * otherwise: use et_linear_dense_fwd + et_attention_fwd).  Masks as et_attention_fwd.
+ * Replaces the fused-QKV Linear + attention launch of Attention<cfg, single>::forward
+ * (Attention/Attention.h:204-266). */
+int et_qkv_attention_fwd(const et_half* X, const et_half* Wqkv, const et_half* bqkv, et_half* Z,
+                         int batch, int seq, int hidden, int nhead, int kdim, int vdim,
+                         int mask_kind, const et_half* mask, const int32_t* valid_len, float scale,
+                         et_stream stream);
+
 /* Attention whose V is column-compressed: Vc[T, nnz_col] holds the value features
  * col_id[0..nnz_col) (ascending); head_ptr[h]..head_ptr[h+1] delimits head h's entries
  * (mat_type/col_mat/col_mat.cu:34-58).  Z[T, nhead*dh_v] is written in full: pruned

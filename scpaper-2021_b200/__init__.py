@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "et_linear_1x16_fwd",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
     "et_validate_csr", "et_skip_layernorm_fwd", "et_layernorm_fwd", "et_act_fwd",
-    "et_bias_add_fwd", "et_attention_fwd", "et_attention_pruned_v_fwd",
+    "et_bias_add_fwd", "et_attention_fwd", "et_qkv_attention_fwd", "et_attention_pruned_v_fwd",
     "et_attention_fuse_o_fwd", "et_fused_vo_attention_fwd", "et_linear_vo_fwd",
     "et_encoder_layer_workspace_bytes", "et_encoder_layer_fwd",
 ]
@@ -297,6 +297,18 @@ def attention(q, k, v, batch, seq, nhead, dh_qk, dh_v, mask_kind=MASK_NONE, mask
                                  c_int(nhead), c_int(dh_qk), c_int(dh_v), c_int(ldq), c_int(ldk),
                                  c_int(ldv), c_int(nhead * dh_v), c_int(mask_kind), _p(mask),
                                  _p(valid_len), c_float(scale), _stream()), "et_attention_fwd")
+    return z
+
+
+def qkv_attention(x, wqkv, bqkv, batch, seq, nhead, kdim, vdim, mask_kind=MASK_NONE, mask=None,
+                  valid_len=None, scale=None):
+    """Fused Q/K/V projection + attention (seq <= 128, 64-wide heads)."""
+    z = _empty((batch * seq, vdim), x)
+    scale = (1.0 / (kdim // nhead) ** 0.5) if scale is None else scale
+    check(lib().et_qkv_attention_fwd(_p(x), _p(wqkv), _p(bqkv), _p(z), c_int(batch), c_int(seq),
+                                     c_int(x.shape[1]), c_int(nhead), c_int(kdim), c_int(vdim),
+                                     c_int(mask_kind), _p(mask), _p(valid_len), c_float(scale),
+                                     _stream()), "et_qkv_attention_fwd")
     return z
 
 

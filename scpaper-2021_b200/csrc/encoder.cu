@@ -30,6 +30,7 @@ struct LayerBuffers {
 // Number of K slices for a dense [T, K] x [hidden, K]^T product feeding a LayerNorm: few
 // output tiles and a long K leave most SMs idle unless K is split.
 int g_force_splits = 0;  // test hook: 0 = automatic
+bool g_qkv_fusion = true;  // test hook: false = always the separate projection + attention
 
 // Split-K on CTA pairs: 256 x 256 pair tiles, as many K slices as SM pairs allow.  Returns 0
 // when the pair form does not apply.  Measured on B200 at BERT-base sizes the fp32 partial
@@ -121,6 +122,9 @@ extern "C" {
 // slices on single-CTA tiles, -2 = K slices on 256 x 256 CTA-pair tiles).
 void et_debug_force_ffn2_splits(int n) { et::g_force_splits = n; }
 
+// Test hook: 0 = never fuse the Q/K/V projection into the attention kernel.
+void et_debug_set_qkv_fusion(int on) { et::g_qkv_fusion = on != 0; }
+
 size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq) {
     if (et::check_layer(layer) != ET_OK || batch <= 0 || seq <= 0) return 0;
     return et::carve(layer, batch, seq, nullptr).total;
@@ -144,12 +148,26 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
     const int ldqkv = 2 * layer->kdim + layer->vdim;
     const int dh_qk = layer->kdim / layer->nhead, dh_v = layer->vdim / layer->nhead;
 
-    if ((st = et::run_linear(layer->qkv, xin, b.qkv, T, ET_ACT_NONE, s)) != ET_OK) return st;
-    if ((st = et::launch_attention(b.qkv, b.qkv + layer->kdim, b.qkv + 2 * layer->kdim, b.z, batch,
-                                   seq, layer->nhead, dh_qk, dh_v, ldqkv, ldqkv, ldqkv, layer->vdim,
-                                   mask_kind, reinterpret_cast<const __half*>(mask), valid_len,
-                                   1.0f / sqrtf(static_cast<float>(dh_qk)), s)) != ET_OK)
-        return st;
+    if (et::g_qkv_fusion && layer->qkv.format == ET_FMT_DENSE &&
+        et::qkv_attention_applies(seq, layer->nhead, layer->kdim, layer->vdim)) {
+        // short sequences, 64-wide heads: projection and attention in one kernel, the projected
+        // Q / K / V never leave the SM
+        if ((st = et::launch_qkv_attention(
+                 xin, reinterpret_cast<const __half*>(layer->qkv.weight),
+                 reinterpret_cast<const __half*>(layer->qkv.bias), b.z, batch, seq, layer->hidden,
+                 layer->nhead, layer->kdim, layer->vdim, layer->vdim, mask_kind,
+                 reinterpret_cast<const __half*>(mask), valid_len,
+                 1.0f / sqrtf(static_cast<float>(dh_qk)), s)) != ET_OK)
+            return st;
+    } else {
+        if ((st = et::run_linear(layer->qkv, xin, b.qkv, T, ET_ACT_NONE, s)) != ET_OK) return st;
+        if ((st = et::launch_attention(b.qkv, b.qkv + layer->kdim, b.qkv + 2 * layer->kdim, b.z,
+                                       batch, seq, layer->nhead, dh_qk, dh_v, ldqkv, ldqkv, ldqkv,
+                                       layer->vdim, mask_kind, reinterpret_cast<const __half*>(mask),
+                                       valid_len, 1.0f / sqrtf(static_cast<float>(dh_qk)), s)) !=
+            ET_OK)
+            return st;
+    }
     if ((st = et::run_linear(layer->o, b.z, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
     if ((st = et::launch_skip_layernorm(b.a, xin, reinterpret_cast<const __half*>(layer->ln1_gamma),
                                         reinterpret_cast<const __half*>(layer->ln1_beta), b.y, T,

@@ -18,6 +18,13 @@ int launch_gemm_pair_f16(const __half* X, int ldx, const __half* W, int ldw, con
                          __half* Y, int ldy, int M, int N, int K, int act, int bn,
                          cudaStream_t stream);
 
+// Fused Q/K/V projection + attention for seq <= 128 and 64-wide heads; see qkv_attention.cu.
+bool qkv_attention_applies(int seq, int nhead, int kdim, int vdim);
+int launch_qkv_attention(const __half* X, const __half* Wqkv, const __half* bqkv, __half* Z,
+                         int batch, int seq, int hidden, int nhead, int kdim, int vdim, int ldz,
+                         int mask_kind, const __half* mask, const int* valid_len, float scale,
+                         cudaStream_t stream);
+
 // fp32 split-K partial sums on 256 x 256 pair tiles; see gemm_pair.cu.
 int launch_gemm_pair_splitk(const __half* X, int ldx, const __half* W, int ldw, float* P, int M,
                             int N, int K, int splits, cudaStream_t stream);

@@ -187,3 +187,51 @@ def test_attention_fuse_o(et, orc, cuda):
     assert et.device_error() == 0
     z = orc.round_fp16(orc.attention(q, k, v, batch, seq, nhead, dh, dh, 1))
     assert_close(out.float().cpu().numpy(), orc.linear_dense(z, wo, bo), "attention + tile O")
+
+
+@pytest.mark.parametrize("batch,seq,hidden,nhead", [
+    (2, 128, 768, 12), (3, 100, 256, 4), (1, 16, 64, 1), (16, 128, 768, 12), (2, 72, 208, 2),
+])
+@pytest.mark.parametrize("mask_kind", [0, 1, 2, 3])
+def test_qkv_attention_fused(et, orc, cuda, batch, seq, hidden, nhead, mask_kind):
+    """Projection + attention in one kernel against the oracle's Linear followed by its
+    attention, for every mask kind, ragged sequence lengths and hidden sizes that are not a
+    multiple of the 64-feature K block."""
+    import torch
+    T, kdim = batch * seq, nhead * 64
+    x = et.synth.normal(600 + seq, 1, (T, hidden), 1.0)
+    w = et.synth.normal(600 + seq, 2, (3 * kdim, hidden), 0.06)
+    bq = et.synth.normal(600 + seq, 3, (3 * kdim,), 0.1)
+    vl = np.array([(37 * i + 5) % seq + 1 for i in range(batch)], dtype=np.int32)
+    if batch > 1:
+        vl[1] = seq
+    mask = None
+    if mask_kind == 3:
+        mask = np.where(et.synth.normal(600 + seq, 4, (seq, seq), 1.0).astype(np.float32) > 0.8,
+                        -np.inf, 0.0).astype(np.float16)
+        mask[np.arange(seq), np.arange(seq)] = 0
+    d = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    z = et.qkv_attention(d(x), d(w), d(bq), batch, seq, nhead, kdim, kdim, mask_kind, d(mask),
+                         d(vl) if mask_kind == 2 else None)
+    assert et.device_error() == 0
+    qkv = orc.round_fp16(orc.linear_dense(x, w, bq, 0))
+    ref = orc.attention(qkv[:, :kdim], qkv[:, kdim:2 * kdim], qkv[:, 2 * kdim:], batch, seq, nhead,
+                        64, 64, mask_kind, mask, vl if mask_kind == 2 else None)
+    assert_close(z.float().cpu().numpy(), ref, f"fused qkv attention b{batch} s{seq} m{mask_kind}")
+    # the separate kernels give the same result up to rounding
+    q2 = et.linear_dense(d(x), d(w), d(bq))
+    z2 = et.attention(q2[:, :kdim], q2[:, kdim:2 * kdim], q2[:, 2 * kdim:], batch, seq, nhead, 64,
+                      64, mask_kind, d(mask), d(vl) if mask_kind == 2 else None)
+    assert_close(z.float().cpu().numpy(), z2.float().cpu().numpy(), "fused vs separate kernels",
+                 rel_tol=2e-3, abs_tol=4e-3)
+
+
+def test_qkv_attention_rejects_other_shapes(et, cuda):
+    import torch
+    x = torch.zeros((256, 64), dtype=torch.float16, device=cuda)
+    w = torch.zeros((192, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(et.EtError):
+        et.qkv_attention(x, w, None, 1, 256, 1, 64, 64)       # seq > 128
+    w2 = torch.zeros((96, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(et.EtError):
+        et.qkv_attention(x[:128], w2, None, 1, 128, 1, 32, 32)  # 32-wide head
