@@ -31,7 +31,10 @@ WORKLOAD = ("BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, seq 128
             "all-ones mask")
 HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
 SEED = 2021
-KERNELS_PER_LAYER = 7  # QKV, attention, O, skip-LN, FFN1(+GELU), FFN2, skip-LN
+KERNELS_PER_LAYER = 6  # QKV + attention (fused), O, skip-LN, FFN1(+GELU), FFN2, skip-LN
+# dram__bytes_read + dram__bytes_write of one FFN1 launch from the ncu capture summarised in
+# profiles/ncu_full_one_layer_bert_base_b16.md (cold operands; the result stays in L2)
+FFN1_DRAM_TRAFFIC_BYTES = 7944704
 
 
 def flops_per_sequence(keep_lin: float = 1.0) -> float:
@@ -366,6 +369,17 @@ def main():
                                                         64, 64, out=z[i]) for i in range(NSETS)])
             per_kernel["attention"] = {"us": sec * 1e6,
                                        "tflops": 4.0 * BATCH * SEQ * SEQ * HIDDEN / sec * 1e-12}
+            xs = [torch.from_numpy(et.synth.normal(1, 10 + i, (T, HIDDEN), 1.0)).to(dev)
+                  for i in range(NSETS)]
+            wq = [torch.from_numpy(et.synth.normal(1, 40 + i, (3 * HIDDEN, HIDDEN), 0.02)).to(dev)
+                  for i in range(NSETS)]
+            bqz = torch.zeros(3 * HIDDEN, dtype=torch.float16, device=dev)
+            sec = time_kernel([lambda i=i: et.qkv_attention(xs[i], wq[i], bqz, BATCH, SEQ, NHEAD,
+                                                            HIDDEN, HIDDEN) for i in range(NSETS)])
+            per_kernel["qkv_attention_fused"] = {
+                "us": sec * 1e6,
+                "tflops": (2.0 * T * HIDDEN * 3 * HIDDEN + 4.0 * BATCH * SEQ * SEQ * HIDDEN) / sec * 1e-12}
+            del xs, wq
             a = [torch.from_numpy(et.synth.normal(1, 90 + i, (T, HIDDEN), 1.0)).to(dev)
                  for i in range(4 * NSETS)]
             o = [torch.empty((T, HIDDEN), dtype=torch.float16, device=dev) for _ in range(4 * NSETS)]
@@ -380,7 +394,9 @@ def main():
         line["roofline"] = {"bound": "tensor", "kernel": "gemm_f16_kernel (FFN1 + GELU, "
                             f"[{T}x768]x[3072x768]^T)", "achieved": k["tflops"],
                             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": k["tflops"] / peaks["bf16_tflops"], "traffic": None,
+                            "frac": k["tflops"] / peaks["bf16_tflops"],
+                            "traffic": FFN1_DRAM_TRAFFIC_BYTES,
+                            "algorithmic_bytes": 2 * (T * HIDDEN + FF * HIDDEN + T * FF),
                             "peak_source": peaks["source"] + " (burst, kernel timed alone)"}
         line["kernels"] = per_kernel
 
