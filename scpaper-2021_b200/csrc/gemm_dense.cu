@@ -20,6 +20,15 @@
 
 namespace et {
 
+// Bring-up aid: with -DET_TIMELINE every CTA records clock64() at a few points of its life.
+#ifdef ET_TIMELINE
+__device__ long long et_gemm_timeline[4096 * 16];
+#define ET_TL(slot) \
+    do { if (blockIdx.x < 4096) et_gemm_timeline[blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+#else
+#define ET_TL(slot) ((void)0)
+#endif
+
 namespace {
 
 using namespace gemm;
@@ -57,7 +66,11 @@ struct TileCoord {
 // B_MN == false: W is [N, K] with K contiguous (the Linear weight layout).
 // B_MN == true : W is [groups][K, N] with N contiguous; its tiles are consumed in place
 //                as MN-major operands (64-column atoms of 64 K-rows, 8 KB each).
-template <int BN, int STAGES, bool PERSIST, bool B_MN>
+// EPI: 0 = every output mode and activation chosen at run time (index-list, grouped and
+// partial-sum epilogues); 1 + act = the fp16 tile store with that activation compiled in.  The
+// specialised form matters: with all variants inlined behind run-time branches the same
+// staging code ran three times slower.
+template <int BN, int STAGES, bool PERSIST, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, STAGES, PERSIST>::MIN_CTAS))
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmY, const GemmArgs g) {
@@ -109,6 +122,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     };
 
     if (threadIdx.x == 0) {
+        ET_TL(0);
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
         for (int s = 0; s < STAGES; ++s) {
@@ -130,6 +144,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) ET_TL(1);
     pdl_launch_dependents();  // the next kernel may begin its own set-up
 
     if (warp == 0) {
@@ -159,6 +174,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         load_b(c, c.kb_begin + i, i);
                     }
                     pdl_wait();
+                    ET_TL(2);
                     for (int i = 0; i < pre; ++i)
                         tma_load_2d(sA + i * A_STAGE_BYTES, &tmA, &full_bar[i], (c.kb_begin + i) * BK,
                                     c.m0);
@@ -215,6 +231,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         break;
                     }
                     tc_fence_after_sync();
+                    if (it == 0) ET_TL(3);
                     const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
                     const uint32_t b_addr = smem_u32(sB + s * Cfg::B_STAGE_BYTES);
 #pragma unroll
@@ -230,6 +247,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     mma_commit(&empty_bar[s]);
                 }
                 if (ok) mma_commit(&acc_full[buf]);
+                ET_TL(tile_iter == 0 ? 4 : 5);
             }
         }
     } else {
@@ -268,15 +286,18 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) continue;
             tc_fence_after_sync();
+            if (threadIdx.x == 64) ET_TL(tile_iter == 0 ? 7 : 8);
             // the TMA stores of this warp's previous tile must have read the staging tiles
-            if (lane == 0) tma_store_wait_read();
-            __syncwarp();
+            if (tile_iter > 0) {
+                if (lane == 0) tma_store_wait_read();
+                __syncwarp();
+            }
 
             const int row = c.m0 + q * 32 + lane;
             const uint32_t lane_addr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
             // This warp's share of the tile's 32-column chunks: for the fp16 tile store whole
             // 64-column groups alternate between the quadrant's two warps, otherwise chunks do.
-            const bool by_group = g.out_mode == OUT_TILE_F16;
+            const bool by_group = EPI != 0 || g.out_mode == OUT_TILE_F16;
             int my_chunks[NCHUNK];
             int n_my = 0;
 #pragma unroll
@@ -287,6 +308,17 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
 
             auto finish_chunk = [&](int ch, const uint32_t (&r)[32]) {
+                if (EPI != 0) {
+                    uint8_t* tile = sStage + (q * (BN / 64) + (ch >> 1)) * 4096;
+                    stage_f16_chunk<EPI - 1>(r, tb + ch * 32, tile + lane * 128, ch & 1, lane);
+                    if ((ch & 1) || c.n0 + ch * 32 + 32 >= N) {  // the 64-column group is complete
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && c.m0 + q * 32 < M)
+                            tma_store_2d(&tmY, tile, c.n0 + (ch >> 1) * 64, c.m0 + q * 32);
+                    }
+                    return;
+                }
                 if (g.out_mode == OUT_TILE_F16) {
                     uint8_t* tile = sStage + (q * (BN / 64) + (ch >> 1)) * 4096;
                     uint8_t* srow = tile + lane * 128;
@@ -346,12 +378,34 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
                 for (int i = 0; i < n_my; i += 2) {
                     tmem_ld_wait_regs(ra);
+#ifdef ET_TIMELINE
+                    const long long tl_a = clock64();
+#endif
                     if (i + 1 < n_my) tmem_ld32(lane_addr + my_chunks[i + 1] * 32, rb);
+#ifdef ET_TIMELINE
+                    const long long tl_b = clock64();
+#endif
                     finish_chunk(my_chunks[i], ra);
+#ifdef ET_TIMELINE
+                    const long long tl_c = clock64();
+#endif
                     if (i + 1 < n_my) {
                         tmem_ld_wait_regs(rb);
+#ifdef ET_TIMELINE
+                        const long long tl_d = clock64();
+#endif
                         if (i + 2 < n_my) tmem_ld32(lane_addr + my_chunks[i + 2] * 32, ra);
                         finish_chunk(my_chunks[i + 1], rb);
+#ifdef ET_TIMELINE
+                        const long long tl_e = clock64();
+                        if (threadIdx.x == 64 && tile_iter == 0 && i == 0 && blockIdx.x < 4096) {
+                            et_gemm_timeline[blockIdx.x * 16 + 12] = tl_a;
+                            et_gemm_timeline[blockIdx.x * 16 + 13] = tl_b;
+                            et_gemm_timeline[blockIdx.x * 16 + 14] = tl_c;
+                            et_gemm_timeline[blockIdx.x * 16 + 15] = tl_d;
+                            et_gemm_timeline[blockIdx.x * 16 + 6] = tl_e;
+                        }
+#endif
                     }
                 }
             }
@@ -362,14 +416,17 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 mbar_arrive(&acc_empty[buf]);
                 tma_store_commit();
             }
+            if (threadIdx.x == 64 && tile_iter != 0) ET_TL(9);
         }
         if (lane == 0) tma_store_wait_read();
+        if (threadIdx.x == 64) ET_TL(10);
     }
 
     pdl_wait();  // no CTA may retire before the kernels it depends on have completed
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (threadIdx.x == 32) ET_TL(11);
 }
 
 // out[r, c] = act(bias[c]) for every element: the columns a row-pruned Linear never computes.
@@ -420,11 +477,11 @@ __global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __re
 
 int g_max_ctas = 0;  // test hook: cap on the persistent grid (0 = one CTA per SM)
 
-template <int BN, int STAGES, bool PERSIST, bool B_MN>
-int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
-               GemmArgs args, int zdim, cudaStream_t stream) {
+template <int BN, int STAGES, bool PERSIST, bool B_MN, int EPI>
+int launch_cfg_epi(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+                   GemmArgs args, int zdim, cudaStream_t stream) {
     using Cfg = GemmCfg<BN, STAGES, PERSIST>;
-    auto kern = gemm_f16_kernel<BN, STAGES, PERSIST, B_MN>;
+    auto kern = gemm_f16_kernel<BN, STAGES, PERSIST, B_MN, EPI>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -443,6 +500,21 @@ int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap
                          args) == cudaSuccess
                ? ET_OK
                : ET_ERR_CUDA;
+}
+
+// Picks the epilogue specialisation: the fp16 tile store of a K-major product gets its
+// activation compiled in; everything else uses the run-time form.
+template <int BN, int STAGES, bool PERSIST, bool B_MN>
+int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+               const GemmArgs& args, int zdim, cudaStream_t stream) {
+    if (!B_MN && args.out_mode == OUT_TILE_F16) {
+        if (args.act == ET_ACT_GELU)
+            return launch_cfg_epi<BN, STAGES, PERSIST, false, 1 + ET_ACT_GELU>(tmA, tmB, tmY, args, zdim, stream);
+        if (args.act == ET_ACT_RELU)
+            return launch_cfg_epi<BN, STAGES, PERSIST, false, 1 + ET_ACT_RELU>(tmA, tmB, tmY, args, zdim, stream);
+        return launch_cfg_epi<BN, STAGES, PERSIST, false, 1 + ET_ACT_NONE>(tmA, tmB, tmY, args, zdim, stream);
+    }
+    return launch_cfg_epi<BN, STAGES, PERSIST, B_MN, 0>(tmA, tmB, tmY, args, zdim, stream);
 }
 
 int g_force_bn = 0;       // test hook: 0 = automatic, else 64 / 128 / 256
@@ -519,6 +591,38 @@ int pick_pair(int M, int N, int K) {
     return 0;
 }
 
+int g_force_tall = -1;  // test hook: -1 = automatic, 0 = never, 128 / 192 / 256 = always that width
+
+// Width of the 256-row single-CTA tile to use, or 0.  That form wins when it covers the
+// problem in ONE round of at most one tile per SM where 128-row tiles would need several
+// rounds: the weight tile is fetched once per 256 rows, so a K block costs
+// max(4 * bn, (256 + bn) * 128 B / 75) cycles for twice the rows.
+int pick_tall(int M, int N, int K) {
+    (void)K;
+    if (g_force_tall == 0) return 0;
+    if (g_force_tall == 128 || g_force_tall == 192 || g_force_tall == 256) return g_force_tall;
+    // Measured on B200 (BERT-base / BERT-large FFN shapes, 2048..8192 tokens): never faster than
+    // the persistent 128-row tiles or the CTA pairs - the epilogue of both accumulators is
+    // exposed after the single round - so this form only runs when the test hook asks for it.
+    if (g_force_tall < 0) return 0;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const long mt = (M + BM - 1) / BM, mt2 = (M + 2 * BM - 1) / (2 * BM);
+    if (mt * ((N + 127) / 128) <= 2L * sms) return 0;  // few tiles: the 128-row forms are resident at once
+    int best_bn = 0;
+    long best = -1;
+    for (int bn : {256, 192, 128}) {
+        const long tiles = mt2 * ((N + bn - 1) / bn);
+        if (tiles > sms || tiles * 10 < sms * 6L) continue;
+        const long tensor = 4L * bn, bytes = (256L + bn) * 128 / 75;
+        const long cost = tensor > bytes ? tensor : bytes;
+        if (best < 0 || cost < best) {
+            best = cost;
+            best_bn = bn;
+        }
+    }
+    return best_bn;
+}
+
 template <bool B_MN>
 int dispatch(const TilePlan& p, const CUtensorMap& tmA, const CUtensorMap& tmB,
              const CUtensorMap& tmY, const GemmArgs& args, int zdim, cudaStream_t stream) {
@@ -562,6 +666,7 @@ void gemm_force_bn(int bn) { g_force_bn = bn; }
 void gemm_force_persist(int mode) { g_force_persist = mode; }
 void gemm_set_max_ctas(int n) { g_max_ctas = n; }
 void gemm_force_pair(int mode) { g_force_pair = mode; }
+void gemm_force_tall(int mode) { g_force_tall = mode; }
 
 // ---- built-in gather scratch of et_linear_col_noalloc_fwd -------------------------------
 // Callers that cannot allocate device memory (see the entry point) use this array instead of
@@ -599,6 +704,9 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
         const int pair_bn = pick_pair(M, N, K);
         if (pair_bn != 0)
             return launch_gemm_pair_f16(X, ldx, W, ldw, bias, Y, ldy, M, N, K, act, pair_bn, stream);
+        const int tall_bn = pick_tall(M, N, K);
+        if (tall_bn != 0)
+            return launch_gemm_tall_f16(X, ldx, W, ldw, bias, Y, ldy, M, N, K, act, tall_bn, stream);
     }
     TilePlan plan = pick_plan(M, N, K, 1);
     if (plan.bn == 192 && col_map != nullptr) plan.bn = 128;  // 192 exists for the tile store only
@@ -700,6 +808,8 @@ extern "C" {
 void et_debug_force_gemm_bn(int bn) { et::gemm_force_bn(bn); }
 // Test hook: cap on the number of persistent CTAs (0 = one per SM).
 void et_debug_set_gemm_max_ctas(int n) { et::gemm_set_max_ctas(n); }
+// Test hook: -1 = automatic, 0 = never, 128 / 192 / 256 = 256-row single-CTA tiles of that width.
+void et_debug_force_gemm_tall(int mode) { et::gemm_force_tall(mode); }
 // Test hook: -1 = automatic, 0 = single-CTA kernels only, 128 / 256 = CTA-pair tiles of that width.
 void et_debug_force_gemm_pair(int mode) { et::gemm_force_pair(mode); }
 // Test hook: -1 = automatic, 0 = one tile per CTA, 1 = persistent CTAs.

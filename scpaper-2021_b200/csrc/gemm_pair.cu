@@ -63,7 +63,9 @@ struct PairTile {
     int n0, m0;
 };
 
-template <int BN, int STAGES, bool PERSIST, bool PARTIAL>
+// ACT: the activation, compiled in (run-time branches around the staging code cost a factor
+// of three in the epilogue).
+template <int BN, int STAGES, bool PERSIST, bool PARTIAL, int ACT>
 __global__ void __cluster_dims__(2, 1, 1)
 __launch_bounds__(GEMM_THREADS, (PairCfg<BN, STAGES, PERSIST, PARTIAL>::MIN_CTAS))
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -273,8 +275,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!ok) continue;
             tc_fence_after_sync();
             if (threadIdx.x == 64) ET_TL(7);
-            if (lane == 0) tma_store_wait_read();  // staging tiles of the previous tile
-            __syncwarp();
+            if (tile_iter > 0) {
+                if (lane == 0) tma_store_wait_read();  // staging tiles of the previous tile
+                __syncwarp();
+            }
 
             const uint32_t lane_addr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
             int my_chunks[NCHUNK];
@@ -301,12 +305,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 uint8_t* tile = sStage + (q * (BN / 64) + (ch >> 1)) * 4096;
                 uint8_t* srow = tile + lane * 128;
                 const float* b32 = tb + ch * 32;
-                if (g.act == ET_ACT_GELU)
-                    stage_f16_chunk<ET_ACT_GELU>(r, b32, srow, ch & 1, lane);
-                else if (g.act == ET_ACT_RELU)
-                    stage_f16_chunk<ET_ACT_RELU>(r, b32, srow, ch & 1, lane);
-                else
-                    stage_f16_chunk<ET_ACT_NONE>(r, b32, srow, ch & 1, lane);
+                stage_f16_chunk<ACT>(r, b32, srow, ch & 1, lane);
                 if ((ch & 1) || c.n0 + ch * 32 + 32 >= N) {  // the 64-column group is complete
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -364,11 +363,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 32) ET_TL(12);
 }
 
-template <int BN, int STAGES, bool PERSIST, bool PARTIAL = false>
-int launch_pair_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+template <int BN, int STAGES, bool PERSIST, bool PARTIAL, int ACT>
+int launch_pair_act(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
                     const GemmArgs& args, cudaStream_t stream) {
     using Cfg = PairCfg<BN, STAGES, PERSIST, PARTIAL>;
-    auto kern = gemm_pair_kernel<BN, STAGES, PERSIST, PARTIAL>;
+    auto kern = gemm_pair_kernel<BN, STAGES, PERSIST, PARTIAL, ACT>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -386,6 +385,16 @@ int launch_pair_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtens
                          Cfg::SMEM_BYTES, stream, tmA, tmB, tmY, args) == cudaSuccess
                ? ET_OK
                : ET_ERR_CUDA;
+}
+
+template <int BN, int STAGES, bool PERSIST, bool PARTIAL = false>
+int launch_pair_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+                    const GemmArgs& args, cudaStream_t stream) {
+    if (!PARTIAL && args.act == ET_ACT_GELU)
+        return launch_pair_act<BN, STAGES, PERSIST, PARTIAL, ET_ACT_GELU>(tmA, tmB, tmY, args, stream);
+    if (!PARTIAL && args.act == ET_ACT_RELU)
+        return launch_pair_act<BN, STAGES, PERSIST, PARTIAL, ET_ACT_RELU>(tmA, tmB, tmY, args, stream);
+    return launch_pair_act<BN, STAGES, PERSIST, PARTIAL, ET_ACT_NONE>(tmA, tmB, tmY, args, stream);
 }
 
 int g_pair_persist = -1;  // test hook: -1 = automatic, 0 = single-tile pairs, 1 = persistent

@@ -18,6 +18,12 @@ int launch_gemm_pair_f16(const __half* X, int ldx, const __half* W, int ldw, con
                          __half* Y, int ldy, int M, int N, int K, int act, int bn,
                          cudaStream_t stream);
 
+// The same product on 256 x bn single-CTA tiles (two accumulators share one weight tile);
+// see gemm_tall.cu.
+int launch_gemm_tall_f16(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
+                         __half* Y, int ldy, int M, int N, int K, int act, int bn,
+                         cudaStream_t stream);
+
 // Fused Q/K/V projection + attention for seq <= 128 and 64-wide heads; see qkv_attention.cu.
 bool qkv_attention_applies(int seq, int nhead, int kdim, int vdim);
 int launch_qkv_attention(const __half* X, const __half* Wqkv, const __half* bqkv, __half* Z,

@@ -70,6 +70,33 @@ def test_dense_cta_pairs(et, orc, cuda, T, inn, out, act, pair_bn, persist):
     assert torch.equal(y, y0), "CTA-pair and single-CTA results differ"
 
 
+@pytest.mark.parametrize("bn", [128, 192, 256])
+@pytest.mark.parametrize("T,inn,out,act", [
+    (256, 64, 256, 0), (2048, 768, 3072, 2), (512, 3072, 768, 0), (300, 768, 3072, 2),
+    (1, 16, 16, 0), (333, 1008, 1008, 2), (4100, 272, 528, 1),
+])
+def test_dense_256_row_tiles(et, orc, cuda, T, inn, out, act, bn):
+    """The 256-row single-CTA tiles (two accumulators per weight tile) against the oracle and,
+    bit for bit, against the 128-row kernels."""
+    import ctypes
+    import torch
+    x, w, b = _case(et, 14, T, inn, out)
+    xd, wd, bd = _dev(x, cuda), _dev(w, cuda), _dev(b, cuda)
+    L = et.lib()
+    try:
+        L.et_debug_force_gemm_pair(ctypes.c_int(0))
+        L.et_debug_force_gemm_tall(ctypes.c_int(0))
+        y0 = et.linear_dense(xd, wd, bd, act)
+        L.et_debug_force_gemm_tall(ctypes.c_int(bn))
+        y = et.linear_dense(xd, wd, bd, act)
+        assert et.device_error() == 0
+    finally:
+        L.et_debug_force_gemm_pair(ctypes.c_int(-1))
+        L.et_debug_force_gemm_tall(ctypes.c_int(-1))
+    assert_close(_host(y), orc.linear_dense(x, w, b, act), f"tall {T}x{inn}x{out} bn{bn}")
+    assert torch.equal(y, y0), "256-row and 128-row tiles differ"
+
+
 def test_dense_constant_closed_form(et, cuda):
     """W = 1, x = 1, b = 0.5 gives in + 0.5 everywhere (the reference's constant generators,
     Linear/gen_linear.hpp:15-23, Linear/test/test_tile.cu:61-74)."""
