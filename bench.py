@@ -415,6 +415,7 @@ def main():
         line["tile_pruned_80"] = pruned(0.8, "auto")
         line["tile_pruned_80"]["tile_kernel_only"] = pruned(0.8, True)
         line["tile_pruned_95"] = pruned(0.95, "auto")
+        line["tile_pruned_95"]["tile_kernel_only"] = pruned(0.95, True)
 
         # ---- CPU baseline (rank 0, N = 1 only) ----
         if world == 1:

@@ -152,7 +152,7 @@ def test_tile(et, orc, cuda, T, inn, out, act, sparsity):
     dense = et.tile_densify(_dev(rp, cuda), _dev(ro, cuda) if len(ro) else None,
                             _dev(tiles, cuda) if len(ro) else None, inn, out)
     assert np.array_equal(_host(dense), w)
-    assert et.tile_prefer_dense(inn, out, len(ro)) == (len(ro) > 0.08 * (inn // 16) * (out // 16))
+    assert et.tile_prefer_dense(inn, out, len(ro)) == (len(ro) > 0.02 * (inn // 16) * (out // 16))
 
 
 def test_tile_empty_block_rows(et, orc, cuda):
