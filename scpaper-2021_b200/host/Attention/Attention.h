@@ -244,15 +244,29 @@ class Attention<_config, std::enable_if_t<_config::isSingleKernel>> {
         assert(query == key && key == value);
         (void)key;
         (void)value;
-        linearQKV->forward(mat_qkv->get(), query, stream);
         const int ld = model->kdim * 2 + model->vdim;
         const int dh_qk = model->kdim / model->nhead, dh_v = model->vdim / model->nhead;
-        half* Q = mat_qkv->get();
-        half* K = Q + model->kdim;
-        half* V = K + model->kdim;
         int kind = mask ? ET_MASK_ADDITIVE : model->mask_kind;
         if (kind == ET_MASK_ADDITIVE && !mask) kind = ET_MASK_NONE;
         if (kind == ET_MASK_PADDING && !valid_len) kind = ET_MASK_NONE;
+        if constexpr (std::is_same_v<typename config::W_t, base_mat>) {
+            // dense fused-QKV weight, short sequences, 64-wide heads: projection and attention
+            // run as one kernel and the projected activations never reach memory
+            if (model->seq_len <= 128 && dh_qk == 64 && dh_v == 64) {
+                etChk(et_qkv_attention_fwd(et_ptr(query), et_ptr(linearQKV->weight.get()),
+                                           et_ptr(linearQKV->bias.get()), et_ptr(mat_z->get()),
+                                           model->batch, model->seq_len, linearQKV->in_size,
+                                           model->nhead, model->kdim, model->vdim, kind,
+                                           mask ? et_ptr(mask->get()) : nullptr, valid_len,
+                                           1.0f / std::sqrt((float)dh_qk), stream));
+                linearO->forward(out, mat_z->get(), stream);
+                return;
+            }
+        }
+        linearQKV->forward(mat_qkv->get(), query, stream);
+        half* Q = mat_qkv->get();
+        half* K = Q + model->kdim;
+        half* V = K + model->kdim;
         etChk(et_attention_fwd(et_ptr(Q), et_ptr(K), et_ptr(V), et_ptr(mat_z->get()), model->batch,
                                model->seq_len, model->nhead, dh_qk, dh_v, ld, ld, ld, model->vdim,
                                kind, mask ? et_ptr(mask->get()) : nullptr, valid_len,

@@ -274,6 +274,30 @@ static void test_attention_variants() {
     }
 }
 
+// Attention<dense fused-QKV weight, single kernel>: projection and attention run as one launch
+static void test_attention_fused_qkv_dense() {
+    const int batch = 3, seq = 100, hidden = 256, nhead = 4, T = batch * seq, dh = hidden / nhead;
+    auto model = std::make_shared<Model_t>(Model_t{hidden, hidden, seq, nhead, 512, hidden, 1, batch, 1});
+    auto wqkv = nvec((size_t)3 * hidden * hidden, 0.05f), wo = nvec((size_t)hidden * hidden, 0.05f);
+    auto bqkv = nvec(3 * hidden, 0.02f), bo = nvec(hidden, 0.02f);
+    auto x = nvec((size_t)T * hidden, 1.0f);
+    std::vector<float> qkv((size_t)T * 3 * hidden), z((size_t)T * hidden), ref(z.size());
+    orc_linear_dense(x.data(), wqkv.data(), bqkv.data(), qkv.data(), T, hidden, 3 * hidden, 0);
+    orc_attention(qkv.data(), qkv.data() + hidden, qkv.data() + 2 * hidden, z.data(), batch, seq, nhead, dh,
+                  dh, 3 * hidden, 3 * hidden, 3 * hidden, hidden, 1, nullptr, nullptr,
+                  1.0f / std::sqrt((float)dh));
+    orc_linear_dense(z.data(), wo.data(), bo.data(), ref.data(), T, hidden, hidden, 0);
+    using cfg = Attention_config<base_mat, base_mat, base_mat, base_mat, OTF_attn_full, true, false>;
+    auto lqkv = std::make_unique<Linear<base_mat>>(hidden, 3 * hidden, base_mat(to_half(wqkv)),
+                                                   to_half(bqkv).data(), T);
+    auto lo = std::make_unique<Linear<base_mat>>(hidden, hidden, base_mat(to_half(wo)), to_half(bo).data(), T);
+    Attention<cfg> attn(std::move(lqkv), std::move(lo), model);
+    culib::CUDA_ptr<half> dx(to_half(x)), dout((size_t)T * hidden);
+    attn.forward(dout.get(), dx.get(), dx.get(), dx.get());
+    CHECK(device_error() == 0, "device error");
+    compare(to_float(dout), ref, "Attention<dense fused QKV, single kernel>");
+}
+
 static void test_errors() {
     bool threw = false;
     try {
@@ -307,6 +331,7 @@ int main() {
         test_encoder_tile(2, 128, 1);
         test_encoder_tile(3, 80, 0);
         test_attention_variants();
+    test_attention_fused_qkv_dense();
         test_errors();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());
