@@ -272,6 +272,25 @@ int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half*
 int et_linear_vo_fwd(const et_half* X, const et_half* Wvo_t, const et_half* bias, et_half* VO,
                      int batch, int seq, int nhead, int emdim, et_stream stream);
 
+/* Column-pruned V.O: the pre-multiplied weight keeps only the output features
+ * col_id[0 .. nnz_col) (ascending, nnz_col % 16 == 0).
+ *   et_linear_vo_pruned_fwd: VOc[b][h] = X_b . Wvo_c[h] + bias[h] with Wvo_c
+ *     [nhead][emdim][nnz_col], bias [nhead][nnz_col] or null, VOc [batch][nhead][seq][nnz_col]
+ *     (Linear_VO_prune::forward, Fused_attention/Linear_VO.h:60-96).
+ *   et_fused_vo_attention_pruned_fwd: the attention at width nnz_col into scratch
+ *     [batch * seq, nnz_col], then out[t, col_id[k]] = scratch[t, k] + bias_o[col_id[k]] and
+ *     out[t, c] = bias_o[c] for pruned c (bias_o [emdim] or null)
+ *     (Fused_prune_Multihead_attention, Fused_attention/Fused_attention.cu:273-309). */
+int et_linear_vo_pruned_fwd(const et_half* X, const et_half* Wvo_c, const et_half* bias,
+                            et_half* VOc, int batch, int seq, int nhead, int emdim, int nnz_col,
+                            et_stream stream);
+int et_fused_vo_attention_pruned_fwd(const et_half* Q, const et_half* K, const et_half* VOc,
+                                     const int32_t* col_id, int nnz_col, const et_half* bias_o,
+                                     et_half* scratch, et_half* out, int batch, int seq, int nhead,
+                                     int dh_qk, int emdim, int ldq, int ldk, int mask_kind,
+                                     const et_half* mask, const int32_t* valid_len, float scale,
+                                     et_stream stream);
+
 /* =================================================================================
  * Whole encoder layer (post-LN), the call Encoder<config>::forward makes
  * (Encoder/Encoder.h:81-96):

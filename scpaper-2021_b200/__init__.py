@@ -30,6 +30,7 @@ ABI_SYMBOLS = [
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
     "et_validate_csr", "et_skip_layernorm_fwd", "et_layernorm_fwd", "et_act_fwd",
     "et_bias_add_fwd", "et_attention_fwd", "et_qkv_attention_fwd", "et_attention_pruned_v_fwd",
+    "et_linear_vo_pruned_fwd", "et_fused_vo_attention_pruned_fwd",
     "et_attention_fuse_o_fwd", "et_fused_vo_attention_fwd", "et_linear_vo_fwd",
     "et_encoder_layer_workspace_bytes", "et_encoder_layer_fwd",
 ]
@@ -363,6 +364,30 @@ def fused_vo_attention(q, k, vo, bias_o, batch, seq, nhead, dh_qk, emdim, mask_k
 
 
 # ---- encoder layer / stack ----------------------------------------------------------------
+
+def linear_vo_pruned(x, w_vo_c, bias, batch, seq, nhead, emdim):
+    """w_vo_c: [nhead, emdim, nnz_col]; returns VOc [batch * nhead * seq, nnz_col]."""
+    nnz = int(w_vo_c.shape[2])
+    vo = _empty((batch * nhead * seq, nnz), x)
+    check(lib().et_linear_vo_pruned_fwd(_p(x), _p(w_vo_c), _p(bias), _p(vo), c_int(batch), c_int(seq),
+                                        c_int(nhead), c_int(emdim), c_int(nnz), _stream()),
+          "et_linear_vo_pruned_fwd")
+    return vo
+
+
+def fused_vo_attention_pruned(q, k, vo_c, col_id, bias_o, batch, seq, nhead, dh_qk, emdim,
+                              mask_kind=MASK_NONE, mask=None, valid_len=None, scale=None):
+    nnz = int(vo_c.shape[1])
+    scratch = _empty((batch * seq, nnz), q)
+    out = _empty((batch * seq, emdim), q)
+    scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
+    check(lib().et_fused_vo_attention_pruned_fwd(
+        _p(q), _p(k), _p(vo_c), _p(col_id), c_int(nnz), _p(bias_o), _p(scratch), _p(out),
+        c_int(batch), c_int(seq), c_int(nhead), c_int(dh_qk), c_int(emdim), c_int(q.stride(0)),
+        c_int(k.stride(0)), c_int(mask_kind), _p(mask), _p(valid_len), c_float(scale), _stream()),
+        "et_fused_vo_attention_pruned_fwd")
+    return out
+
 
 class EncoderLayer:
     """Device-resident weights of one encoder layer plus the et_encoder_layer_t that

@@ -357,6 +357,38 @@ attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }  // namespace
 }  // namespace et
 
+namespace et {
+
+// out[t, c] = bias[c] (0 without a bias) for every element.
+__global__ void vo_fill_bias_kernel(__half* __restrict__ out, const __half* __restrict__ bias, int T,
+                                    int emdim) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t total = static_cast<size_t>(T) * emdim;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        out[i] = bias ? __ldg(bias + i % emdim) : __float2half_rn(0.f);
+}
+
+// out[t, col_id[k]] = comp[t, k] + bias[col_id[k]]: the kept features of a column-pruned result.
+__global__ void vo_scatter_cols_kernel(const __half* __restrict__ comp, const int* __restrict__ col_id,
+                                       const __half* __restrict__ bias, __half* __restrict__ out,
+                                       int T, int nnz_col, int emdim) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t total = static_cast<size_t>(T) * nnz_col;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = i / nnz_col;
+        const int c = __ldg(col_id + (i - t * nnz_col));
+        if (c < 0 || c >= emdim) continue;
+        const float b = bias ? __half2float(__ldg(bias + c)) : 0.f;
+        out[t * emdim + c] = __float2half_rn(__half2float(comp[i]) + b);
+    }
+}
+
+}  // namespace et
+
 extern "C" {
 
 int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half* VO,
@@ -424,4 +456,52 @@ int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half*
                : ET_ERR_CUDA;
 }
 
+// ---- column-pruned V.O (Linear_VO_prune + Fused_prune_Multihead_attention) -----------------
+// The pre-multiplied weight keeps only the output features col_id[0 .. nnz_col): VO_c is
+// [batch][nhead][seq][nnz_col]; the attention runs at that width and its result is scattered
+// back to the full feature dimension (pruned features carry the output bias alone).
+
+int et_linear_vo_pruned_fwd(const et_half* X, const et_half* Wvo_c, const et_half* bias,
+                            et_half* VOc, int batch, int seq, int nhead, int emdim, int nnz_col,
+                            et_stream stream) {
+    if (batch <= 0 || seq <= 0 || nhead <= 0 || emdim <= 0 || nnz_col <= 0) return ET_ERR_INVALID_ARG;
+    if (emdim % 16 || nnz_col % 16) return ET_ERR_SHAPE;
+    return et::launch_gemm_f16_grouped_kn(
+        reinterpret_cast<const __half*>(X), emdim, reinterpret_cast<const __half*>(Wvo_c),
+        reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(VOc), batch * seq, nnz_col,
+        emdim, nhead, seq, static_cast<cudaStream_t>(stream));
+}
+
+int et_fused_vo_attention_pruned_fwd(const et_half* Q, const et_half* K, const et_half* VOc,
+                                     const int32_t* col_id, int nnz_col, const et_half* bias_o,
+                                     et_half* scratch, et_half* out, int batch, int seq, int nhead,
+                                     int dh_qk, int emdim, int ldq, int ldk, int mask_kind,
+                                     const et_half* mask, const int32_t* valid_len, float scale,
+                                     et_stream stream) {
+    if (!col_id || !scratch || !out || nnz_col <= 0 || emdim <= 0) return ET_ERR_INVALID_ARG;
+    if (nnz_col % 16 || emdim % 8 || nnz_col > emdim) return ET_ERR_SHAPE;
+    if (!et::aligned16(out) || !et::aligned16(scratch) || (bias_o && !et::aligned16(bias_o)))
+        return ET_ERR_ALIGNMENT;
+    int st = et_fused_vo_attention_fwd(Q, K, VOc, nullptr, scratch, batch, seq, nhead, dh_qk, nnz_col,
+                                       ldq, ldk, mask_kind, mask, valid_len, scale, stream);
+    if (st != ET_OK) return st;
+    const int T = batch * seq;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t total = static_cast<size_t>(T) * emdim;
+    const int blocks = static_cast<int>((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048);
+    if (et::launch_kernel(et::vo_fill_bias_kernel, dim3(blocks), dim3(256), 0, s,
+                          reinterpret_cast<__half*>(out), reinterpret_cast<const __half*>(bias_o), T,
+                          emdim) != cudaSuccess)
+        return ET_ERR_CUDA;
+    const size_t totc = static_cast<size_t>(T) * nnz_col;
+    const int blocks2 = static_cast<int>((totc + 255) / 256 < 2048 ? (totc + 255) / 256 : 2048);
+    return et::launch_kernel(et::vo_scatter_cols_kernel, dim3(blocks2), dim3(256), 0, s,
+                             reinterpret_cast<const __half*>(scratch), col_id,
+                             reinterpret_cast<const __half*>(bias_o), reinterpret_cast<__half*>(out),
+                             T, nnz_col, emdim) == cudaSuccess
+               ? ET_OK
+               : ET_ERR_CUDA;
+}
+
 }  // extern "C"
+

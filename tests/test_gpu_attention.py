@@ -235,3 +235,38 @@ def test_qkv_attention_rejects_other_shapes(et, cuda):
     w2 = torch.zeros((96, 64), dtype=torch.float16, device=cuda)
     with pytest.raises(et.EtError):
         et.qkv_attention(x[:128], w2, None, 1, 128, 1, 32, 32)  # 32-wide head
+
+
+@pytest.mark.parametrize("batch,seq,nhead,dh,emdim,sparsity", [
+    (2, 128, 4, 64, 256, 0.5), (1, 200, 3, 64, 320, 0.75), (2, 96, 2, 32, 80, 0.0),
+])
+def test_fused_vo_attention_column_pruned(et, orc, cuda, batch, seq, nhead, dh, emdim, sparsity):
+    """Column-pruned V.O: projection and attention run at the kept width, the result is
+    scattered back; pruned output features carry the bias alone."""
+    T = batch * seq
+    q = et.synth.normal(700 + seq, 1, (T, nhead * dh), 1.0)
+    k = et.synth.normal(700 + seq, 2, (T, nhead * dh), 1.0)
+    x = et.synth.normal(700 + seq, 3, (T, emdim), 1.0)
+    wvo = et.synth.normal(700 + seq, 4, (nhead, emdim, emdim), 0.05)
+    bvo = et.synth.normal(700 + seq, 5, (nhead, emdim), 0.05)
+    bo = et.synth.normal(700 + seq, 6, (emdim,), 0.1)
+    cid = et.synth.choose_ids(700 + seq, 7, emdim, sparsity)
+    wc = np.ascontiguousarray(wvo[:, :, cid])
+    bc = np.ascontiguousarray(bvo[:, cid])
+    voc = et.linear_vo_pruned(_dev(x, cuda), _dev(wc, cuda), _dev(bc, cuda), batch, seq, nhead, emdim)
+    assert et.device_error() == 0
+    xf = x.astype(np.float32).reshape(batch, seq, emdim)
+    vo_ref = np.einsum("bse,heo->bhso", xf, wc.astype(np.float32)) + bc.astype(np.float32)[None, :, None, :]
+    assert_close(voc.float().cpu().numpy(), vo_ref.reshape(-1, len(cid)), "linear_vo_pruned")
+    out = et.fused_vo_attention_pruned(_dev(q, cuda), _dev(k, cuda), voc, _dev(cid, cuda), _dev(bo, cuda),
+                                       batch, seq, nhead, dh, emdim, 1)
+    assert et.device_error() == 0
+    comp = orc.fused_vo_attention(q, k, voc.float().cpu().numpy(), None, batch, seq, nhead, dh,
+                                  len(cid), 1)
+    ref = np.tile(bo.astype(np.float32), (T, 1))
+    ref[:, cid] += orc.round_fp16(comp)
+    assert_close(out.float().cpu().numpy(), ref, f"pruned fused VO s{seq} e{emdim}")
+    pruned = np.setdiff1d(np.arange(emdim), cid)
+    if len(pruned):
+        assert np.array_equal(out.float().cpu().numpy()[:, pruned],
+                              np.tile(bo.astype(np.float32)[pruned], (T, 1)))
