@@ -50,9 +50,10 @@ def errors(got: np.ndarray, ref: np.ndarray):
 def assert_close(got, ref, what="", rel_tol=REL_L2_TOL, abs_tol=MAX_ABS_TOL, dump=None):
     """rel-L2 <= 5e-3 and max-abs <= 2e-2, the tolerance stated for fp16 compute."""
     rel, mx = errors(got, ref)
-    if not (rel <= rel_tol and mx <= abs_tol) and dump is not None:
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        np.savez_compressed(os.path.join(ROOT, "gpurun_out", dump + ".npz"),
+    dump_dir = os.environ.get("ET_DUMP_DIR")  # set it to keep the arrays of a failing comparison
+    if not (rel <= rel_tol and mx <= abs_tol) and dump is not None and dump_dir:
+        os.makedirs(dump_dir, exist_ok=True)
+        np.savez_compressed(os.path.join(dump_dir, dump + ".npz"),
                             got=np.asarray(got, np.float32), ref=np.asarray(ref, np.float32))
     assert np.isfinite(rel) and rel <= rel_tol and mx <= abs_tol, \
         f"{what}: rel-L2 {rel:.3e} (tol {rel_tol}), max-abs {mx:.3e} (tol {abs_tol})"

@@ -1,6 +1,7 @@
-"""Generates the golden fixtures under tests/golden/.  Run it where /root/reference is mounted:
+"""Generates the golden fixtures under tests/golden/.  Run it where a checkout of the reference
+(cctry/SCpaper-2021) is available:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 1. tile_csr_golden.npz   the reference exporter's own tile-CSR builder (gen_csr in
                          example/npy2pt.py:75-109, executed from its source text) applied to
@@ -24,7 +25,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ET_REFERENCE_DIR", "")
+if not os.path.isdir(os.path.join(REF, "example")):
+    raise SystemExit("usage: make_golden.py <path to the reference checkout>")
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
