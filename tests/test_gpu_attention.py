@@ -270,3 +270,29 @@ def test_fused_vo_attention_column_pruned(et, orc, cuda, batch, seq, nhead, dh, 
     if len(pruned):
         assert np.array_equal(out.float().cpu().numpy()[:, pruned],
                               np.tile(bo.astype(np.float32)[pruned], (T, 1)))
+
+
+def test_qkv_attention_edge_lengths(et, orc, cuda):
+    """One-token sequences, a sequence whose valid length is zero (zeros out), no bias."""
+    import torch
+    d = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    hidden, nhead, kdim = 64, 1, 64
+    w = et.synth.normal(810, 2, (3 * kdim, hidden), 0.1)
+    # seq = 1: softmax over one key is 1, so Z = V
+    x = et.synth.normal(810, 1, (5, hidden), 1.0)
+    z = et.qkv_attention(d(x), d(w), None, 5, 1, nhead, kdim, kdim)
+    assert et.device_error() == 0
+    v = orc.round_fp16(orc.linear_dense(x, w[2 * kdim:], None, 0))
+    assert_close(z.float().cpu().numpy(), v, "seq 1: Z equals V")
+    # padding mask with an empty sequence
+    batch, seq = 3, 40
+    x = et.synth.normal(811, 1, (batch * seq, hidden), 1.0)
+    vl = np.array([40, 0, 17], dtype=np.int32)
+    z = et.qkv_attention(d(x), d(w), None, batch, seq, nhead, kdim, kdim, 2, None, d(vl))
+    assert et.device_error() == 0
+    zz = z.float().cpu().numpy()
+    assert np.all(zz[seq:2 * seq] == 0)
+    qkv = orc.round_fp16(orc.linear_dense(x, w, None, 0))
+    ref = orc.attention(qkv[:, :kdim], qkv[:, kdim:2 * kdim], qkv[:, 2 * kdim:], batch, seq, nhead, 64,
+                        64, 2, None, vl)
+    assert_close(zz, ref, "padding with an empty sequence")
