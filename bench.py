@@ -417,6 +417,7 @@ def main():
 
         line["tile_pruned_80"] = pruned(0.8, "auto")
         line["tile_pruned_80"]["tile_kernel_only"] = pruned(0.8, True)
+        line["tile_pruned_90"] = pruned(0.9, "auto")
         line["tile_pruned_95"] = pruned(0.95, "auto")
         line["tile_pruned_95"]["tile_kernel_only"] = pruned(0.95, True)
 

@@ -416,7 +416,11 @@ class EncoderLayer:
             if tile_sparse:
                 rp, ro, tiles = synth.dense_to_tile(W)
                 d.nnz_tiles = int(tiles.shape[0])
-                if tile_sparse == "auto" and tile_prefer_dense(d.in_, d.out, d.nnz_tiles):
+                # the fused projection + attention kernel needs a dense Q/K/V weight and beats
+                # the tile kernel followed by the attention kernel at any sparsity below ~97 %
+                fusable = wname == "wqkv" and d.out % (3 * 64) == 0 and d.out // 3 == 64 * nhead
+                if tile_sparse == "auto" and (fusable or
+                                              tile_prefer_dense(d.in_, d.out, d.nnz_tiles)):
                     dense = tile_densify(dev(rp), dev(ro) if d.nnz_tiles else None,
                                          dev(tiles) if d.nnz_tiles else None, d.in_, d.out)
                     self._keep.append(dense)

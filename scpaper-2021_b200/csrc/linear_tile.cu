@@ -53,20 +53,24 @@ constexpr int MAX_STAGES = 4;
 constexpr int MAX_IN = 8192;
 
 // PACKED: pk_mask / pk_off / tiles describe the re-packed weights (row_off unused).
-// ACT: the activation, compiled in.
-template <bool PACKED, int ACT>
+// ACT: the activation, compiled in.  NP: panels of 8 output block rows per CTA (1, or 2 for
+// packed weights with many panels: both panels share every activation slab, which halves the
+// activation traffic and the per-CTA fixed cost per output).
+template <bool PACKED, int ACT, int NP>
 __global__ void __launch_bounds__(TILE_THREADS, 2)
 linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmY, const int* __restrict__ row_ptr,
                    const int* __restrict__ row_off, const uint32_t* __restrict__ pk_mask,
                    const int* __restrict__ pk_off, const __half* __restrict__ pk_tiles,
                    const __half* __restrict__ bias, int T, int in, int out, int* err_word) {
+    static_assert(NP == 1 || PACKED, "two panels per CTA exist for packed weights only");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
     // shared-memory provenance (plain LDS / STS instead of generic accesses)
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int nbc = in >> 4;  // input block columns
     const int nchunk = (in + CHUNK - 1) / CHUNK;
+    const int nchunk_p = (nchunk + 3) & ~3;
     uint8_t* ring = smem;
     uint8_t* misc = smem + RING_BYTES;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);
@@ -75,36 +79,43 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* max_cnt = reinterpret_cast<int*>(tmem_slot + 2);
-    int* rp = reinterpret_cast<int*>(tmem_slot + 4);                  // [PANEL_ROWS + 1]
-    float* s_bias = reinterpret_cast<float*>(misc + 256);             // [TBN]
-    uint32_t* chunk_mask = reinterpret_cast<uint32_t*>(s_bias + TBN);  // [nchunk]
-    // unpacked: tile_at[8][nbc]; packed: chunk_off[nchunk] (first tile of each chunk)
-    int* tile_at = reinterpret_cast<int*>(chunk_mask + ((nchunk + 3) & ~3));
+    int* rp = reinterpret_cast<int*>(tmem_slot + 4);                       // [NP][PANEL_ROWS + 1]
+    float* s_bias = reinterpret_cast<float*>(misc + 256);                  // [NP * TBN]
+    uint32_t* chunk_mask = reinterpret_cast<uint32_t*>(s_bias + NP * TBN);  // [NP][nchunk_p]
+    // unpacked: tile_at[8][nbc]; packed: [NP][nchunk_p] (first tile of each chunk)
+    int* tile_at = reinterpret_cast<int*>(chunk_mask + NP * nchunk_p);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int panel = blockIdx.x;
+    const int panel0 = blockIdx.x * NP;
     const int m0 = blockIdx.y * TBM;
-    const int n0 = panel * TBN;
     const int nbr = out >> 4;
+    const int npanel = (out + TBN - 1) / TBN;
 
     // ---- prologue: panel index tables and bias (weights: independent of earlier kernels) ----
     if (threadIdx.x == 0) ET_TL(0);
-    if (threadIdx.x <= PANEL_ROWS) {
-        int br = panel * PANEL_ROWS + threadIdx.x;
+    if (threadIdx.x < NP * (PANEL_ROWS + 1)) {
+        const int k = threadIdx.x / (PANEL_ROWS + 1), i = threadIdx.x % (PANEL_ROWS + 1);
+        int br = (panel0 + k) * PANEL_ROWS + i;
         br = br < nbr ? br : nbr;
         rp[threadIdx.x] = __ldg(row_ptr + br);
     }
-    for (int i = threadIdx.x; i < nchunk; i += TILE_THREADS) {
+    for (int i = threadIdx.x; i < NP * nchunk; i += TILE_THREADS) {
+        const int k = i / nchunk, c = i - k * nchunk;
         if (PACKED) {
-            chunk_mask[i] = __ldg(pk_mask + static_cast<size_t>(panel) * nchunk + i);
-            tile_at[i] = __ldg(pk_off + static_cast<size_t>(panel) * nchunk + i);
+            const bool live = panel0 + k < npanel;
+            chunk_mask[k * nchunk_p + c] =
+                live ? __ldg(pk_mask + static_cast<size_t>(panel0 + k) * nchunk + c) : 0u;
+            tile_at[k * nchunk_p + c] =
+                live ? __ldg(pk_off + static_cast<size_t>(panel0 + k) * nchunk + c) : 0;
         } else {
-            chunk_mask[i] = 0u;
+            chunk_mask[c] = 0u;
         }
     }
-    for (int i = threadIdx.x; i < TBN; i += TILE_THREADS)
-        s_bias[i] = (bias != nullptr && n0 + i < out) ? __half2float(__ldg(bias + n0 + i)) : 0.f;
+    for (int i = threadIdx.x; i < NP * TBN; i += TILE_THREADS) {
+        const int n = panel0 * TBN + i;
+        s_bias[i] = (bias != nullptr && n < out) ? __half2float(__ldg(bias + n)) : 0.f;
+    }
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmX);
         tma_prefetch_desc(&tmW);
@@ -118,7 +129,7 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, TBN);
+        tmem_alloc(tmem_slot, NP * TBN);
         tmem_relinquish();
     }
     __syncthreads();
@@ -136,9 +147,10 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     }
     {
         int mc = 0;
-        for (int i = threadIdx.x; i < nchunk; i += TILE_THREADS) {
-            const int c = __popc(chunk_mask[i]);
-            mc = c > mc ? c : mc;
+        for (int i = threadIdx.x; i < NP * nchunk; i += TILE_THREADS) {
+            const int k = i / nchunk, c = i - k * nchunk;
+            const int cnt = __popc(chunk_mask[k * nchunk_p + c]);
+            mc = cnt > mc ? cnt : mc;
         }
         if (mc > 0) atomicMax(max_cnt, mc);
     }
@@ -146,42 +158,61 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const int panel_tiles = rp[PANEL_ROWS] - rp[0];
-    // stage geometry: activation slab + densely packed tile slots
+    int panel_tiles = 0;
+#pragma unroll
+    for (int k = 0; k < NP; ++k)
+        panel_tiles += rp[k * (PANEL_ROWS + 1) + PANEL_ROWS] - rp[k * (PANEL_ROWS + 1)];
+    // stage geometry: activation slab + densely packed tile slots (per panel)
     const int nslot = *max_cnt <= 16 ? 16 : 32;
-    const int stage_bytes = X_STAGE_BYTES + nslot * 512;
-    const int nstages = RING_BYTES / stage_bytes;  // 4 or 3
+    const int stage_bytes = X_STAGE_BYTES + NP * nslot * 512;
+    const int nstages = RING_BYTES / stage_bytes;  // 4, 3 or 2
     if (threadIdx.x == 0) ET_TL(1);
     pdl_launch_dependents();
     pdl_wait();  // the tables above are weights; activations and Y need the wait
 
+    // all panels' masks of one chunk
+    auto masks_of = [&](int kc, uint32_t (&m)[NP]) -> uint32_t {
+        uint32_t any = 0;
+#pragma unroll
+        for (int k = 0; k < NP; ++k) {
+            m[k] = chunk_mask[k * nchunk_p + kc];
+            any |= m[k];
+        }
+        return any;
+    };
+
     if (warp < 2) {
         // ---------------- producers ----------------
         // packed: lane 0 of warps 0 and 1 take alternate chunks, each fetching the activation
-        // slab and the chunk's tiles (one bulk copy); tile-CSR: warp 0 alone, lane = row * 4 + column in chunk fetches
-        // its own tile.  Stage index and phase advance incrementally (no divisions on the path).
+        // slab and the chunk's tiles (one bulk copy per panel); tile-CSR: warp 0 alone, lane =
+        // row * 4 + column in chunk fetches its own tile.  Stage index and phase advance
+        // incrementally (no divisions on the path).
         int s = 0, issued = 0;
         uint32_t ph = 0;
         if (PACKED) {
             if (lane == 0) {
-                // the two producer threads take alternate chunks
                 for (int kc = 0; kc < nchunk; ++kc) {
-                    const uint32_t mask = chunk_mask[kc];
-                    if (mask == 0u) continue;
+                    uint32_t m[NP];
+                    if (masks_of(kc, m) == 0u) continue;
                     if ((issued & 1) == warp) {
                         uint8_t* stage = ring + s * stage_bytes;
                         if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) {
                             report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_PRODUCER);
                             break;
                         }
-                        const uint32_t bytes = 512u * __popc(mask);
+                        uint32_t bytes = 0;
+#pragma unroll
+                        for (int k = 0; k < NP; ++k) bytes += 512u * __popc(m[k]);
                         mbar_arrive_expect_tx(&full_bar[s], X_STAGE_BYTES + bytes);
                         if (issued < 12) ET_TL(16 + issued * 4);
                         tma_load_2d(stage, &tmX, &full_bar[s], kc * CHUNK, m0);
-                        // the chunk's tiles are one contiguous, pre-swizzled run
-                        bulk_load(stage + X_STAGE_BYTES,
-                                  pk_tiles + static_cast<size_t>(tile_at[kc]) * 256, bytes,
-                                  &full_bar[s]);
+                        // a panel's tiles of the chunk are one contiguous, pre-swizzled run
+#pragma unroll
+                        for (int k = 0; k < NP; ++k)
+                            if (m[k] != 0u)
+                                bulk_load(stage + X_STAGE_BYTES + k * nslot * 512,
+                                          pk_tiles + static_cast<size_t>(tile_at[k * nchunk_p + kc]) * 256,
+                                          512u * __popc(m[k]), &full_bar[s]);
                         if (issued < 12) ET_TL(17 + issued * 4);
                     }
                     ++issued;
@@ -234,24 +265,26 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             }
         }
     } else {
-        // ------- warps 2..9: MMA issue for one block row each, then the epilogue -------
+        // ------- warps 2..9: MMA issue for one block row (of every panel) each, then the epilogue
         // Issuing a 128 x 16 x 16 product costs far more issue time than tensor time, so the
-        // eight block rows of the panel are issued by eight threads in parallel; every warp
+        // eight block rows of a panel are issued by eight threads in parallel; every warp
         // commits its own products to the stage's empty barrier and to the accumulator barrier.
         const int e = warp - 2;            // block row issued by this warp
         const int q = warp & 3;            // TMEM lane quadrant read in the epilogue
-        const int half = (warp - 2) >> 2;  // which 64 output columns of the panel
+        const int half = (warp - 2) >> 2;  // which 64 output columns of a panel
         bool ok = true;
         if (panel_tiles > 0) {
             if (lane == 0) {
                 constexpr uint32_t idesc = make_idesc_f16(TBM, 16, 0, 0);
-                uint32_t started = 0;
+                uint32_t started[NP];
+#pragma unroll
+                for (int k = 0; k < NP; ++k) started[k] = 0u;
                 int s = 0, stage_it = 0;
                 uint32_t ph = 0;
                 const uint32_t below_mask = (1u << (4 * e)) - 1u;
                 for (int kc = 0; kc < nchunk; ++kc) {
-                    const uint32_t mask = chunk_mask[kc];
-                    if (mask == 0u) continue;
+                    uint32_t m[NP];
+                    if (masks_of(kc, m) == 0u) continue;
                     // a warp without a tile in this chunk still waits: its arrival must not
                     // run ahead into the stage's next use
                     if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
@@ -260,27 +293,32 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                         break;
                     }
                     if (e == 0 && stage_it < 12) ET_TL(18 + stage_it * 4);
-                    uint32_t nib = (mask >> (4 * e)) & 0xFu;
-                    if (nib) {
-                        tc_fence_after_sync();
+                    bool issued_any = false;
+#pragma unroll
+                    for (int k = 0; k < NP; ++k) {
+                        uint32_t nib = (m[k] >> (4 * e)) & 0xFu;
+                        if (nib == 0u) continue;
+                        if (!issued_any) tc_fence_after_sync();
+                        issued_any = true;
                         const uint32_t x_addr = smem_u32(ring + s * stage_bytes);
                         // descriptors differ from tile to tile only in their start address
                         const uint64_t a_base = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
-                        uint64_t bd = make_smem_desc(
-                            x_addr + X_STAGE_BYTES + 512u * __popc(mask & below_mask), 16, 256,
-                            SWZ_32B);
+                        uint64_t bd = make_smem_desc(x_addr + X_STAGE_BYTES + k * nslot * 512 +
+                                                         512u * __popc(m[k] & below_mask),
+                                                     16, 256, SWZ_32B);
                         while (nib) {
                             const int kb = __ffs(nib) - 1;
                             nib &= nib - 1;
-                            mma_f16_ss(tmem_base + e * 16, a_base + static_cast<uint64_t>(kb * 2),
-                                       bd, idesc, started);
-                            started = 1u;
+                            mma_f16_ss(tmem_base + k * TBN + e * 16,
+                                       a_base + static_cast<uint64_t>(kb * 2), bd, idesc, started[k]);
+                            started[k] = 1u;
                             bd += 32;  // next 512-byte slot
                         }
-                        mma_commit(&empty_bar[s]);
-                    } else {
-                        mbar_arrive(&empty_bar[s]);
                     }
+                    if (issued_any)
+                        mma_commit(&empty_bar[s]);
+                    else
+                        mbar_arrive(&empty_bar[s]);
                     if (e == 0 && stage_it < 12) ET_TL(19 + stage_it * 4);
                     ++stage_it;
                     if (++s == nstages) {
@@ -297,22 +335,28 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
         ok = __all_sync(0xffffffffu, ok);
         if (threadIdx.x == 64) ET_TL(3);
-        if (ok && n0 + half * 64 < out) {
+        bool stored = false;
+#pragma unroll
+        for (int k = 0; k < NP; ++k) {
+            const int n0 = (panel0 + k) * TBN;
+            if (!ok || n0 + half * 64 >= out) continue;
             tc_fence_after_sync();
+            const int* rpk = rp + k * (PANEL_ROWS + 1);
+            const bool panel_has_tiles = rpk[PANEL_ROWS] > rpk[0];
             // every MMA has completed: the ring is idle and serves as the staging area
-            uint8_t* tile = ring + (q * 2 + half) * 4096;
+            uint8_t* tile = ring + (k * 8 + q * 2 + half) * 4096;
             uint8_t* srow = tile + lane * 128;
-            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+            const uint32_t lane_addr = tmem_base + k * TBN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 const int c = half * 2 + cc;  // 32-column chunk = block rows 2c, 2c + 1
                 uint32_t v[32];
-                if (panel_tiles > 0) {
+                if (panel_has_tiles) {
                     tmem_ld32(lane_addr + c * 32, v);
                     tmem_ld_wait_regs(v);
                 }
                 // block rows without a stored tile were never written by the tensor core
-                const bool has0 = rp[2 * c + 1] > rp[2 * c], has1 = rp[2 * c + 2] > rp[2 * c + 1];
+                const bool has0 = rpk[2 * c + 1] > rpk[2 * c], has1 = rpk[2 * c + 2] > rpk[2 * c + 1];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if (!has0) v[j] = 0u;
@@ -323,7 +367,9 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     float f[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        f[j] = apply_act(__uint_as_float(v[gq * 8 + j]) + s_bias[c * 32 + gq * 8 + j], ACT);
+                        f[j] = apply_act(__uint_as_float(v[gq * 8 + j]) +
+                                             s_bias[k * TBN + c * 32 + gq * 8 + j],
+                                         ACT);
                     uint4 o;
                     o.x = pack_half2(f[0], f[1]);
                     o.y = pack_half2(f[2], f[3]);
@@ -336,9 +382,12 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             __syncwarp();
             if (lane == 0 && m0 + q * 32 < T) {
                 tma_store_2d(&tmY, tile, n0 + half * 64, m0 + q * 32);
-                tma_store_commit();
-                tma_store_wait_read();
+                stored = true;
             }
+        }
+        if (stored) {
+            tma_store_commit();
+            tma_store_wait_read();
         }
         if (threadIdx.x == 64) ET_TL(4);
     }
@@ -346,7 +395,7 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) ET_TL(5);
-    if (warp == 1) tmem_dealloc(tmem_base, TBN);
+    if (warp == 1) tmem_dealloc(tmem_base, NP * TBN);
 }
 
 __global__ void tile_fill_bias_kernel(__half* __restrict__ Y, const __half* __restrict__ bias,
@@ -391,6 +440,8 @@ __global__ void pack_tiles_kernel(const uint4* __restrict__ src, const int* __re
         dst[t * 32 + dc] = __ldg(src + static_cast<size_t>(__ldg(perm + t)) * 32 + c);
     }
 }
+
+int g_tile_wide = -1;  // test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA
 
 namespace {
 int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, const uint32_t* pk_mask,
@@ -440,14 +491,23 @@ int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, cons
         int st = make_tensor_map_f16(&tmY, Y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != ET_OK) return st;
     }
-    const int nbc = in / 16, nchunk = (in + CHUNK - 1) / CHUNK;
-    const int smem_bytes = RING_BYTES + 256 + TBN * 4 + ((nchunk + 3) & ~3) * 4 +
-                           PANEL_ROWS * nbc * 4 + 1024;
+    const int nbc = in / 16, nchunk = (in + CHUNK - 1) / CHUNK, nchunk_p = (nchunk + 3) & ~3;
+    const int npanel = (out + TBN - 1) / TBN;
+    // two panels per CTA when that grid still holds more CTAs than fit at once (measured on
+    // B200: 768 -> 3072 at 2048 tokens gains 20 %, 768 -> 2304 with 144 wide CTAs loses 25 %):
+    // the panels share every activation slab
+    const long wide_ctas = static_cast<long>((npanel + 1) / 2) * ((T + TBM - 1) / TBM);
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const bool wide =
+        packed && g_tile_wide != 0 && (g_tile_wide > 0 || (npanel >= 2 && wide_ctas * 4 >= sms * 5L));
+    const int np = wide ? 2 : 1;
+    const int smem_bytes = RING_BYTES + 256 + np * TBN * 4 + np * nchunk_p * 4 +
+                           (packed ? np * nchunk_p * 4 : PANEL_ROWS * nbc * 4) + 1024;
     int dev = 0;
     cudaGetDevice(&dev);
-    dim3 grid((out + TBN - 1) / TBN, (T + TBM - 1) / TBM);
+    dim3 grid((npanel + np - 1) / np, (T + TBM - 1) / TBM);
     auto go = [&](auto kern, int slot) -> cudaError_t {
-        static int attr_bytes[6][64] = {};
+        static int attr_bytes[9][64] = {};
         if (dev >= 0 && dev < 64 && attr_bytes[slot][dev] < smem_bytes) {
             const cudaError_t ea =
                 cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -458,14 +518,18 @@ int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, cons
                              row_ptr, row_off, pk_mask, pk_off, tiles, bias, T, in, out, err);
     };
     cudaError_t e;
-    if (packed) {
-        e = act == ET_ACT_GELU   ? go(linear_tile_kernel<true, ET_ACT_GELU>, 0)
-            : act == ET_ACT_RELU ? go(linear_tile_kernel<true, ET_ACT_RELU>, 1)
-                                 : go(linear_tile_kernel<true, ET_ACT_NONE>, 2);
+    if (wide) {
+        e = act == ET_ACT_GELU   ? go(linear_tile_kernel<true, ET_ACT_GELU, 2>, 6)
+            : act == ET_ACT_RELU ? go(linear_tile_kernel<true, ET_ACT_RELU, 2>, 7)
+                                 : go(linear_tile_kernel<true, ET_ACT_NONE, 2>, 8);
+    } else if (packed) {
+        e = act == ET_ACT_GELU   ? go(linear_tile_kernel<true, ET_ACT_GELU, 1>, 0)
+            : act == ET_ACT_RELU ? go(linear_tile_kernel<true, ET_ACT_RELU, 1>, 1)
+                                 : go(linear_tile_kernel<true, ET_ACT_NONE, 1>, 2);
     } else {
-        e = act == ET_ACT_GELU   ? go(linear_tile_kernel<false, ET_ACT_GELU>, 3)
-            : act == ET_ACT_RELU ? go(linear_tile_kernel<false, ET_ACT_RELU>, 4)
-                                 : go(linear_tile_kernel<false, ET_ACT_NONE>, 5);
+        e = act == ET_ACT_GELU   ? go(linear_tile_kernel<false, ET_ACT_GELU, 1>, 3)
+            : act == ET_ACT_RELU ? go(linear_tile_kernel<false, ET_ACT_RELU, 1>, 4)
+                                 : go(linear_tile_kernel<false, ET_ACT_NONE, 1>, 5);
     }
     return e == cudaSuccess ? ET_OK : ET_ERR_CUDA;
 }
@@ -489,6 +553,9 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
 }  // namespace et
 
 extern "C" {
+
+// Test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA (packed weights).
+void et_debug_set_tile_wide(int mode) { et::g_tile_wide = mode; }
 
 int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,
                        int nnz_tiles, const et_half* bias, const et_half* X, et_half* Y, int T,
@@ -572,15 +639,16 @@ int et_linear_tile_packed_fwd(const int32_t* row_ptr, const uint32_t* pk_mask, c
 // ---- plan-time choice between the tile kernel and dense math -------------------------------
 // A 128 x 16 x 16 tensor-core product occupies the tensor pipe for about 45 cycles on B200
 // whatever its operands' source, against 8 cycles of arithmetic, and every panel of the tile
-// kernel streams the whole activation matrix like a 128-wide dense tile does.  Measured at 2048
-// tokens on BERT-base shapes the packed tile kernel reaches the dense GEMM's time only at about
-// 97 % sparsity (0.75-1.03 x at 80 %, 0.81-1.15 x at 90 %, 0.91-1.20 x at 95 %, the upper
-// figures for the widest output), so weights with more than 2 % of their tiles stored are
-// expanded once and served by the dense GEMM.
+// kernel streams the whole activation matrix.  Measured at 2048 tokens on BERT-base shapes
+// (packed tile kernel time / dense GEMM time): 768 -> 3072 with two panels per CTA 1.21 at
+// 80 % sparsity, 0.98 at 90 %, 0.88 at 95 %; 768 -> 2304 0.97 / 0.87 / 0.83; 768 -> 768 and
+// 3072 -> 768 never below 1.0 up to 97 %.  So weights are expanded once and served by the dense
+// GEMM unless they are both wide and sparse enough.
 int et_tile_prefer_dense(int in, int out, int nnz_tiles) {
     if (in <= 0 || out <= 0 || (in & 15) || (out & 15)) return 0;
     const double total = static_cast<double>(in >> 4) * (out >> 4);
-    return nnz_tiles > 0.02 * total ? 1 : 0;
+    const double keep = out >= 3072 ? 0.10 : (out >= 2048 ? 0.15 : 0.02);
+    return nnz_tiles > keep * total ? 1 : 0;
 }
 
 int et_tile_densify(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,
