@@ -241,3 +241,25 @@ def test_bad_arguments_are_rejected_before_launch(et, cuda):
                                       vp(x.data_ptr()), 16, 32, 16, 0, None)
     assert st == -2
     assert et.device_error() == 0
+
+
+def test_dense_plan_sweep(et, orc, cuda):
+    """Shapes chosen to hit every branch of the tile plan (single-tile CTAs, persistent 128 / 192
+    / 256-wide tiles, CTA pairs of both widths) with ragged edges, through the automatic
+    dispatch, against the oracle."""
+    shapes = [
+        (2048, 768, 3072, 2),   # persistent 192-wide tiles
+        (2048, 3072, 768, 0),   # 256 x 128 CTA pairs (long K, few tiles)
+        (2048, 1024, 4096, 1),  # 256 x 256 CTA pairs
+        (2064, 784, 2320, 0),   # single-tile CTAs, every dimension ragged
+        (4104, 272, 3088, 2),   # many tiles, ragged
+        (130, 2048, 144, 0),    # long K, one tile column, M just above one tile
+        (255, 4096, 4096, 1),   # M below the pair threshold
+        (257, 2064, 528, 0),    # M just above it, pair tiles half empty
+        (24, 48, 48, 2),        # everything smaller than one tile
+    ]
+    for i, (T, inn, out, act) in enumerate(shapes):
+        x, w, b = _case(et, 300 + i, T, inn, out)
+        y = et.linear_dense(_dev(x, cuda), _dev(w, cuda), _dev(b, cuda), act)
+        assert et.device_error() == 0
+        assert_close(_host(y), orc.linear_dense(x, w, b, act), f"plan sweep {T}x{inn}x{out} act{act}")
