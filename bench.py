@@ -34,7 +34,7 @@ SEED = 2021
 KERNELS_PER_LAYER = 6  # QKV + attention (fused), O, skip-LN, FFN1(+GELU), FFN2, skip-LN
 # dram__bytes_read + dram__bytes_write of one FFN1 launch from the ncu capture summarised in
 # profiles/ncu_full_one_layer_bert_base_b16.md (cold operands; the result stays in L2)
-FFN1_DRAM_TRAFFIC_BYTES = 7944704
+FFN1_DRAM_TRAFFIC_BYTES = 7931392
 
 
 def flops_per_sequence(keep_lin: float = 1.0) -> float:
