@@ -134,6 +134,10 @@ template <> class Linear<col_mat> {
     }
 };
 
+// Tile-pruned Linear.  At construction the weight is prepared once for the kernel that will
+// serve it (the choice et_tile_prefer_dense makes): expanded to a dense matrix for the GEMM, or
+// re-packed (tiles of a panel and chunk contiguous, pre-swizzled) for the tile kernel.  The
+// reference's arrays stay available in `weight`.
 template <> class Linear<tile_mat> {
   public:
     const uint32_t in_size;
@@ -143,23 +147,74 @@ template <> class Linear<tile_mat> {
     culib::CUDA_ptr<half> bias;
 
     Linear(int _in_size, int _out_size, const tile_mat& w, const half* b, int _size)
-        : in_size(_in_size), out_size(_out_size), size(_size), weight(w), bias(b, _out_size) {}
+        : in_size(_in_size), out_size(_out_size), size(_size), weight(w), bias(b, _out_size) {
+        prepare();
+    }
     Linear(int _in_size, int _out_size, const tile_mat& w, culib::CUDA_ptr<half>& b, int _size)
-        : in_size(_in_size), out_size(_out_size), size(_size), weight(w), bias(b) {}
+        : in_size(_in_size), out_size(_out_size), size(_size), weight(w), bias(b) {
+        prepare();
+    }
     Linear(int _in_size, int _out_size, tile_mat&& w, const half* b, int _size)
         : in_size(_in_size), out_size(_out_size), size(_size), weight(std::move(w)),
-          bias(b, _out_size) {}
+          bias(b, _out_size) {
+        prepare();
+    }
     Linear(Linear<tile_mat>&& o)
         : in_size(o.in_size), out_size(o.out_size), size(o.size), weight(std::move(o.weight)),
-          bias(std::move(o.bias)) {}
+          bias(std::move(o.bias)), dense(std::move(o.dense)), pk_mask(std::move(o.pk_mask)),
+          pk_off(std::move(o.pk_off)), pk_tiles(std::move(o.pk_tiles)) {}
     void forward(half* output, const half* const input, cudaStream_t stream = 0) {
         forward_act(output, input, ET_ACT_NONE, stream);
     }
     void forward_act(half* output, const half* input, int act, cudaStream_t stream = 0) {
-        etChk(et_linear_tile_fwd(weight.row_ptr.get(), weight.row_offset.get(),
-                                 et_ptr(weight.data.get()), weight.num_blk, et_ptr(bias.get()),
-                                 et_ptr(input), et_ptr(output), size, (int)in_size, (int)out_size,
-                                 act, stream));
+        if (dense) {
+            etChk(et_linear_dense_fwd(et_ptr(input), et_ptr(dense->get()), et_ptr(bias.get()),
+                                      et_ptr(output), size, (int)in_size, (int)out_size, act,
+                                      stream));
+        } else if (pk_tiles) {
+            etChk(et_linear_tile_packed_fwd(
+                weight.row_ptr.get(), reinterpret_cast<const uint32_t*>(pk_mask->get()),
+                pk_off->get(), et_ptr(pk_tiles->get()), weight.num_blk, et_ptr(bias.get()),
+                et_ptr(input), et_ptr(output), size, (int)in_size, (int)out_size, act, stream));
+        } else {
+            etChk(et_linear_tile_fwd(weight.row_ptr.get(), weight.row_offset.get(),
+                                     et_ptr(weight.data.get()), weight.num_blk, et_ptr(bias.get()),
+                                     et_ptr(input), et_ptr(output), size, (int)in_size,
+                                     (int)out_size, act, stream));
+        }
+    }
+
+  private:
+    std::unique_ptr<culib::CUDA_ptr<half>> dense;     // expanded weight [out, in]
+    std::unique_ptr<culib::CUDA_ptr<int>> pk_mask;    // per (panel, chunk) presence bits
+    std::unique_ptr<culib::CUDA_ptr<int>> pk_off;     // per (panel, chunk) first tile
+    std::unique_ptr<culib::CUDA_ptr<half>> pk_tiles;  // tiles in packed order
+
+    void prepare() {
+        if (weight.num_blk <= 0) return;
+        if (et_tile_prefer_dense((int)in_size, (int)out_size, weight.num_blk)) {
+            dense = std::make_unique<culib::CUDA_ptr<half>>((size_t)in_size * out_size);
+            etChk(et_tile_densify(weight.row_ptr.get(), weight.row_offset.get(),
+                                  et_ptr(weight.data.get()), weight.num_blk, (int)in_size,
+                                  (int)out_size, et_ptr(dense->get()), 0));
+            cudaChk(cudaStreamSynchronize(0));
+            return;
+        }
+        int npanel = 0, nchunk = 0;
+        etChk(et_tile_pack_dims((int)in_size, (int)out_size, &npanel, &nchunk));
+        const std::vector<int> rp = weight.row_ptr.to_host(), ro = weight.row_offset.to_host();
+        std::vector<uint32_t> mask((size_t)npanel * nchunk);
+        std::vector<int> off((size_t)npanel * nchunk), perm((size_t)weight.num_blk);
+        etChk(et_tile_pack_plan(rp.data(), ro.data(), weight.num_blk, (int)in_size, (int)out_size,
+                                mask.data(), off.data(), perm.data()));
+        pk_mask = std::make_unique<culib::CUDA_ptr<int>>(reinterpret_cast<const int*>(mask.data()),
+                                                         mask.size());
+        pk_off = std::make_unique<culib::CUDA_ptr<int>>(off.data(), off.size());
+        culib::CUDA_ptr<int> dperm(perm.data(), perm.size());
+        pk_tiles = std::make_unique<culib::CUDA_ptr<half>>((size_t)weight.num_blk * 256);
+        etChk(et_tile_pack_tiles(et_ptr(weight.data.get()), dperm.get(), weight.num_blk,
+                                 et_ptr(pk_tiles->get()), 0));
+        cudaChk(cudaStreamSynchronize(0));
     }
 };
 

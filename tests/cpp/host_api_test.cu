@@ -322,7 +322,8 @@ int main() {
     try {
         closed_form_linear<base_mat>("base_mat", 0.f);
         closed_form_linear<tile_mat>("tile_mat", 0.f);
-        closed_form_linear<tile_mat>("tile_mat", 0.5f);
+        closed_form_linear<tile_mat>("tile_mat", 0.5f);   // expanded to dense at construction
+        closed_form_linear<tile_mat>("tile_mat", 0.99f);  // sparse enough for the packed tile kernel
         closed_form_linear<row_mat>("row_mat", 0.5f);
         closed_form_linear<col_mat>("col_mat", 0.5f);
         closed_form_linear<mat1x16>("mat1x16", 0.9f);
@@ -331,7 +332,7 @@ int main() {
         test_encoder_tile(2, 128, 1);
         test_encoder_tile(3, 80, 0);
         test_attention_variants();
-    test_attention_fused_qkv_dense();
+        test_attention_fused_qkv_dense();
         test_errors();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());
