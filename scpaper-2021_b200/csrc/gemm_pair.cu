@@ -195,7 +195,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                 }
             }
-            (void)issued;
+            if (*abort_flag && rank == 0) {
+                // Let copies in flight land before shared memory is released: both CTAs' loads
+                // signal the leader's barriers, and the peer cannot leave before the leader has
+                // reached the final cluster barrier, so this wait covers the peer's copies too.
+                for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+                    for (uint32_t sp = 0; sp < ET_SPIN_LIMIT; ++sp)
+                        if (mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1)) break;
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA) ----------------
