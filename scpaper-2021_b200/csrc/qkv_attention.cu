@@ -46,6 +46,9 @@ struct QkvAttnArgs {
     int* err_word;
 };
 
+// MASK: the mask kind, compiled in (run-time branches around the softmax code cost issue
+// efficiency, as they did in the GEMM epilogues).
+template <int MASK>
 __global__ void __launch_bounds__(QA_THREADS, 2)
 qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                      const __grid_constant__ CUtensorMap tmZ, const QkvAttnArgs a) {
@@ -75,7 +78,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     const int nkb = (a.hidden + 63) >> 6;
 
     int kv_len = a.seq;
-    if (a.mask_kind == ET_MASK_PADDING) {
+    if (MASK == ET_MASK_PADDING) {
         kv_len = a.valid_len[b];
         kv_len = kv_len < 0 ? 0 : (kv_len > a.seq ? a.seq : kv_len);
     }
@@ -270,15 +273,15 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             tmem_ld_wait_regs(v0);
             tmem_ld_wait_regs(v1);
             const int kbase = hf * 64;
-            need_mask = (128 > kv_len) || (a.mask_kind == ET_MASK_ADDITIVE) ||
-                        (a.mask_kind == ET_MASK_CAUSAL);
+            need_mask = (128 > kv_len) || (MASK == ET_MASK_ADDITIVE) ||
+                        (MASK == ET_MASK_CAUSAL);
             if (need_mask) {
-                const __half* mrow = (a.mask_kind == ET_MASK_ADDITIVE && r < a.seq)
+                const __half* mrow = (MASK == ET_MASK_ADDITIVE && r < a.seq)
                                          ? a.mask + static_cast<size_t>(r) * a.seq
                                          : nullptr;
                 auto fix = [&](uint32_t raw, int kc) -> uint32_t {
                     float s = __uint_as_float(raw) * a.scale_log2;
-                    if (kc >= kv_len || (a.mask_kind == ET_MASK_CAUSAL && kc > r)) s = NINF;
+                    if (kc >= kv_len || (MASK == ET_MASK_CAUSAL && kc > r)) s = NINF;
                     else if (mrow) s += __half2float(__ldg(mrow + kc)) * 1.4426950408889634f;
                     mx = fmaxf(mx, s);
                     return __float_as_uint(s);
@@ -415,15 +418,21 @@ int launch_qkv_attention(const __half* X, const __half* Wqkv, const __half* bqkv
         if ((st = make_tensor_map_f16(&tmZ, Z, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != ET_OK)
             return st;
     }
-    static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(qkv_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 QA_SMEM) != cudaSuccess)
-            return ET_ERR_CUDA;
-        attr_set[dev] = true;
-    }
+    auto go = [&](auto kern, int slot, const QkvAttnArgs& args) -> int {
+        static bool attr_set[4][64] = {};
+        if (dev >= 0 && dev < 64 && !attr_set[slot][dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QA_SMEM) !=
+                cudaSuccess)
+                return ET_ERR_CUDA;
+            attr_set[slot][dev] = true;
+        }
+        return launch_kernel(kern, dim3(nhead, batch), dim3(QA_THREADS), QA_SMEM, stream, tmX, tmW,
+                             tmZ, args) == cudaSuccess
+                   ? ET_OK
+                   : ET_ERR_CUDA;
+    };
     QkvAttnArgs a;
     a.bias = bqkv;
     a.mask = mask;
@@ -434,10 +443,12 @@ int launch_qkv_attention(const __half* X, const __half* Wqkv, const __half* bqkv
     a.mask_kind = mask_kind;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.err_word = err;
-    return launch_kernel(qkv_attention_kernel, dim3(nhead, batch), dim3(QA_THREADS), QA_SMEM, stream,
-                         tmX, tmW, tmZ, a) == cudaSuccess
-               ? ET_OK
-               : ET_ERR_CUDA;
+    switch (mask_kind) {
+        case ET_MASK_CAUSAL: return go(qkv_attention_kernel<ET_MASK_CAUSAL>, 1, a);
+        case ET_MASK_PADDING: return go(qkv_attention_kernel<ET_MASK_PADDING>, 2, a);
+        case ET_MASK_ADDITIVE: return go(qkv_attention_kernel<ET_MASK_ADDITIVE>, 3, a);
+        default: return go(qkv_attention_kernel<ET_MASK_NONE>, 0, a);
+    }
 }
 
 }  // namespace et
