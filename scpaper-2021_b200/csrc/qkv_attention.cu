@@ -22,6 +22,17 @@
 
 namespace et {
 
+// Bring-up aid: with -DET_TIMELINE every CTA records clock64() at a few points of its life.
+#ifdef ET_TIMELINE
+__device__ long long et_qa_timeline[4096 * 16];
+#define QA_TL(slot)                                                                      \
+    do {                                                                                 \
+        et_qa_timeline[(blockIdx.y * gridDim.x + blockIdx.x) * 16 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define QA_TL(slot) ((void)0)
+#endif
+
 namespace {
 
 constexpr int QA_THREADS = 320;
@@ -84,6 +95,17 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     }
 
     if (threadIdx.x == 0) {
+        QA_TL(0);
+#ifdef ET_TIMELINE
+        {
+            unsigned smid;
+            unsigned long long gt;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+            et_qa_timeline[(blockIdx.y * gridDim.x + blockIdx.x) * 16 + 13] = smid;
+            et_qa_timeline[(blockIdx.y * gridDim.x + blockIdx.x) * 16 + 14] = (long long)gt;
+        }
+#endif
         tma_prefetch_desc(&tmX);
         tma_prefetch_desc(&tmW);
         for (int s = 0; s < QA_STAGES; ++s) {
@@ -109,6 +131,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     const uint32_t tmem_S = tmem_base;
     const uint32_t tmem_O = tmem_base + 192;
     pdl_launch_dependents();
+    if (threadIdx.x == 0) QA_TL(1);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -126,6 +149,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 load_w(i, i);
             }
             pdl_wait();
+            QA_TL(2);
             for (int i = 0; i < pre; ++i)
                 tma_load_3d(smem + i * QA_STAGE, &tmX, &full_bar[i], i * 64, 0, b);
             int s = pre % QA_STAGES;
@@ -145,6 +169,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     ph ^= 1u;
                 }
             }
+            QA_TL(3);
             if (*abort_flag) {
                 // let copies in flight land before the ring is reused or released
                 for (int i = issued > QA_STAGES ? issued - QA_STAGES : 0; i < issued; ++i)
@@ -168,6 +193,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     break;
                 }
                 tc_fence_after_sync();
+                if (i == 0) QA_TL(4);
                 const uint32_t a_addr = smem_u32(smem + s * QA_STAGE);
                 const uint32_t b_addr = a_addr + QA_ATOM;
 #pragma unroll
@@ -183,6 +209,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             }
             if (ok) {
                 mma_commit(proj_full);
+                QA_TL(5);
                 ok = mbar_wait_bounded(qkv_ready, 0, abort_flag);
                 if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
             }
@@ -234,6 +261,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
+            if (threadIdx.x == 64) QA_TL(6);
             // this warp's three 32-column chunks of Q | K | V: accumulator -> fp16 operand tile
             uint32_t ra[32], rb[32];
             const int c0 = hf * 3;
@@ -255,6 +283,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             tc_fence_before_sync();
             fence_proxy_async_smem();  // the tiles are read by the tensor core
             mbar_arrive(qkv_ready);
+            if (threadIdx.x == 64) QA_TL(7);
 
             ok = mbar_wait_bounded(s_full, 0, abort_flag);
             if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_SOFTMAX);
@@ -268,6 +297,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         bool need_mask = false;
         if (ok) {
             tc_fence_after_sync();
+            if (threadIdx.x == 64) QA_TL(8);
             tmem_ld32(tmem_S + lane_off + hf * 64, v0);
             tmem_ld32(tmem_S + lane_off + hf * 64 + 32, v1);
             tmem_ld_wait_regs(v0);
@@ -325,6 +355,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             tc_fence_before_sync();
             fence_proxy_async_smem();
             mbar_arrive(p_full);
+            if (threadIdx.x == 64) QA_TL(9);
             xsum[hf * 128 + r] = l_part;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(QA_SM_THREADS) : "memory");
@@ -336,6 +367,7 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after_sync();
+                if (threadIdx.x == 64) QA_TL(10);
                 // this warp's 32 of the 64 output columns -> staging tile (P is dead by now)
                 uint32_t o[32];
                 tmem_ld32(tmem_O + lane_off + hf * 32, o);
@@ -359,11 +391,13 @@ qkv_attention_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             tma_store_3d(&tmZ, sP + qd * 32 * 128, h * 64, qd * 32, b);
             tma_store_commit();
             tma_store_wait_read();
+            if (qd == 0) QA_TL(11);
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) QA_TL(12);
     if (warp == 1) tmem_dealloc(tmem_base, QA_TMEM);
 }
 
