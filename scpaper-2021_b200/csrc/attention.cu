@@ -10,8 +10,10 @@
 // computes exp2 (with log2(e)/sqrt(dh) folded into one FMA), keeps a running max / partial
 // sum (online softmax across key blocks), writes its fp16 probabilities into the
 // 128-byte-swizzled shared-memory tile that is the A operand of the second product and
-// rescales its share of the output accumulator when the running max moved.  The MMA thread
-// accumulates O += P.V with V consumed directly in its row-major (MN-major) layout.  After
+// rescales its share of the output accumulator when the running max was raised (only when a
+// block exceeds it by more than 2^8, so a few times per row).  The MMA thread issues the next
+// block's Q.K^T ahead of O += P.V (V consumed directly in its row-major, MN-major layout), so
+// the scores of block j+1 are ready when the softmax warps finish block j.  After
 // the last block the row sums are combined, each thread scales its share of the output
 // columns and the tile leaves through a swizzled staging buffer and TMA stores.
 // All waits are bounded.
@@ -43,6 +45,38 @@ constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 fp16, one 128-byte-swizz
 constexpr int TMEM_COLS_ATT = 256;     // S: columns [0,128), O: columns [128, 128 + v_n)
 constexpr int EXTRA_BYTES = 256 + 6 * 128 * 4;   // barriers + max / sum exchange arrays
 
+// The running maximum is only raised when a block's maximum exceeds it by more than this many
+// powers of two: probabilities then stay below 2^8 (exact in fp16's range, fp32 sums), the final
+// division by the row sum removes the common factor, and the output accumulator is rescaled
+// in tensor memory a few times per row instead of after most key blocks.
+constexpr float RESCALE_SLACK = 8.0f;
+
+// 64 scores of one query row -> fp16 probabilities in the swizzled P tile; returns their sum.
+// SCALED: the scores were already scaled and masked in place (log2 domain).
+template <bool SCALED>
+__device__ __forceinline__ float store_probabilities(const uint32_t (&v0)[32],
+                                                     const uint32_t (&v1)[32], float scale_log2,
+                                                     float neg_m, uint8_t* prow, int r) {
+    float rowsum = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float raw = __uint_as_float(g < 4 ? v0[g * 8 + i] : v1[(g - 4) * 8 + i]);
+            p[i] = exp2_approx(SCALED ? raw + neg_m : fmaf(raw, scale_log2, neg_m));
+            rowsum += p[i];
+        }
+        uint4 pk;
+        pk.x = pack_half2(p[0], p[1]);
+        pk.y = pack_half2(p[2], p[3]);
+        pk.z = pack_half2(p[4], p[5]);
+        pk.w = pack_half2(p[6], p[7]);
+        *reinterpret_cast<uint4*>(prow + ((g ^ (r & 7)) * 16)) = pk;
+    }
+    return rowsum;
+}
+
 struct AttnArgs {
     __half* Z;
     const __half* mask;
@@ -60,6 +94,9 @@ struct AttnArgs {
     int tma_out;    // 1: the output tile is written with TMA stores (dense V, dh_v % 64 == 0)
 };
 
+// MASK: the mask kind, compiled in (keeps the mask bookkeeping out of the registers of the
+// kinds that do not need it).
+template <int MASK>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmZ,
@@ -107,12 +144,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int nva = (v_n + 63) >> 6;  // 64-feature atoms of V actually loaded
 
     int kv_len = a.seq;
-    if (a.mask_kind == ET_MASK_PADDING) {
+    if (MASK == ET_MASK_PADDING) {
         kv_len = a.valid_len[b];
         kv_len = kv_len < 0 ? 0 : (kv_len > a.seq ? a.seq : kv_len);
     }
     int n_kv = (kv_len + BKV - 1) / BKV;
-    if (a.mask_kind == ET_MASK_CAUSAL) {
+    if (MASK == ET_MASK_CAUSAL) {
         const int last_q = (q0 + BQ - 1 < a.seq ? q0 + BQ - 1 : a.seq - 1);
         const int lim = last_q / BKV + 1;
         n_kv = n_kv < lim ? n_kv : lim;
@@ -158,7 +195,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n_kv; ++j) {
                 const uint32_t ph = j & 1;
-                if (!mbar_wait_bounded(k_empty, ph ^ 1, abort_flag)) {
+                if (!mbar_wait_bounded_relaxed(k_empty, ph ^ 1, abort_flag)) {
                     report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_PRODUCER);
                     break;
                 }
@@ -166,7 +203,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 for (int t = 0; t < nqa; ++t)
                     tma_load_3d(sK + t * ATOM_BYTES, &tmK, k_full, h * a.dh_qk + t * 64, j * BKV, b);
                 ++k_issued;
-                if (!mbar_wait_bounded(v_empty, ph ^ 1, abort_flag)) {
+                if (!mbar_wait_bounded_relaxed(v_empty, ph ^ 1, abort_flag)) {
                     report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_PRODUCER);
                     break;
                 }
@@ -197,14 +234,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                            p_addr = smem_u32(sP);
             bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
             if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
-            for (int j = 0; ok && j < n_kv; ++j) {
+            // S_j = Q.K_j^T; the score block is free as soon as the softmax warps hold it in
+            // registers, so S_{j+1} is issued BEFORE P_j.V_j and runs under softmax(j).
+            auto issue_s = [&](int j) -> bool {
                 const uint32_t ph = j & 1;
-                ok = mbar_wait_bounded(k_full, ph, abort_flag) &&
-                     mbar_wait_bounded(s_free, ph ^ 1, abort_flag);
-                if (!ok) {
-                    report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
-                    break;
-                }
+                if (!(mbar_wait_bounded(k_full, ph, abort_flag) &&
+                      mbar_wait_bounded(s_free, ph ^ 1, abort_flag)))
+                    return false;
                 tc_fence_after_sync();
                 const int ksteps = a.dh_qk >> 4;
                 for (int kk = 0; kk < ksteps; ++kk) {
@@ -215,9 +251,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 mma_commit(s_full);
                 mma_commit(k_empty);
-                if (j == 0) ET_TL(3);
-
-                ok = mbar_wait_bounded(p_full, ph, abort_flag) &&
+                return true;
+            };
+            if (ok) {
+                ok = issue_s(0);
+                if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
+                ET_TL(3);
+            }
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const uint32_t ph = j & 1;
+                if (j + 1 < n_kv) ok = issue_s(j + 1);
+                ok = ok && mbar_wait_bounded(p_full, ph, abort_flag) &&
                      mbar_wait_bounded(v_full, ph, abort_flag);
                 if (!ok) {
                     report_error(a.err_word, abort_flag, DEV_TIMEOUT_ATTN_MMA);
@@ -272,41 +316,42 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc_fence_after_sync();
             if (threadIdx.x == 64 && j == 0) ET_TL(4);
 
-            // this thread's 64 scores, read once
-            uint32_t v0[32], v1[32];
-            tmem_ld32(tmem_S + lane_off + hf * 64, v0);
-            tmem_ld32(tmem_S + lane_off + hf * 64 + 32, v1);
-            tmem_ld_wait_regs(v0);
-            tmem_ld_wait_regs(v1);
-            tc_fence_before_sync();
-            mbar_arrive(s_free);  // S may be overwritten by the next Q.K^T
-
             const int kbase = j * BKV + hf * 64;
-            const bool need_mask = (j * BKV + BKV > kv_len) || (a.mask_kind == ET_MASK_ADDITIVE) ||
-                                   (a.mask_kind == ET_MASK_CAUSAL && j * BKV + BKV - 1 > q0);
+            const bool need_mask = (j * BKV + BKV > kv_len) || (MASK == ET_MASK_ADDITIVE) ||
+                                   (MASK == ET_MASK_CAUSAL && j * BKV + BKV - 1 > q0);
+            // general path: a score scaled and masked (log2 domain)
+            const __half* mrow = (MASK == ET_MASK_ADDITIVE && qrow < a.seq)
+                                     ? a.mask + static_cast<size_t>(qrow) * a.seq
+                                     : nullptr;
+            auto score = [&](uint32_t raw, int kc) -> float {
+                float s = __uint_as_float(raw) * a.scale_log2;
+                if (kc >= kv_len || (MASK == ET_MASK_CAUSAL && kc > qrow)) s = NINF;
+                else if (MASK == ET_MASK_ADDITIVE && mrow)
+                    s += __half2float(__ldg(mrow + kc)) * 1.4426950408889634f;
+                return s;
+            };
+
+            // pass 1: the maximum of this thread's 64 scores.  The scores are not kept: they are
+            // read from tensor memory again for pass 2 (cheap), which keeps 64 registers free
+            // across the exchange and the accumulator rescale.
             float mx = NINF;
-            if (need_mask) {
-                // general path: scores are scaled and masked in place (log2 domain)
-                const __half* mrow = (a.mask_kind == ET_MASK_ADDITIVE && qrow < a.seq)
-                                         ? a.mask + static_cast<size_t>(qrow) * a.seq
-                                         : nullptr;
-                auto fix = [&](uint32_t raw, int kc) -> uint32_t {
-                    float s = __uint_as_float(raw) * a.scale_log2;
-                    if (kc >= kv_len || (a.mask_kind == ET_MASK_CAUSAL && kc > qrow)) s = NINF;
-                    else if (mrow) s += __half2float(__ldg(mrow + kc)) * 1.4426950408889634f;
-                    mx = fmaxf(mx, s);
-                    return __float_as_uint(s);
-                };
+            {
+                uint32_t v0[32], v1[32];
+                tmem_ld32(tmem_S + lane_off + hf * 64, v0);
+                tmem_ld32(tmem_S + lane_off + hf * 64 + 32, v1);
+                tmem_ld_wait_regs(v0);
+                tmem_ld_wait_regs(v1);
+                if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v0[i] = fix(v0[i], kbase + i);
+                    for (int i = 0; i < 32; ++i)
+                        mx = fmaxf(mx, fmaxf(score(v0[i], kbase + i), score(v1[i], kbase + 32 + i)));
+                } else {
+                    // fast path: max of the raw scores, the (positive) scale applied once
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v1[i] = fix(v1[i], kbase + 32 + i);
-            } else {
-                // fast path: max of the raw scores, the (positive) scale applied once
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
-                mx *= a.scale_log2;
+                    for (int i = 0; i < 32; ++i)
+                        mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+                    mx *= a.scale_log2;
+                }
             }
             // combine with the other half of the row
             xmax[(ph * 2 + hf) * 128 + r] = mx;
@@ -314,9 +359,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mx = fmaxf(mx, xmax[(ph * 2 + (hf ^ 1)) * 128 + r]);
             if (threadIdx.x == 64 && j == 0) ET_TL(5);
 
-            const float m_new = fmaxf(m_run, mx);
+            // raise the running maximum only when it is -inf or the block exceeds it by more
+            // than the slack (both halves of a row take the same decision: same inputs)
+            const bool raise = (m_run == NINF) || (mx > m_run + RESCALE_SLACK);
+            const float m_new = raise ? fmaxf(m_run, mx) : m_run;
             const float m_use = (m_new == NINF) ? 0.f : m_new;
-            const float alpha = exp2_approx(m_run - m_use);  // 0 when m_run = -inf
+            const float alpha = raise ? exp2_approx(m_run - m_use) : 1.0f;  // 0 when m_run = -inf
 
             if (j > 0) {
                 // P and O of the previous block must have been consumed / produced
@@ -339,27 +387,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
 
-            // probabilities -> shared memory (A operand of P.V, atom `hf`), partial row sum
-            float rowsum = 0.f;
+            // pass 2: probabilities -> shared memory (A operand of P.V, atom `hf`), partial sum
             uint8_t* prow = sP + hf * ATOM_BYTES + r * 128;
-            const float neg_m = -m_use;
+            float rowsum;
+            {
+                uint32_t v0[32], v1[32];
+                tmem_ld32(tmem_S + lane_off + hf * 64, v0);
+                tmem_ld32(tmem_S + lane_off + hf * 64 + 32, v1);
+                tmem_ld_wait_regs(v0);
+                tmem_ld_wait_regs(v1);
+                tc_fence_before_sync();
+                mbar_arrive(s_free);  // S may be overwritten by the next Q.K^T
+                if (need_mask) {
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                float p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t raw = g < 4 ? v0[g * 8 + i] : v1[(g - 4) * 8 + i];
-                    const float arg = need_mask ? __uint_as_float(raw) + neg_m
-                                                : fmaf(__uint_as_float(raw), a.scale_log2, neg_m);
-                    p[i] = exp2_approx(arg);
-                    rowsum += p[i];
+                    for (int i = 0; i < 32; ++i) {
+                        v0[i] = __float_as_uint(score(v0[i], kbase + i));
+                        v1[i] = __float_as_uint(score(v1[i], kbase + 32 + i));
+                    }
+                    rowsum = store_probabilities<true>(v0, v1, a.scale_log2, -m_use, prow, r);
+                } else {
+                    rowsum = store_probabilities<false>(v0, v1, a.scale_log2, -m_use, prow, r);
                 }
-                uint4 pk;
-                pk.x = pack_half2(p[0], p[1]);
-                pk.y = pack_half2(p[2], p[3]);
-                pk.z = pack_half2(p[4], p[5]);
-                pk.w = pack_half2(p[6], p[7]);
-                *reinterpret_cast<uint4*>(prow + ((g ^ (r & 7)) * 16)) = pk;
             }
             l_part = l_part * alpha + rowsum;
             m_run = m_new;
@@ -503,15 +551,8 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     const int v_n_max = pruned ? ((7 + dh_v + 15) & ~15) : dh_v;
     const int nqa = (dh_qk + 63) / 64, nva = (v_n_max + 63) / 64;
     const int smem_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + EXTRA_BYTES + 1024;
-    static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (2 * 2 + 3 + 2) * ATOM_BYTES + EXTRA_BYTES + 1024) != cudaSuccess)
-            return ET_ERR_CUDA;
-        attr_set[dev] = true;
-    }
     AttnArgs a;
     a.Z = Z;
     a.mask = mask;
@@ -530,11 +571,27 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     a.nva_max = nva;
     a.tmem_cols = (128 + v_n_max > 256) ? 512 : TMEM_COLS_ATT;
     a.tma_out = tma_out ? 1 : 0;
-    dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
-    return launch_kernel(attention_kernel, grid, dim3(ATT_THREADS), smem_bytes, stream, tmQ, tmK,
-                         tmV, tmZ, a) == cudaSuccess
-               ? ET_OK
-               : ET_ERR_CUDA;
+    const dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
+    auto go = [&](auto kern, int slot) -> int {
+        static bool attr_set[4][64] = {};
+        if (dev >= 0 && dev < 64 && !attr_set[slot][dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (2 * 2 + 3 + 2) * ATOM_BYTES + EXTRA_BYTES + 1024) !=
+                cudaSuccess)
+                return ET_ERR_CUDA;
+            attr_set[slot][dev] = true;
+        }
+        return launch_kernel(kern, grid, dim3(ATT_THREADS), smem_bytes, stream, tmQ, tmK, tmV, tmZ,
+                             a) == cudaSuccess
+                   ? ET_OK
+                   : ET_ERR_CUDA;
+    };
+    switch (mask_kind) {
+        case ET_MASK_CAUSAL: return go(attention_kernel<ET_MASK_CAUSAL>, 1);
+        case ET_MASK_PADDING: return go(attention_kernel<ET_MASK_PADDING>, 2);
+        case ET_MASK_ADDITIVE: return go(attention_kernel<ET_MASK_ADDITIVE>, 3);
+        default: return go(attention_kernel<ET_MASK_NONE>, 0);
+    }
 }
 }  // namespace
 
