@@ -30,6 +30,7 @@ UNIT = "sequences/s"
 WORKLOAD = ("BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, seq 128, dense weights, "
             "all-ones mask")
 HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
+LONG_BATCH, LONG_SEQ = 2, 4096  # secondary per-kernel entry: attention on long sequences
 SEED = 2021
 KERNELS_PER_LAYER = 6  # QKV + attention (fused), O, skip-LN, FFN1(+GELU), FFN2, skip-LN
 # dram__bytes_read + dram__bytes_write of one FFN1 launch from the ncu capture summarised in
@@ -198,6 +199,9 @@ def main():
                     help="groups of sequences that run through the stack on their own streams")
     ap.add_argument("--skip-extras", action="store_true",
                     help="skip the pruned / per-kernel / CPU legs (used under profilers)")
+    ap.add_argument("--attention-only", action="store_true",
+                    help="launch the attention kernel alone (2 sequences of 4096 tokens, three "
+                         "times) and exit: the small case profilers capture")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -224,6 +228,17 @@ def main():
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
             os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.attention_only:
+        qkv = torch.from_numpy(et.synth.normal(1, 70, (LONG_BATCH * LONG_SEQ, 3 * HIDDEN), 1.0)).to(dev)
+        z = torch.empty((LONG_BATCH * LONG_SEQ, HIDDEN), dtype=torch.float16, device=dev)
+        for _ in range(3):
+            et.attention(qkv[:, :HIDDEN], qkv[:, HIDDEN:2 * HIDDEN], qkv[:, 2 * HIDDEN:],
+                         LONG_BATCH, LONG_SEQ, NHEAD, 64, 64, out=z)
+        torch.cuda.synchronize()
+        print(json.dumps({"attention_only": True, "batch": LONG_BATCH, "seq": LONG_SEQ,
+                          "device_error": et.device_error()}))
+        return
 
     job = et.sharding.Job(rank=rank, world=world, device=dev)
 
@@ -382,7 +397,21 @@ def main():
             per_kernel["qkv_attention_fused"] = {
                 "us": sec * 1e6,
                 "tflops": (2.0 * T * HIDDEN * 3 * HIDDEN + 4.0 * BATCH * SEQ * SEQ * HIDDEN) / sec * 1e-12}
-            del xs, wq
+            del xs, wq, qkv, z
+            # the on-the-fly attention kernel where it dominates: long sequences (not part of
+            # the headline workload, whose 128-token sequences take the fused kernel above)
+            TL = LONG_BATCH * LONG_SEQ
+            qkv = [torch.from_numpy(et.synth.normal(1, 70 + i, (TL, 3 * HIDDEN), 1.0)).to(dev)
+                   for i in range(4)]
+            z = [torch.empty((TL, HIDDEN), dtype=torch.float16, device=dev) for _ in range(4)]
+            sec = time_kernel([lambda i=i: et.attention(qkv[i][:, :HIDDEN],
+                                                        qkv[i][:, HIDDEN:2 * HIDDEN],
+                                                        qkv[i][:, 2 * HIDDEN:], LONG_BATCH,
+                                                        LONG_SEQ, NHEAD, 64, 64, out=z[i])
+                               for i in range(4)], rounds=3)
+            per_kernel[f"attention_b{LONG_BATCH}_seq{LONG_SEQ}"] = {
+                "us": sec * 1e6,
+                "tflops": 4.0 * LONG_BATCH * LONG_SEQ * LONG_SEQ * HIDDEN / sec * 1e-12}
             a = [torch.from_numpy(et.synth.normal(1, 90 + i, (T, HIDDEN), 1.0)).to(dev)
                  for i in range(4 * NSETS)]
             o = [torch.empty((T, HIDDEN), dtype=torch.float16, device=dev) for _ in range(4 * NSETS)]
