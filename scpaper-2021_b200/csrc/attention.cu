@@ -126,7 +126,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * BQ;
+    // causal: the last query blocks have the most key blocks; they are launched first so that
+    // the short ones fill the tail of the grid
+    const int q0 = (MASK == ET_MASK_CAUSAL ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * BQ;
     const int h = blockIdx.y;
     const int b = blockIdx.z;
 
