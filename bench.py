@@ -14,6 +14,7 @@ Prints ONE JSON line on rank 0.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -32,7 +33,6 @@ WORKLOAD = ("BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, seq 128
 HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
 LONG_BATCH, LONG_SEQ = 2, 4096  # secondary per-kernel entry: attention on long sequences
 SEED = 2021
-KERNELS_PER_LAYER = 6  # QKV + attention (fused), O, skip-LN, FFN1(+GELU), FFN2, skip-LN
 # dram__bytes_read + dram__bytes_write of one FFN1 launch from the ncu capture summarised in
 # profiles/ncu_full_one_layer_bert_base_b16.md (cold operands; the result stays in L2)
 FFN1_DRAM_TRAFFIC_BYTES = 7931392
@@ -240,6 +240,11 @@ def main():
                           "device_error": et.device_error()}))
         return
 
+    et.lib().et_debug_launch_count.restype = ctypes.c_longlong
+
+    def launch_count():
+        return int(et.lib().et_debug_launch_count())
+
     job = et.sharding.Job(rank=rank, world=world, device=dev)
 
     def barrier():
@@ -259,10 +264,14 @@ def main():
     stream = torch.cuda.Stream(device=dev)
     graph = None
 
+    launches_per_step = [0]
+
     def make_step(st):
         """Returns (callable, graph): one forward of the whole stack on the current stream."""
         with torch.cuda.stream(stream):
+            n0 = launch_count()
             st.forward(x_dev)  # warm: sets kernel attributes before capture
+            launches_per_step[0] = launch_count() - n0  # the library's own host-side count
             stream.synchronize()
             if args.no_graph:
                 return (lambda: st.forward(x_dev)), None
@@ -298,6 +307,8 @@ def main():
 
     final_out = stack.buf[(LAYERS - 1) & 1]
     step_fn, graph = make_step(stack)
+    kernels_per_step = launches_per_step[0]  # BERT-base b16: 4 per layer (projection+attention,
+    # O+LayerNorm, FFN1+GELU, FFN2+LayerNorm)
     sampler = ClockSampler(local_rank)
     sampler.start()
     dt = timed(step_fn, args.steps, sampler=sampler)
@@ -352,7 +363,8 @@ def main():
                        "note": "copy in, stack, copy out on one stream (no overlap)"},
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": x_pinned.numel() * 2, "d2h_bytes_per_step": y_pinned.numel() * 2},
-        "gpu_launches": world * args.steps * LAYERS * KERNELS_PER_LAYER,
+        "gpu_launches": world * args.steps * kernels_per_step,
+        "kernels_per_step": kernels_per_step,
         "stack_tflops": value / world * flops_per_sequence() * 1e-12,
         "stack_frac_of_peak": value / world * flops_per_sequence() * 1e-12 / peaks["bf16_tflops_sustained"],
     }
@@ -378,6 +390,18 @@ def main():
                 sec = time_kernel([lambda i=i: et.linear_dense(a[i], w[i], b, act, out=y[i])
                                    for i in range(NSETS)])
                 per_kernel[name] = {"us": sec * 1e6, "tflops": 2.0 * T * inn * out / sec * 1e-12}
+                if out == HIDDEN:
+                    # the same product with residual + LayerNorm in its epilogue (what the
+                    # stack runs at this batch for the O projection and FFN2)
+                    res = [torch.from_numpy(et.synth.normal(1, 60 + i, (T, out), 1.0)).to(dev)
+                           for i in range(NSETS)]
+                    gm = torch.ones(out, dtype=torch.float16, device=dev)
+                    sec = time_kernel([lambda i=i: et.linear_skip_layernorm(a[i], w[i], b, res[i],
+                                                                            gm, b, out=y[i])
+                                       for i in range(NSETS)])
+                    per_kernel[name + "_layernorm_fused"] = {
+                        "us": sec * 1e6, "tflops": 2.0 * T * inn * out / sec * 1e-12}
+                    del res
             qkv = [torch.from_numpy(et.synth.normal(1, 70 + i, (T, 3 * HIDDEN), 1.0)).to(dev)
                    for i in range(NSETS)]
             z = [torch.empty((T, HIDDEN), dtype=torch.float16, device=dev) for _ in range(NSETS)]

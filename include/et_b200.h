@@ -77,6 +77,17 @@ int et_device_error(int* code);
 int et_linear_dense_fwd(const et_half* X, const et_half* W, const et_half* bias, et_half* Y,
                         int T, int in, int out, int act, et_stream stream);
 
+/* Dense Linear fused with the skip-LayerNorm that follows it:
+ *   out = LayerNorm(X . W^T + bias + resid) * gamma + beta        (eps 1e-5, fp32 statistics)
+ * in one kernel; the pre-normalisation activations never reach memory.  out: 256 .. 1024 in
+ * steps of 128 (ET_ERR_SHAPE otherwise: use et_linear_dense_fwd + et_skip_layernorm_fwd);
+ * bias and resid may be NULL; `result` must not alias X or resid.  Replaces the pair
+ * Linear<base_mat>::forward + SkipLayerNorm::forward of the encoder layer (Encoder/Encoder.h:
+ * the O projection and FFN2, each followed by SkipLayerNorm/SkipLayerNorm.cu:73-82). */
+int et_linear_skip_layernorm_fwd(const et_half* X, const et_half* W, const et_half* bias,
+                                 const et_half* resid, const et_half* gamma, const et_half* beta,
+                                 et_half* result, int T, int in, int out, et_stream stream);
+
 /* 16x16 tile-CSR weights: row_ptr[out/16 + 1], row_off[nnz] (input block column,
  * ascending inside a block row), tiles[nnz][16][16] row-major [out_local][in_local].
  * Only stored tiles are loaded.  Stands in for Linear<tile_mat>::forward

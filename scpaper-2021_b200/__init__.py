@@ -22,7 +22,7 @@ FMT_DENSE, FMT_TILE, FMT_TILE_PACKED = 0, 1, 2
 # Every symbol include/et_b200.h declares (checked by the CPU test-suite against the header).
 ABI_SYMBOLS = [
     "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
-    "et_linear_dense_fwd", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
+    "et_linear_dense_fwd", "et_linear_skip_layernorm_fwd", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
     "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_tile_prefer_dense", "et_tile_densify",
     "et_linear_row_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
@@ -259,6 +259,17 @@ def skip_layernorm(src, skip, gamma, beta, out=None):
     check(lib().et_skip_layernorm_fwd(_p(src), _p(skip), _p(gamma), _p(beta), _p(out), c_int(rows),
                                       c_int(size), _stream()), "et_skip_layernorm_fwd")
     return out
+
+
+def linear_skip_layernorm(x, w, bias, resid, gamma, beta, out=None):
+    """LayerNorm(x w^T + bias + resid) * gamma + beta in one kernel (out: 256..1024, % 128)."""
+    T, inn = x.shape
+    n = w.shape[0]
+    y = _empty((T, n), x) if out is None else out
+    check(lib().et_linear_skip_layernorm_fwd(_p(x), _p(w), _p(bias), _p(resid), _p(gamma),
+                                             _p(beta), _p(y), c_int(T), c_int(inn), c_int(n),
+                                             _stream()), "et_linear_skip_layernorm_fwd")
+    return y
 
 
 def layernorm(src, gamma, beta):

@@ -61,6 +61,10 @@ enum : int {
 
 #if defined(__CUDACC__)
 
+// Every kernel launch of the library is counted on the host (et_debug_launch_count), so that a
+// caller can state how many kernels one call issued.
+void count_launch();
+
 // Launches `kernel` with the programmatic-stream-serialization attribute when PDL is on.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -75,6 +79,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    count_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -31,6 +31,21 @@ struct LayerBuffers {
 // output tiles and a long K leave most SMs idle unless K is split.
 int g_force_splits = 0;  // test hook: 0 = automatic
 bool g_qkv_fusion = true;  // test hook: false = always the separate projection + attention
+// test hook: which dense Linear + skip-LayerNorm pairs run as one kernel (gemm_ln.cu):
+// -1 = automatic, otherwise a mask: 1 = the O projection, 2 = FFN2
+int g_ln_fusion = -1;
+
+// The fused kernel computes 128 x 128 tiles, one per CTA.  Measured on B200: while all its CTAs
+// fit the GPU at once it beats the separate GEMM + LayerNorm (BERT-base, 2048 tokens: 8.0 vs
+// 10.8 us for the O projection, 15.3 vs 18.4 us for FFN2, +10 % on the whole stack); with
+// several waves of CTAs the wider tiles and CTA pairs of the plain GEMM win by more than the
+// LayerNorm launch costs (8192 tokens: -3 %).
+int ln_fusion_mask(int T, int hidden) {
+    if (g_ln_fusion >= 0) return g_ln_fusion;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    const long ctas = static_cast<long>((T + 127) / 128) * (hidden / 128);
+    return ctas <= sms ? 3 : 0;
+}
 
 // Split-K on CTA pairs: 256 x 256 pair tiles, as many K slices as SM pairs allow.  Returns 0
 // when the pair form does not apply.  Measured on B200 at BERT-base sizes the fp32 partial
@@ -124,6 +139,7 @@ void et_debug_force_ffn2_splits(int n) { et::g_force_splits = n; }
 
 // Test hook: 0 = never fuse the Q/K/V projection into the attention kernel.
 void et_debug_set_qkv_fusion(int on) { et::g_qkv_fusion = on != 0; }
+void et_debug_set_ln_fusion(int mode) { et::g_ln_fusion = mode; }
 
 size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq) {
     if (et::check_layer(layer) != ET_OK || batch <= 0 || seq <= 0) return 0;
@@ -170,12 +186,40 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
             ET_OK)
             return st;
     }
-    if ((st = et::run_linear(layer->o, b.z, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
-    if ((st = et::launch_skip_layernorm(b.a, xin, reinterpret_cast<const __half*>(layer->ln1_gamma),
-                                        reinterpret_cast<const __half*>(layer->ln1_beta), b.y, T,
-                                        layer->hidden, s)) != ET_OK)
-        return st;
+    const int ln_fused = et::ln_fusion_mask(T, layer->hidden);
+    if ((ln_fused & 1) && layer->o.format == ET_FMT_DENSE &&
+        et::gemm_ln_applies(T, layer->hidden, layer->vdim)) {
+        // O projection, residual and LayerNorm in one kernel
+        if ((st = et::launch_gemm_ln(b.z, layer->vdim,
+                                     reinterpret_cast<const __half*>(layer->o.weight), layer->vdim,
+                                     reinterpret_cast<const __half*>(layer->o.bias), xin,
+                                     layer->hidden,
+                                     reinterpret_cast<const __half*>(layer->ln1_gamma),
+                                     reinterpret_cast<const __half*>(layer->ln1_beta), b.y,
+                                     layer->hidden, T, layer->hidden, layer->vdim, s)) != ET_OK)
+            return st;
+    } else {
+        if ((st = et::run_linear(layer->o, b.z, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
+        if ((st = et::launch_skip_layernorm(b.a, xin,
+                                            reinterpret_cast<const __half*>(layer->ln1_gamma),
+                                            reinterpret_cast<const __half*>(layer->ln1_beta), b.y,
+                                            T, layer->hidden, s)) != ET_OK)
+            return st;
+    }
     if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, s)) != ET_OK) return st;
+    if ((ln_fused & 2) && layer->ffn2.format == ET_FMT_DENSE &&
+        et::gemm_ln_applies(T, layer->hidden, layer->ff) &&
+        reinterpret_cast<const __half*>(out) != b.y) {
+        // FFN2, residual and LayerNorm in one kernel
+        return et::launch_gemm_ln(b.f, layer->ff,
+                                  reinterpret_cast<const __half*>(layer->ffn2.weight), layer->ff,
+                                  reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
+                                  layer->hidden,
+                                  reinterpret_cast<const __half*>(layer->ln2_gamma),
+                                  reinterpret_cast<const __half*>(layer->ln2_beta),
+                                  reinterpret_cast<__half*>(out), layer->hidden, T, layer->hidden,
+                                  layer->ff, s);
+    }
     const bool ffn2_splittable = layer->ffn2.format == ET_FMT_DENSE && layer->hidden <= 2048;
     const int pair_splits =
         ffn2_splittable ? et::pick_pair_splits(T, layer->hidden, layer->ff) : 0;

@@ -1,0 +1,382 @@
+// Dense Linear whose epilogue is the skip-LayerNorm that follows it in the encoder layer:
+//   out = LayerNorm(X W^T + bias + residual) * gamma + beta          (eps 1e-5)
+// in ONE kernel (reference Encoder/Encoder.h: the O projection followed by SkipLayerNorm, and
+// FFN2 followed by SkipLayerNorm; SkipLayerNorm/SkipLayerNorm.cu:73-82 for the normalisation).
+//
+// A row of the output spans N / 128 tiles, i.e. N / 128 CTAs.  Those CTAs form one thread-block
+// cluster (2 .. 8 CTAs along N): each CTA computes its 128 x 128 tile with tcgen05.mma as the
+// dense GEMM does, adds bias and residual in registers, sums its 128 columns of every row
+// (sum and sum of squares, fp32), writes that pair into the shared memory of EVERY CTA of the
+// cluster (distributed shared memory), and after one cluster barrier each CTA holds the
+// statistics of its 128 full rows, normalises its tile from registers and stores it with TMA.
+// The pre-normalisation activations never reach global memory and the LayerNorm launch (a
+// latency-bound pass of about 3 us at 2048 rows) disappears.
+//
+// Roles per CTA: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = epilogue (two warps per
+// tensor-memory lane quadrant, 64 columns of a row each).  Every thread of every CTA executes
+// the cluster barrier exactly once on every path (a CTA whose bounded wait ran out skips its
+// stores, not the barrier), so a fault in one CTA cannot leave its neighbours waiting.
+#include "common.cuh"
+#include "gemm_common.cuh"
+#include "kernels.h"
+
+namespace et {
+
+namespace {
+
+using namespace gemm;
+
+constexpr int LN_BN = 128;
+constexpr int LN_STAGES = 6;
+constexpr int LN_STAGE_BYTES = A_STAGE_BYTES + LN_BN * BK * 2;  // 32 KB
+constexpr int LN_RING = LN_STAGES * LN_STAGE_BYTES;             // 192 KB
+constexpr int LN_MAX_CLUSTER = 8;
+// barriers | bias, gamma, beta (fp32) | per-half partial sums | per-CTA row statistics
+constexpr int LN_MISC = 256 + 3 * LN_BN * 4 + 2 * BM * 8 + LN_MAX_CLUSTER * BM * 8;
+constexpr int LN_SMEM = LN_RING + LN_MISC + 1024;
+static_assert(LN_SMEM <= 227 * 1024, "shared memory budget exceeded");
+
+struct LnGemmArgs {
+    const __half* bias;   // [N] or null
+    const __half* resid;  // [M, ldr] or null
+    const __half* gamma;  // [N]
+    const __half* beta;   // [N]
+    int ldr, M, N, K;
+    float eps;
+    int* err_word;
+};
+
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void st_cluster_f32x2(uint32_t cluster_addr, float a, float b) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(cluster_addr), "f"(a), "f"(b)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_ln_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmY, const LnGemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + LN_STAGES * A_STAGE_BYTES;
+    uint8_t* sStage = smem;  // the ring is idle once the tile's products are complete
+    uint8_t* misc = smem + LN_RING;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);
+    uint64_t* empty_bar = full_bar + LN_STAGES;
+    uint64_t* acc_full = empty_bar + LN_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* s_bias = reinterpret_cast<float*>(misc + 256);
+    float* s_gamma = s_bias + LN_BN;
+    float* s_beta = s_gamma + LN_BN;
+    float2* s_part = reinterpret_cast<float2*>(s_beta + LN_BN);  // [2 halves][128 rows]
+    float2* s_stats = s_part + 2 * BM;                           // [cluster size][128 rows]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();   // this CTA's tile along N
+    const uint32_t csize = cluster_nctarank();  // = N / 128
+    const int n0 = static_cast<int>(rank) * LN_BN;
+    const int m0 = static_cast<int>(blockIdx.x / csize) * BM;
+    const int num_kb = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        for (int s = 0; s < LN_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, LN_BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    // this thread's 64 values of its row (epilogue warps only), kept across the cluster barrier
+    float v[64];
+    bool ok = true;
+    const int q = warp & 3;            // tensor-memory lane quadrant
+    const int half = (warp - 2) >> 2;  // which 64 columns of the tile
+    const int r = q * 32 + lane;       // row inside the tile
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            // weights do not depend on the previous kernel: fetch them before waiting for it
+            const int pre = num_kb < LN_STAGES ? num_kb : LN_STAGES;
+            for (int i = 0; i < pre; ++i) {
+                mbar_arrive_expect_tx(&full_bar[i], LN_STAGE_BYTES);
+                tma_load_2d(sB + i * (LN_BN * BK * 2), &tmB, &full_bar[i], i * BK, n0);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(sA + i * A_STAGE_BYTES, &tmA, &full_bar[i], i * BK, m0);
+            int issued = pre;
+            for (int i = pre; i < num_kb; ++i) {
+                const int s = i % LN_STAGES;
+                const uint32_t ph = (i / LN_STAGES) & 1;
+                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) {
+                    report_error(g.err_word, abort_flag, DEV_TIMEOUT_GEMM_PRODUCER);
+                    break;
+                }
+                mbar_arrive_expect_tx(&full_bar[s], LN_STAGE_BYTES);
+                tma_load_2d(sA + s * A_STAGE_BYTES, &tmA, &full_bar[s], i * BK, m0);
+                tma_load_2d(sB + s * (LN_BN * BK * 2), &tmB, &full_bar[s], i * BK, n0);
+                ++issued;
+            }
+            if (*abort_flag) {
+                // let copies in flight land before the CTA's shared memory is released
+                for (int i = issued > LN_STAGES ? issued - LN_STAGES : 0; i < issued; ++i)
+                    for (uint32_t sp = 0; sp < ET_SPIN_LIMIT; ++sp)
+                        if (mbar_try_wait(&full_bar[i % LN_STAGES], (i / LN_STAGES) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc_f16(BM, LN_BN, 0, 0);
+            bool mma_ok = true;
+            for (int i = 0; i < num_kb; ++i) {
+                const int s = i % LN_STAGES;
+                const uint32_t ph = (i / LN_STAGES) & 1;
+                if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
+                    report_error(g.err_word, abort_flag, DEV_TIMEOUT_GEMM_MMA);
+                    mma_ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+                const uint32_t b_addr = smem_u32(sB + s * (LN_BN * BK * 2));
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    mma_f16_ss(tmem_base, make_smem_desc(a_addr + k * 32, 16, 1024, SWZ_128B),
+                               make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B), idesc,
+                               (i | k) != 0 ? 1u : 0u);
+                mma_commit(&empty_bar[s]);
+            }
+            if (mma_ok) mma_commit(acc_full);
+        }
+    } else {
+        // ---------------- epilogue, part 1: bias + residual, this CTA's share of the sums ----
+        const int et = threadIdx.x - 64;
+        if (et < LN_BN) {
+            const int n = n0 + et;
+            s_bias[et] = g.bias != nullptr ? __half2float(__ldg(g.bias + n)) : 0.f;
+            s_gamma[et] = __half2float(__ldg(g.gamma + n));
+            s_beta[et] = __half2float(__ldg(g.beta + n));
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+        pdl_wait();  // the residual and the output buffer belong to earlier kernels
+        // the residual does not depend on this kernel's products: fetch it while they run
+        uint4 res[8];
+        const int row = m0 + r;
+        if (g.resid != nullptr && row < g.M) {
+            const uint4* rp = reinterpret_cast<const uint4*>(
+                g.resid + static_cast<size_t>(row) * g.ldr + n0 + half * 64);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) res[i] = __ldg(rp + i);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) res[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        ok = num_kb == 0 || mbar_wait_bounded(acc_full, 0, abort_flag);
+        if (!ok) report_error(g.err_word, abort_flag, DEV_TIMEOUT_GEMM_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok);
+        float sum = 0.f, sq = 0.f;
+        if (ok) {
+            tc_fence_after_sync();
+            const uint32_t lane_addr =
+                tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 64;
+            uint32_t ra[32], rb[32];
+            if (num_kb > 0) {
+                tmem_ld32(lane_addr, ra);
+                tmem_ld32(lane_addr + 32, rb);
+                tmem_ld_wait_regs(ra);
+                tmem_ld_wait_regs(rb);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ra[j] = rb[j] = 0u;
+            }
+            const float* b64 = s_bias + half * 64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half2* h = reinterpret_cast<const __half2*>(&res[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    const int c = i * 8 + j * 2;
+                    const float a0 = __uint_as_float(c < 32 ? ra[c] : rb[c - 32]);
+                    const float a1 = __uint_as_float(c + 1 < 32 ? ra[c + 1] : rb[c + 1 - 32]);
+                    v[c] = a0 + b64[c] + f.x;
+                    v[c + 1] = a1 + b64[c + 1] + f.y;
+                    sum += v[c] + v[c + 1];
+                    sq = fmaf(v[c], v[c], fmaf(v[c + 1], v[c + 1], sq));
+                }
+            }
+        }
+        s_part[half * BM + r] = make_float2(sum, sq);
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+        if (half == 0) {
+            const float2 o = s_part[BM + r];
+            const uint32_t mine = smem_u32(&s_stats[rank * BM + r]);
+            for (uint32_t p = 0; p < csize; ++p)
+                st_cluster_f32x2(map_to_cta(mine, p), sum + o.x, sq + o.y);
+        }
+    }
+
+    // every thread of every CTA of the cluster: the row statistics are complete after this
+    __syncwarp();
+    cluster_sync_all();
+
+    if (warp >= 2) {
+        // ---------------- epilogue, part 2: normalise from registers, store ----------------
+        float tsum = 0.f, tsq = 0.f;
+        for (uint32_t p = 0; p < csize; ++p) {
+            const float2 s = s_stats[p * BM + r];
+            tsum += s.x;
+            tsq += s.y;
+        }
+        const float inv_n = 1.0f / static_cast<float>(g.N);
+        const float mean = tsum * inv_n;
+        const float var = fmaxf(tsq * inv_n - mean * mean, 0.f);
+        const float rstd = rsqrtf(var + g.eps);
+        const float shift = -mean * rstd;
+        if (ok && !*abort_flag) {
+            uint8_t* tile = sStage + (q * 2 + half) * 4096;  // 32 rows x 64 fp16, swizzled
+            uint8_t* srow = tile + lane * 128;
+            const float* gm = s_gamma + half * 64;
+            const float* bt = s_beta + half * 64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float y[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    y[j] = fmaf(fmaf(v[i * 8 + j], rstd, shift), gm[i * 8 + j], bt[i * 8 + j]);
+                uint4 o;
+                o.x = pack_half2(y[0], y[1]);
+                o.y = pack_half2(y[2], y[3]);
+                o.z = pack_half2(y[4], y[5]);
+                o.w = pack_half2(y[6], y[7]);
+                *reinterpret_cast<uint4*>(srow + ((i ^ (lane & 7)) * 16)) = o;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && m0 + q * 32 < g.M) {
+                tma_store_2d(&tmY, tile, n0 + half * 64, m0 + q * 32);
+                tma_store_commit();
+                tma_store_wait_read();
+            }
+        }
+    }
+
+    pdl_wait();  // no CTA may retire before the kernels it depends on have completed
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, LN_BN);
+}
+
+}  // namespace
+
+bool gemm_ln_applies(int M, int N, int K) {
+    return M > 0 && K > 0 && N >= 2 * LN_BN && N % LN_BN == 0 && N / LN_BN <= LN_MAX_CLUSTER;
+}
+
+// out[m, :] = LayerNorm(X[m, :] W^T + bias + resid[m, :]) * gamma + beta; N = 256 .. 1024 in
+// steps of 128.  resid and bias may be null.  out must not alias X or resid.
+int launch_gemm_ln(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
+                   const __half* resid, int ldr, const __half* gamma, const __half* beta,
+                   __half* out, int ldo, int M, int N, int K, cudaStream_t stream) {
+    if (!X || !W || !gamma || !beta || !out) return ET_ERR_INVALID_ARG;
+    if (!gemm_ln_applies(M, N, K)) return ET_ERR_SHAPE;
+    if (!aligned16(X) || !aligned16(W) || !aligned16(out) || (resid && !aligned16(resid)))
+        return ET_ERR_ALIGNMENT;
+    if (ldx % 8 || ldw % 8 || K % 8 || ldo % 8 || (resid && ldr % 8)) return ET_ERR_SHAPE;
+    int* err = device_error_word();
+    if (!err) return ET_ERR_NO_DEVICE;
+    CUtensorMap tmA, tmB, tmY;
+    int st;
+    if ((st = gemm::encode_operand(&tmA, X, ldx, M, K, gemm::BM)) != ET_OK) return st;
+    if ((st = gemm::encode_operand(&tmB, W, ldw, N, K, LN_BN)) != ET_OK) return st;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldo) * 2};
+        const uint32_t box[2] = {64, 32};
+        st = make_tensor_map_f16(&tmY, out, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != ET_OK) return st;
+    }
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemm_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 LN_SMEM) != cudaSuccess)
+            return ET_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    LnGemmArgs a;
+    a.bias = bias;
+    a.resid = resid;
+    a.gamma = gamma;
+    a.beta = beta;
+    a.ldr = ldr;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.eps = 1e-5f;
+    a.err_word = err;
+    const int csize = N / LN_BN;
+    const int tiles_m = (M + gemm::BM - 1) / gemm::BM;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles_m * csize));
+    cfg.blockDim = dim3(gemm::GEMM_THREADS);
+    cfg.dynamicSmemBytes = LN_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, gemm_ln_kernel, tmA, tmB, tmY, a) == cudaSuccess ? ET_OK
+                                                                                      : ET_ERR_CUDA;
+}
+
+}  // namespace et
+
+extern "C" {
+
+int et_linear_skip_layernorm_fwd(const et_half* X, const et_half* W, const et_half* bias,
+                                 const et_half* resid, const et_half* gamma, const et_half* beta,
+                                 et_half* result, int T, int in, int out, et_stream stream) {
+    if (T == 0) return ET_OK;
+    if (T < 0 || in <= 0 || out <= 0) return ET_ERR_INVALID_ARG;
+    if (in % 16 || out % 16) return ET_ERR_SHAPE;
+    return et::launch_gemm_ln(reinterpret_cast<const __half*>(X), in,
+                              reinterpret_cast<const __half*>(W), in,
+                              reinterpret_cast<const __half*>(bias),
+                              reinterpret_cast<const __half*>(resid), out,
+                              reinterpret_cast<const __half*>(gamma),
+                              reinterpret_cast<const __half*>(beta),
+                              reinterpret_cast<__half*>(result), out, T, out, in,
+                              static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -65,6 +65,13 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
                      int mask_kind, const __half* mask, const int* valid_len, float scale,
                      cudaStream_t stream);
 
+// out = LN(X W^T + bias + resid) * gamma + beta in one kernel (gemm_ln.cu); N = 256 .. 1024 in
+// steps of 128.
+bool gemm_ln_applies(int M, int N, int K);
+int launch_gemm_ln(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
+                   const __half* resid, int ldr, const __half* gamma, const __half* beta,
+                   __half* out, int ldo, int M, int N, int K, cudaStream_t stream);
+
 // out = LN(src + skip) * gamma + beta (skip may be null).
 int launch_skip_layernorm(const __half* src, const __half* skip, const __half* gamma,
                           const __half* beta, __half* out, int rows, int size,

@@ -317,6 +317,7 @@ int et_act_fwd(const et_half* in, et_half* out, size_t n, int act, et_stream str
     if (!in || !out || n == 0) return ET_ERR_INVALID_ARG;
     if (act < ET_ACT_NONE || act > ET_ACT_GELU) return ET_ERR_INVALID_ARG;
     if (!et::aligned16(in) || !et::aligned16(out)) return ET_ERR_ALIGNMENT;
+    et::count_launch();
     et::act_kernel<<<et::grid_for(n / 8 + 1, 256, 148 * 8), 256, 0,
                      static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const __half*>(in),
                                                           reinterpret_cast<__half*>(out), n, act);
@@ -327,6 +328,7 @@ int et_bias_add_fwd(et_half* data, const et_half* bias, int rows, int cols, et_s
     if (!data || !bias || rows <= 0 || cols <= 0) return ET_ERR_INVALID_ARG;
     if (cols % 8) return ET_ERR_SHAPE;
     if (!et::aligned16(data) || !et::aligned16(bias)) return ET_ERR_ALIGNMENT;
+    et::count_launch();
     et::bias_add_kernel<<<et::grid_for(static_cast<size_t>(rows) * cols / 8, 256, 148 * 8), 256, 0,
                           static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<__half*>(data), reinterpret_cast<const __half*>(bias), rows, cols);

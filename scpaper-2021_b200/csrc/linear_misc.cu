@@ -140,6 +140,7 @@ int et_linear_1x16_fwd(const int32_t* tile_idx, const int32_t* row_idx, const et
         return ET_ERR_ALIGNMENT;
     dim3 grid(out / 16, (T + et::V16_THREADS - 1) / et::V16_THREADS);
     if (grid.y > 65535) return ET_ERR_SHAPE;
+    et::count_launch();
     et::linear_1x16_kernel<<<grid, et::V16_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         tile_idx, row_idx, reinterpret_cast<const __half*>(data),
         reinterpret_cast<const __half*>(bias), reinterpret_cast<const __half*>(X),
@@ -166,6 +167,7 @@ int et_linear_csr_fwd(const int32_t* indptr, const int32_t* indices, const et_ha
         attr_bytes[dev] = smem;
     }
     const int blocks = (T + et::CSR_TOKENS - 1) / et::CSR_TOKENS;
+    et::count_launch();
     et::linear_csr_kernel<<<blocks, et::CSR_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
         indptr, indices, reinterpret_cast<const __half*>(data),
         reinterpret_cast<const __half*>(bias), reinterpret_cast<const __half*>(X),

@@ -618,6 +618,7 @@ int et_tile_pack_tiles(const et_half* tiles, const int32_t* perm, int nnz_tiles,
     if (!et::aligned16(tiles) || !et::aligned16(packed_tiles)) return ET_ERR_ALIGNMENT;
     const size_t total = static_cast<size_t>(nnz_tiles) * 32;
     const int blocks = static_cast<int>((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    et::count_launch();
     et::pack_tiles_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint4*>(tiles), perm, reinterpret_cast<uint4*>(packed_tiles),
         nnz_tiles);
@@ -660,6 +661,7 @@ int et_tile_densify(const int32_t* row_ptr, const int32_t* row_off, const et_hal
     if (cudaMemsetAsync(dense, 0, static_cast<size_t>(in) * out * sizeof(__half), s) != cudaSuccess)
         return ET_ERR_CUDA;
     if (nnz_tiles > 0) {
+        et::count_launch();
         et::densify_tiles_kernel<<<out >> 4, 256, 0, s>>>(row_ptr, row_off,
                                                            reinterpret_cast<const __half*>(tiles),
                                                            in >> 4, in,

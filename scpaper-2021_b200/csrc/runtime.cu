@@ -1,6 +1,7 @@
 // Host-side runtime of the library: status strings, the per-device error word, the
 // tensor-map encoder (driver entry point fetched at run time, so the library does not
 // link against libcuda) and the host validators of the pruned-weight index arrays.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -49,9 +50,11 @@ PerDevice* current_device() {
 }  // namespace
 
 namespace {
+std::atomic<long long> g_launches{0};
 bool g_pdl = true;
 }
 bool pdl_enabled() { return g_pdl; }
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 void set_pdl_enabled(bool on) { g_pdl = on; }
 
 int* device_error_word() {
@@ -143,6 +146,9 @@ const char* et_status_string(int status) {
 
 // Test hook: 0 = plain launches, 1 = programmatic dependent launches (default).
 void et_debug_set_pdl(int on) { et::set_pdl_enabled(on != 0); }
+// Kernels launched by this library so far in this process (host-side count; a replayed CUDA
+// graph launches what was counted while it was captured).
+long long et_debug_launch_count() { return et::g_launches.load(std::memory_order_relaxed); }
 
 int et_version(void) { return 100; }
 int et_built_for_sm(void) { return 100; }

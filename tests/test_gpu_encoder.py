@@ -62,11 +62,33 @@ def test_ffn2_split_k_forms(et, orc, cuda, splits):
     w = et.synth.encoder_layer_weights(2021, 2, hidden, ff, bias_std=0.02, ln_noise=0.05)
     x = et.synth.normal(2021, 94, (batch * seq, hidden), 1.0)
     try:
+        et.lib().et_debug_set_ln_fusion(ctypes.c_int(0))  # the split forms feed the LayerNorm
         et.lib().et_debug_force_ffn2_splits(ctypes.c_int(splits))
         y = _run(et, cuda, [w], x, batch, seq, nhead)
     finally:
         et.lib().et_debug_force_ffn2_splits(ctypes.c_int(0))
+        et.lib().et_debug_set_ln_fusion(ctypes.c_int(-1))
     assert_close(y, _oracle_stack(orc, [w], x, batch, seq, nhead), f"ffn2 splits {splits}")
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("batch,seq,hidden,nhead,ff", [(4, 128, 768, 12, 3072),
+                                                       (3, 100, 1024, 16, 4096),
+                                                       (2, 200, 256, 4, 512)])
+def test_linear_layernorm_fusion_modes(et, orc, cuda, mode, batch, seq, hidden, nhead, ff):
+    """O projection / FFN2 fused with their skip-LayerNorm (mask 1 / 2) against the separate
+    kernels (0) and the oracle; a padding mask so that sequences differ."""
+    import ctypes
+    w = et.synth.encoder_layer_weights(2021, 3, hidden, ff, bias_std=0.02, ln_noise=0.05)
+    x = et.synth.normal(2021, 93, (batch * seq, hidden), 1.0)
+    vl = np.array([seq - 7 * i for i in range(batch)], dtype=np.int32)
+    try:
+        et.lib().et_debug_set_ln_fusion(ctypes.c_int(mode))
+        y = _run(et, cuda, [w, w], x, batch, seq, nhead, mask_kind=2, valid_len=vl)
+    finally:
+        et.lib().et_debug_set_ln_fusion(ctypes.c_int(-1))
+    assert_close(y, _oracle_stack(orc, [w, w], x, batch, seq, nhead, 2, vl),
+                 f"linear+LN fusion mode {mode}")
 
 
 def test_stack_of_three_layers_with_padding(et, orc, cuda):

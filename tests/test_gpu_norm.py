@@ -51,3 +51,38 @@ def test_bias_add(et, cuda):
     y = et.bias_add_(_dev(x, cuda), _dev(b, cuda))
     ref = (x.astype(np.float32) + b.astype(np.float32)).astype(np.float16).astype(np.float32)
     assert np.array_equal(y.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("T,inn,out", [(2048, 768, 768), (300, 256, 256), (130, 3072, 768),
+                                       (100, 512, 1024), (1, 64, 384), (257, 1024, 1024)])
+@pytest.mark.parametrize("with_bias,with_resid", [(True, True), (False, True), (True, False)])
+def test_linear_skip_layernorm(et, orc, cuda, T, inn, out, with_bias, with_resid):
+    """Dense Linear + residual + LayerNorm in one kernel (a cluster of out / 128 CTAs per row
+    block) against the oracle's Linear followed by its SkipLayerNorm."""
+    x = et.synth.normal(8, 1, (T, inn), 1.0)
+    w = et.synth.normal(8, 2, (out, inn), 0.05)
+    b = et.synth.normal(8, 3, (out,), 0.5) if with_bias else None
+    res = et.synth.normal(8, 4, (T, out), 1.0, 0.3) if with_resid else None
+    g = et.synth.normal(8, 5, (out,), 0.2, 1.0)
+    beta = et.synth.normal(8, 6, (out,), 0.2)
+    y = et.linear_skip_layernorm(_dev(x, cuda), _dev(w, cuda),
+                                 _dev(b, cuda) if with_bias else None,
+                                 _dev(res, cuda) if with_resid else None, _dev(g, cuda),
+                                 _dev(beta, cuda))
+    assert et.device_error() == 0
+    ref = orc.skip_layernorm(orc.linear_dense(x, w, b, 0), res, g, beta)
+    assert_close(y.float().cpu().numpy(), ref, f"linear+skipLN {T}x{inn}x{out}")
+
+
+def test_linear_skip_layernorm_shapes(et, cuda):
+    """Widths outside 256..1024 (steps of 128) are refused, not mis-computed."""
+    import torch
+    x = torch.zeros((16, 64), dtype=torch.float16, device=cuda)
+    g = torch.ones((128,), dtype=torch.float16, device=cuda)
+    w = torch.zeros((128, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(Exception):
+        et.linear_skip_layernorm(x, w, None, None, g, g)
+    g = torch.ones((320,), dtype=torch.float16, device=cuda)
+    w = torch.zeros((320, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(Exception):
+        et.linear_skip_layernorm(x, w, None, None, g, g)
