@@ -33,9 +33,24 @@ WORKLOAD = ("BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, seq 128
 HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
 LONG_BATCH, LONG_SEQ = 2, 4096  # secondary per-kernel entry: attention on long sequences
 SEED = 2021
-# dram__bytes_read + dram__bytes_write of one FFN1 launch from the ncu capture summarised in
-# profiles/ncu_full_one_layer_bert_base_b16.md (cold operands; the result stays in L2)
-FFN1_DRAM_TRAFFIC_BYTES = 7931392
+# The four kernels of one layer at this batch: dram__bytes_read + dram__bytes_write of one launch
+# from the ncu capture summarised in profiles/ncu_full_one_layer_bert_base_b16.md (cold operands;
+# results stay in L2), and the operands read / written once (fp16).
+_T = BATCH * SEQ
+STACK_KERNELS = {
+    "qkv_attention_fused": {
+        "label": "qkv_attention_kernel (Q/K/V projection + attention)",
+        "traffic": 6727424, "algorithmic_bytes": 2 * (2 * _T * HIDDEN + 3 * HIDDEN * HIDDEN)},
+    "o_layernorm_fused": {
+        "label": "gemm_ln_kernel (O projection + residual + LayerNorm)",
+        "traffic": 7507712, "algorithmic_bytes": 2 * (3 * _T * HIDDEN + HIDDEN * HIDDEN)},
+    "ffn1_gelu": {
+        "label": f"gemm_f16_kernel (FFN1 + GELU, [{_T}x768]x[3072x768]^T)",
+        "traffic": 7931392, "algorithmic_bytes": 2 * (_T * HIDDEN + FF * HIDDEN + _T * FF)},
+    "ffn2_layernorm_fused": {
+        "label": f"gemm_ln_kernel (FFN2 + residual + LayerNorm, [{_T}x3072]x[768x3072]^T)",
+        "traffic": 20484096, "algorithmic_bytes": 2 * (_T * FF + FF * HIDDEN + 2 * _T * HIDDEN)},
+}
 
 
 def flops_per_sequence(keep_lin: float = 1.0) -> float:
@@ -446,13 +461,15 @@ def main():
             per_kernel["note"] = ("each kernel timed inside one CUDA graph that rotates over buffer "
                                   "sets larger than L2")
             del a, w, y, qkv, z, o
-        k = per_kernel["ffn1_gelu"]
-        line["roofline"] = {"bound": "tensor", "kernel": "gemm_f16_kernel (FFN1 + GELU, "
-                            f"[{T}x768]x[3072x768]^T)", "achieved": k["tflops"],
-                            "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": k["tflops"] / peaks["bf16_tflops"],
-                            "traffic": FFN1_DRAM_TRAFFIC_BYTES,
-                            "algorithmic_bytes": 2 * (T * HIDDEN + FF * HIDDEN + T * FF),
+        # the dominant kernel = the longest of the four that make up a layer at this batch
+        dom = max(STACK_KERNELS, key=lambda n: per_kernel[n]["us"])
+        k = per_kernel[dom]
+        line["roofline"] = {"bound": "tensor", "kernel": STACK_KERNELS[dom]["label"],
+                            "achieved": k["tflops"], "peak": peaks["bf16_tflops"],
+                            "unit": "TFLOP/s", "frac": k["tflops"] / peaks["bf16_tflops"],
+                            "us_per_launch": k["us"],
+                            "traffic": STACK_KERNELS[dom]["traffic"],
+                            "algorithmic_bytes": STACK_KERNELS[dom]["algorithmic_bytes"],
                             "peak_source": peaks["source"] + " (burst, kernel timed alone)"}
         line["kernels"] = per_kernel
 
