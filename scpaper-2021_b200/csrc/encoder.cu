@@ -35,16 +35,17 @@ bool g_qkv_fusion = true;  // test hook: false = always the separate projection 
 // -1 = automatic, otherwise a mask: 1 = the O projection, 2 = FFN2
 int g_ln_fusion = -1;
 
-// The fused kernel computes 128 x 128 tiles, one per CTA.  Measured on B200: while all its CTAs
-// fit the GPU at once it beats the separate GEMM + LayerNorm (BERT-base, 2048 tokens: 8.0 vs
-// 10.8 us for the O projection, 15.3 vs 18.4 us for FFN2, +10 % on the whole stack); with
-// several waves of CTAs the wider tiles and CTA pairs of the plain GEMM win by more than the
-// LayerNorm launch costs (8192 tokens: -3 %).
+// The fused kernel computes 128 x 128 tiles, one per CTA, in clusters of hidden / 128 CTAs.
+// Measured on B200: while all its clusters are resident at once it beats the separate GEMM +
+// LayerNorm (BERT-base, 2048 tokens: 8.0 vs 10.8 us for the O projection, 15.3 vs 18.4 us for
+// FFN2, +10 % on the whole stack); with several waves the wider tiles and CTA pairs of the plain
+// GEMM win by more than the LayerNorm launch costs (8192 tokens: -3 %).  A cluster must fit one
+// GPC, so the number of resident clusters comes from the occupancy query, not from the SM count.
 int ln_fusion_mask(int T, int hidden) {
     if (g_ln_fusion >= 0) return g_ln_fusion;
-    const int sms = sm_count() > 0 ? sm_count() : 148;
-    const long ctas = static_cast<long>((T + 127) / 128) * (hidden / 128);
-    return ctas <= sms ? 3 : 0;
+    if (hidden % 128 != 0) return 0;
+    const int row_blocks = (T + 127) / 128;
+    return row_blocks <= gemm_ln_resident_clusters(hidden) ? 3 : 0;
 }
 
 // Split-K on CTA pairs: 256 x 256 pair tiles, as many K slices as SM pairs allow.  Returns 0

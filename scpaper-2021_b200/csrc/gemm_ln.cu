@@ -295,6 +295,38 @@ bool gemm_ln_applies(int M, int N, int K) {
     return M > 0 && K > 0 && N >= 2 * LN_BN && N % LN_BN == 0 && N / LN_BN <= LN_MAX_CLUSTER;
 }
 
+// How many clusters of N / 128 CTAs of the fused kernel the current device can hold at once
+// (a cluster needs that many free SMs inside one GPC, so this is less than SMs / cluster size
+// in general; asked once per device and size).  0 if the question fails.
+int gemm_ln_resident_clusters(int N) {
+    static int known[64][LN_MAX_CLUSTER + 1] = {};  // 0 = not asked, else answer + 1
+    const int csize = N / LN_BN;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || csize < 2 || csize > LN_MAX_CLUSTER || N % LN_BN) return 0;
+    if (known[dev][csize] == 0) {
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 LN_SMEM) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(csize));
+            cfg.blockDim = dim3(gemm::GEMM_THREADS);
+            cfg.dynamicSmemBytes = LN_SMEM;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_ln_kernel, &cfg) != cudaSuccess) n = 0;
+        }
+        cudaGetLastError();
+        known[dev][csize] = (n < 0 ? 0 : n) + 1;
+    }
+    return known[dev][csize] - 1;
+}
+
 // out[m, :] = LayerNorm(X[m, :] W^T + bias + resid[m, :]) * gamma + beta; N = 256 .. 1024 in
 // steps of 128.  resid and bias may be null.  out must not alias X or resid.
 int launch_gemm_ln(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,

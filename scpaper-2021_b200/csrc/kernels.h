@@ -68,6 +68,7 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
 // out = LN(X W^T + bias + resid) * gamma + beta in one kernel (gemm_ln.cu); N = 256 .. 1024 in
 // steps of 128.
 bool gemm_ln_applies(int M, int N, int K);
+int gemm_ln_resident_clusters(int N);  // clusters of N / 128 CTAs the device holds at once
 int launch_gemm_ln(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
                    const __half* resid, int ldr, const __half* gamma, const __half* beta,
                    __half* out, int ldo, int M, int N, int K, cudaStream_t stream);
