@@ -87,6 +87,10 @@ int et_linear_dense_fwd(const et_half* X, const et_half* W, const et_half* bias,
 int et_linear_skip_layernorm_fwd(const et_half* X, const et_half* W, const et_half* bias,
                                  const et_half* resid, const et_half* gamma, const et_half* beta,
                                  et_half* result, int T, int in, int out, et_stream stream);
+/* Plan-time query for the call above: 1 when it is expected to beat et_linear_dense_fwd followed
+ * by et_skip_layernorm_fwd on the current device, i.e. when the width is supported and every
+ * thread-block cluster of the launch (one per 128 rows) is resident at once; else 0. */
+int et_linear_skip_layernorm_pays(int T, int in, int out);
 
 /* 16x16 tile-CSR weights: row_ptr[out/16 + 1], row_off[nnz] (input block column,
  * ascending inside a block row), tiles[nnz][16][16] row-major [out_local][in_local].

@@ -22,7 +22,7 @@ FMT_DENSE, FMT_TILE, FMT_TILE_PACKED = 0, 1, 2
 # Every symbol include/et_b200.h declares (checked by the CPU test-suite against the header).
 ABI_SYMBOLS = [
     "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
-    "et_linear_dense_fwd", "et_linear_skip_layernorm_fwd", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
+    "et_linear_dense_fwd", "et_linear_skip_layernorm_fwd", "et_linear_skip_layernorm_pays", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
     "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_tile_prefer_dense", "et_tile_densify",
     "et_linear_row_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",

@@ -43,9 +43,7 @@ int g_ln_fusion = -1;
 // GPC, so the number of resident clusters comes from the occupancy query, not from the SM count.
 int ln_fusion_mask(int T, int hidden) {
     if (g_ln_fusion >= 0) return g_ln_fusion;
-    if (hidden % 128 != 0) return 0;
-    const int row_blocks = (T + 127) / 128;
-    return row_blocks <= gemm_ln_resident_clusters(hidden) ? 3 : 0;
+    return et_linear_skip_layernorm_pays(T, hidden, hidden) ? 3 : 0;
 }
 
 // Split-K on CTA pairs: 256 x 256 pair tiles, as many K slices as SM pairs allow.  Returns 0

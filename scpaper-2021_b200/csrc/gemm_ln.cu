@@ -395,6 +395,11 @@ int launch_gemm_ln(const __half* X, int ldx, const __half* W, int ldw, const __h
 
 extern "C" {
 
+int et_linear_skip_layernorm_pays(int T, int in, int out) {
+    if (T <= 0 || in <= 0 || in % 16 || !et::gemm_ln_applies(T, out, in)) return 0;
+    return (T + 127) / 128 <= et::gemm_ln_resident_clusters(out) ? 1 : 0;
+}
+
 int et_linear_skip_layernorm_fwd(const et_half* X, const et_half* W, const et_half* bias,
                                  const et_half* resid, const et_half* gamma, const et_half* beta,
                                  et_half* result, int T, int in, int out, et_stream stream) {

@@ -186,6 +186,25 @@ class Attention<_config, std::enable_if_t<!_config::isSingleKernel>> {
     void set_mask(const half* m) {
         mask = std::make_unique<ptr_t>(m, (size_t)model->seq_len * model->seq_len);
     }
+    // the output projection is a separate step (not so for the operator that fuses it)
+    static constexpr bool has_separate_output =
+        !std::is_same_v<OTF_attn_Ofused, typename config::attn_t>;
+    linearO_t& output_linear() { return *linearO; }
+    // Everything but the output projection; returns Z [rows, vdim].
+    half* forward_heads(half* query, half* key, half* value) {
+        static_assert(has_separate_output);
+        para_handles.fork(stream);
+        cudaStream_t sq = config::isPara ? para_handles.streams[0] : stream;
+        cudaStream_t sk = config::isPara ? para_handles.streams[1] : stream;
+        cudaStream_t sv = config::isPara ? para_handles.streams[2] : stream;
+        linearQ->forward(mat_q->get(), query, sq);
+        linearK->forward(mat_k->get(), key, sk);
+        linearV->forward(mat_v->get(), value, sv);
+        para_handles.join(stream);
+        Multihead_atttion<typename config::attn_t>(mat_q.get(), mat_k.get(), mat_v.get(), nullptr,
+                                                   mask.get(), mat_z.get(), model, stream);
+        return mat_z->get();
+    }
     void forward(half* out, half* query, half* key, half* value) {
         para_handles.fork(stream);
         cudaStream_t sq = config::isPara ? para_handles.streams[0] : stream;
@@ -240,7 +259,13 @@ class Attention<_config, std::enable_if_t<_config::isSingleKernel>> {
         mask = std::make_unique<ptr_t>(m, (size_t)model->seq_len * model->seq_len);
     }
     void set_valid_len(const int* device_lengths) { valid_len = device_lengths; }
+    static constexpr bool has_separate_output = true;
+    linearO_t& output_linear() { return *linearO; }
     void forward(half* out, half* query, half* key, half* value) {
+        linearO->forward(out, forward_heads(query, key, value), stream);
+    }
+    // Everything but the output projection; returns Z [rows, vdim].
+    half* forward_heads(half* query, half* key, half* value) {
         assert(query == key && key == value);
         (void)key;
         (void)value;
@@ -259,8 +284,7 @@ class Attention<_config, std::enable_if_t<_config::isSingleKernel>> {
                                            model->nhead, model->kdim, model->vdim, kind,
                                            mask ? et_ptr(mask->get()) : nullptr, valid_len,
                                            1.0f / std::sqrt((float)dh_qk), stream));
-                linearO->forward(out, mat_z->get(), stream);
-                return;
+                return mat_z->get();
             }
         }
         linearQKV->forward(mat_qkv->get(), query, stream);
@@ -271,6 +295,6 @@ class Attention<_config, std::enable_if_t<_config::isSingleKernel>> {
                                model->seq_len, model->nhead, dh_qk, dh_v, ld, ld, ld, model->vdim,
                                kind, mask ? et_ptr(mask->get()) : nullptr, valid_len,
                                1.0f / std::sqrt((float)dh_qk), stream));
-        linearO->forward(out, mat_z->get(), stream);
+        return mat_z->get();
     }
 };

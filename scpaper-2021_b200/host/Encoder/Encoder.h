@@ -55,6 +55,24 @@ void linear_then_act(L& lin, half* out, half* in, size_t n, cudaStream_t s) {
         act<ACT>(out, (int)n, s);
     }
 }
+// out = SkipLayerNorm(lin(in), skip).  A dense Linear runs with the LayerNorm in its epilogue
+// (one kernel) when the library expects that to pay; otherwise through `tmp`.
+template <typename L>
+void linear_then_skipln(L& lin, const SkipLayerNorm& ln, half* out, half* tmp, half* in,
+                        const half* skip, int rows, cudaStream_t s) {
+    if constexpr (std::is_same_v<L, Linear<base_mat>>) {
+        if (ln.width() == lin.out_size && lin.size == rows &&
+            et_linear_skip_layernorm_pays(rows, lin.in_size, lin.out_size)) {
+            etChk(et_linear_skip_layernorm_fwd(et_ptr(in), et_ptr(lin.weight.get()),
+                                               et_ptr(lin.bias.get()), et_ptr(skip),
+                                               et_ptr(ln.gamma()), et_ptr(ln.beta()), et_ptr(out),
+                                               rows, lin.in_size, lin.out_size, s));
+            return;
+        }
+    }
+    lin.forward(tmp, in, s);
+    ln.forward(out, tmp, skip, rows, s);
+}
 }  // namespace et_host
 
 template <typename _config> class Encoder {
@@ -93,12 +111,18 @@ template <typename _config> class Encoder {
 
     void forward(half* out, half* src) {
         const int rows = et_host::rows_of(*model);
-        attn->forward(temp_attn.get(), src, src, src);
-        LN1->forward(temp_LN.get(), temp_attn.get(), src, rows, stream);
+        if constexpr (attn_t::has_separate_output) {
+            half* z = attn->forward_heads(src, src, src);
+            et_host::linear_then_skipln(attn->output_linear(), *LN1, temp_LN.get(),
+                                        temp_attn.get(), z, src, rows, stream);
+        } else {
+            attn->forward(temp_attn.get(), src, src, src);
+            LN1->forward(temp_LN.get(), temp_attn.get(), src, rows, stream);
+        }
         et_host::linear_then_act<ACT_OP_t>(*linear1, temp_linear.get(), temp_LN.get(),
                                            (size_t)rows * model->dimFF, stream);
-        linear2->forward(temp_attn.get(), temp_linear.get(), stream);
-        LN2->forward(out, temp_attn.get(), temp_LN.get(), rows, stream);
+        et_host::linear_then_skipln(*linear2, *LN2, out, temp_attn.get(), temp_linear.get(),
+                                    temp_LN.get(), rows, stream);
     }
 };
 

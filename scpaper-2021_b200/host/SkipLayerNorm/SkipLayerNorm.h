@@ -14,6 +14,9 @@ class SkipLayerNorm {
   public:
     SkipLayerNorm(const half* w, const half* b, int _size)
         : size(_size), weight(w, _size), bias(b, _size) {}
+    int width() const { return size; }
+    const half* gamma() const { return weight.get(); }
+    const half* beta() const { return bias.get(); }
     void forward(half* out, const half* src, const half* skip, int num,
                  cudaStream_t stream = 0) const {
         etChk(et_skip_layernorm_fwd(et_ptr(src), et_ptr(skip), et_ptr(weight.get()),

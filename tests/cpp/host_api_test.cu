@@ -189,6 +189,57 @@ static void test_encoder_tile(int batch, int seq, int mask_kind) {
     compare(to_float(dout), ref, what);
 }
 
+// Encoder<dense weights, fused-QKV single-kernel attention, GELU>: the O projection and FFN2 run
+// with their SkipLayerNorm in the GEMM epilogue (one kernel each) when the library expects that
+// to pay, the separate kernels otherwise; both against the oracle layer.
+static void test_encoder_dense(int batch, int seq, int mask_kind) {
+    const int hidden = 256, nhead = 4, ff = 512, T = batch * seq;
+    auto model = std::make_shared<Model_t>(Model_t{hidden, hidden, seq, nhead, ff, hidden, 1, batch, mask_kind});
+    LayerW w;
+    w.wqkv = nvec((size_t)3 * hidden * hidden, 0.05f);
+    w.wo = nvec((size_t)hidden * hidden, 0.05f);
+    w.w1 = nvec((size_t)ff * hidden, 0.05f);
+    w.w2 = nvec((size_t)hidden * ff, 0.05f);
+    w.bqkv = nvec(3 * hidden, 0.02f);
+    w.bo = nvec(hidden, 0.02f);
+    w.b1 = nvec(ff, 0.02f);
+    w.b2 = nvec(hidden, 0.02f);
+    w.g1 = nvec(hidden, 0.1f);
+    w.g2 = nvec(hidden, 0.1f);
+    for (auto& g : w.g1) g = __half2float(__float2half_rn(g + 1.f));
+    for (auto& g : w.g2) g = __half2float(__float2half_rn(g + 1.f));
+    w.be1 = nvec(hidden, 0.1f);
+    w.be2 = nvec(hidden, 0.1f);
+    auto x = nvec((size_t)T * hidden, 1.0f);
+
+    using attn_cfg = Attention_config<base_mat, base_mat, base_mat, base_mat, OTF_attn_full, true, false>;
+    using enc_cfg = Encoder_config<attn_cfg, base_mat, base_mat, GELU_OP>;
+    auto hb = [&](const std::vector<float>& b) { return to_half(b); };
+    auto dense = [&](const std::vector<float>& m) { return base_mat(to_half(m)); };
+    auto lqkv = std::make_unique<Linear<base_mat>>(hidden, 3 * hidden, dense(w.wqkv), hb(w.bqkv).data(), T);
+    auto lo = std::make_unique<Linear<base_mat>>(hidden, hidden, dense(w.wo), hb(w.bo).data(), T);
+    auto l1 = std::make_unique<Linear<base_mat>>(hidden, ff, dense(w.w1), hb(w.b1).data(), T);
+    auto l2 = std::make_unique<Linear<base_mat>>(ff, hidden, dense(w.w2), hb(w.b2).data(), T);
+    auto attn = std::make_unique<Attention<attn_cfg>>(std::move(lqkv), std::move(lo), model);
+    auto ln1 = std::make_unique<SkipLayerNorm>(hb(w.g1).data(), hb(w.be1).data(), hidden);
+    auto ln2 = std::make_unique<SkipLayerNorm>(hb(w.g2).data(), hb(w.be2).data(), hidden);
+    Encoder<enc_cfg> enc(std::move(attn), std::move(ln1), std::move(ln2), std::move(l1), std::move(l2), model);
+
+    CHECK(et_linear_skip_layernorm_pays(T, ff, hidden) == 1, "fused Linear + LayerNorm expected to pay here");
+    culib::CUDA_ptr<half> dx(to_half(x)), dout((size_t)T * hidden);
+    enc.forward(dout.get(), dx.get());
+    enc.forward(dout.get(), dx.get());
+    CHECK(device_error() == 0, "device error");
+    std::vector<float> ref((size_t)T * hidden);
+    orc_encoder_layer(x.data(), ref.data(), batch, seq, hidden, nhead, hidden, hidden, ff, w.wqkv.data(),
+                      w.bqkv.data(), w.wo.data(), w.bo.data(), w.w1.data(), w.b1.data(), w.w2.data(),
+                      w.b2.data(), w.g1.data(), w.be1.data(), w.g2.data(), w.be2.data(), 2, mask_kind,
+                      nullptr, nullptr, 0);
+    char what[96];
+    std::snprintf(what, sizeof what, "Encoder<dense, fused QKV, fused LN> b%d s%d mask%d", batch, seq, mask_kind);
+    compare(to_float(dout), ref, what);
+}
+
 // Attention with three dense projections on side streams; Prune_attn with a row-pruned V
 static void test_attention_variants() {
     const int batch = 2, seq = 128, hidden = 256, nhead = 4, T = batch * seq, dh = hidden / nhead;
@@ -331,6 +382,8 @@ int main() {
         test_norms();
         test_encoder_tile(2, 128, 1);
         test_encoder_tile(3, 80, 0);
+        test_encoder_dense(2, 128, 1);
+        test_encoder_dense(3, 100, 0);
         test_attention_variants();
         test_attention_fused_qkv_dense();
         test_errors();
