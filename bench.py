@@ -239,9 +239,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # the job's stdout carries exactly one JSON line: keep NCCL's version banner out of it
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # the job's stdout carries exactly one JSON line: NCCL's own messages (the version
+        # banner it prints at the WARN and VERSION levels included) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     if args.attention_only:
