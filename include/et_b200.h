@@ -311,6 +311,10 @@ int et_fused_vo_attention_pruned_fwd(const et_half* Q, const et_half* K, const e
  * Whole encoder layer (post-LN), the call Encoder<config>::forward makes
  * (Encoder/Encoder.h:81-96):
  *   a = O(attention(QKV(x)));  y = LN1(a + x);  out = LN2(W2 act(W1 y + b1) + b2 + y)
+ * With dense weights the layer runs as four kernels where the shapes allow it: Q/K/V
+ * projection + attention (et_qkv_attention_fwd), O projection + residual + LN1
+ * (et_linear_skip_layernorm_fwd), FFN1 + activation, FFN2 + residual + LN2; the separate
+ * calls otherwise.
  * ================================================================================= */
 #define ET_FMT_DENSE 0
 #define ET_FMT_TILE 1        /* tile-CSR as the reference stores it                        */
