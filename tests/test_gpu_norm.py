@@ -54,7 +54,8 @@ def test_bias_add(et, cuda):
 
 
 @pytest.mark.parametrize("T,inn,out", [(2048, 768, 768), (300, 256, 256), (130, 3072, 768),
-                                       (100, 512, 1024), (1, 64, 384), (257, 1024, 1024)])
+                                       (100, 512, 1024), (1, 64, 384), (257, 1024, 1024),
+                                       (70, 80, 256), (129, 16, 640)])
 @pytest.mark.parametrize("with_bias,with_resid", [(True, True), (False, True), (True, False)])
 def test_linear_skip_layernorm(et, orc, cuda, T, inn, out, with_bias, with_resid):
     """Dense Linear + residual + LayerNorm in one kernel (a cluster of out / 128 CTAs per row
