@@ -383,7 +383,7 @@ __global__ void vo_scatter_cols_kernel(const __half* __restrict__ comp, const in
         const int c = __ldg(col_id + (i - t * nnz_col));
         if (c < 0 || c >= emdim) continue;
         const float b = bias ? __half2float(__ldg(bias + c)) : 0.f;
-        out[t * emdim + c] = __float2half_rn(__half2float(comp[i]) + b);
+        out[t * emdim + c] = __float2half_rn(__half2float(__ldcg(comp + i)) + b);
     }
 }
 

@@ -89,6 +89,10 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 
 // Blocks until every kernel this one depends on has completed and its writes are visible.
 // A no-op when the kernel was launched without programmatic dependencies.
+// A dependent kernel starts BEFORE its predecessors have finished, so data they produce is not
+// read-only for its lifetime: read such data with TMA or __ldcg (L2), never with __ldg or a
+// plain L1-cached load - an SM's L1 may still hold lines of the buffer's previous contents that
+// an earlier kernel fetched there (seen as a rare wrong residual in deep dependent chains).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Lets the next kernel on the stream start its prologue.
 __device__ __forceinline__ void pdl_launch_dependents() {

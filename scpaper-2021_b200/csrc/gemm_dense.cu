@@ -471,7 +471,7 @@ __global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __re
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t t = i / nn_col;
         const int k = static_cast<int>(i - t * nn_col);
-        G[i] = X[t * in + __ldg(col_id + k)];
+        G[i] = __ldcg(X + t * in + __ldg(col_id + k));
     }
 }
 

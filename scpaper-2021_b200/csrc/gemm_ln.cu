@@ -182,13 +182,14 @@ gemm_ln_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         pdl_wait();  // the residual and the output buffer belong to earlier kernels
         // the residual does not depend on this kernel's products: fetch it while they run
+        // (through L2: an earlier kernel wrote it while this one was already resident)
         uint4 res[8];
         const int row = m0 + r;
         if (g.resid != nullptr && row < g.M) {
             const uint4* rp = reinterpret_cast<const uint4*>(
                 g.resid + static_cast<size_t>(row) * g.ldr + n0 + half * 64);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) res[i] = __ldg(rp + i);
+            for (int i = 0; i < 8; ++i) res[i] = __ldcg(rp + i);
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) res[i] = make_uint4(0u, 0u, 0u, 0u);

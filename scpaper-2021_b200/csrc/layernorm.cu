@@ -72,10 +72,10 @@ skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__
         const int c = lane + it * 32;
         if (c < nchunk) {
             float v[8];
-            unpack8(__ldg(s4 + c), v);
+            unpack8(__ldcg(s4 + c), v);
             if (k4) {
                 float w[8];
-                unpack8(__ldg(k4 + c), w);
+                unpack8(__ldcg(k4 + c), w);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] += w[j];
             }
@@ -102,10 +102,10 @@ skip_layernorm_kernel(const __half* __restrict__ src, const __half* __restrict__
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = cache[it][j];
             } else {
-                unpack8(__ldg(s4 + c), v);
+                unpack8(__ldcg(s4 + c), v);
                 if (k4) {
                     float w[8];
-                    unpack8(__ldg(k4 + c), w);
+                    unpack8(__ldcg(k4 + c), w);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) v[j] += w[j];
                 }
@@ -154,7 +154,7 @@ skip_layernorm_partials_kernel(const float* __restrict__ partials, int nsplit, s
             for (int p = 0; p < nsplit; ++p) {
                 const float4* src = reinterpret_cast<const float4*>(
                     partials + p * split_stride + static_cast<size_t>(row) * size + c * 8);
-                const float4 a = __ldg(src), b = __ldg(src + 1);
+                const float4 a = __ldcg(src), b = __ldcg(src + 1);
                 v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
                 v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
             }
@@ -165,7 +165,7 @@ skip_layernorm_partials_kernel(const float* __restrict__ partials, int nsplit, s
                 for (int j = 0; j < 8; ++j) v[j] += w[j];
             }
             if (k4) {
-                unpack8(__ldg(k4 + c), w);
+                unpack8(__ldcg(k4 + c), w);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] += w[j];
             }

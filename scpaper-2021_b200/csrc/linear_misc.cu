@@ -32,8 +32,8 @@ linear_1x16_kernel(const int* __restrict__ tile_idx, const int* __restrict__ row
         if (beg >= end) continue;  // uniform over the CTA
         float x[16];
         {
-            const uint4 a = __ldg(reinterpret_cast<const uint4*>(xrow + p * 16));
-            const uint4 b = __ldg(reinterpret_cast<const uint4*>(xrow + p * 16 + 8));
+            const uint4 a = __ldcg(reinterpret_cast<const uint4*>(xrow + p * 16));
+            const uint4 b = __ldcg(reinterpret_cast<const uint4*>(xrow + p * 16 + 8));
             const __half2* ha = reinterpret_cast<const __half2*>(&a);
             const __half2* hb = reinterpret_cast<const __half2*>(&b);
 #pragma unroll
@@ -99,7 +99,7 @@ linear_csr_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     for (int i = threadIdx.x; i < CSR_TOKENS * chunks; i += CSR_THREADS) {
         const int tt = i / chunks, c = i - tt * chunks;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (tt < nt) v = __ldg(reinterpret_cast<const uint4*>(X + static_cast<size_t>(t0 + tt) * in) + c);
+        if (tt < nt) v = __ldcg(reinterpret_cast<const uint4*>(X + static_cast<size_t>(t0 + tt) * in) + c);
         reinterpret_cast<uint4*>(xs + static_cast<size_t>(tt) * in)[c] = v;
     }
     __syncthreads();

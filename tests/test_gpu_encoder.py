@@ -185,3 +185,22 @@ def test_host_pipeline_matches_resident_forward(et, cuda):
     assert et.device_error() == 0
     for i, (y, w) in enumerate(zip(ys, want)):
         assert torch.equal(y, w), f"batch {i} differs"
+
+
+def test_repeated_forwards_agree(et, orc, cuda):
+    """Dependent launches start kernels before their predecessors finish; a buffer a predecessor
+    writes must never be read through a non-coherent path.  Forty forwards of a short stack
+    (few CTAs per kernel, so that several kernels are resident at once) must all agree."""
+    import torch
+    batch, seq, hidden, nhead, ff = 4, 128, 768, 12, 3072
+    w = et.synth.encoder_layer_weights(2021, 3, hidden, ff, bias_std=0.02, ln_noise=0.05)
+    x = et.synth.normal(2021, 93, (batch * seq, hidden), 1.0)
+    layers = [et.EncoderLayer(w, nhead, et.ACT_GELU, device=cuda) for _ in range(2)]
+    stack = et.EncoderStack(layers, batch, seq, device=cuda)
+    xd = torch.from_numpy(x).to(cuda)
+    outs = [stack.forward(xd).clone() for _ in range(40)]
+    torch.cuda.synchronize()
+    assert et.device_error() == 0
+    assert all(torch.equal(o, outs[0]) for o in outs[1:])
+    assert_close(outs[0].float().cpu().numpy(), _oracle_stack(orc, [w, w], x, batch, seq, nhead),
+                 "two-layer stack, repeated")
