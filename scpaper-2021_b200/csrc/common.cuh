@@ -404,6 +404,14 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
                  "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of a cluster barrier, for threads that have work between them (every thread
+// of the cluster executes one arrive and one wait per phase).
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait;" ::: "memory");
+}
 // Cluster-window address of the same shared-memory offset in CTA `cta` of the cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t cta) {
     uint32_t r;

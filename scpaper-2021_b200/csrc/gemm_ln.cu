@@ -105,6 +105,10 @@ gemm_ln_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    // First half of a start-up cluster barrier: its second half, just before the first write
+    // into a neighbour's shared memory, then finds every CTA of the cluster running (the wait is
+    // long over by that time, so it costs nothing).
+    cluster_arrive_relaxed();
 
     // this thread's 64 values of its row (epilogue warps only), kept across the cluster barrier
     float v[64];
@@ -231,6 +235,7 @@ gemm_ln_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         s_part[half * BM + r] = make_float2(sum, sq);
         asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+        cluster_wait();  // second half of the start-up barrier: every neighbour is running
         if (half == 0) {
             const float2 o = s_part[BM + r];
             const uint32_t mine = smem_u32(&s_stats[rank * BM + r]);
@@ -239,6 +244,7 @@ gemm_ln_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     }
 
+    if (warp < 2) cluster_wait();  // (their half of the start-up barrier)
     // every thread of every CTA of the cluster: the row statistics are complete after this
     __syncwarp();
     cluster_sync_all();
