@@ -128,6 +128,9 @@ int et_linear_tile_packed_fwd(const int32_t* row_ptr, const uint32_t* pk_mask, c
  * out >= 3072, 15 % for out >= 2048, 2 % otherwise: measured crossovers at 2048 tokens);
  * et_tile_densify expands tile-CSR (device arrays) into dense[out, in], pruned tiles zero, for
  * et_linear_dense_fwd.  The result equals et_linear_tile_fwd's up to fp32 summation order.
+ * Like every weight, `dense` must be complete (stream synchronised) before the first Linear
+ * call that uses it: the Linear kernels fetch weights before they wait for their predecessors
+ * on the stream.  The same holds for the output of et_tile_pack_tiles.
  * Same reference call as et_linear_tile_fwd (Linear/SPMM_tile.cu:312-324). */
 int et_tile_prefer_dense(int in, int out, int nnz_tiles);
 int et_tile_densify(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,

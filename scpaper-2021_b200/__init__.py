@@ -172,6 +172,9 @@ def tile_densify(row_ptr, row_off, tiles, inn: int, out: int):
     check(lib().et_tile_densify(_p(row_ptr), _p(row_off) if nnz else None,
                                 _p(tiles) if nnz else None, c_int(nnz), c_int(inn), c_int(out),
                                 _p(dense), _stream()), "et_tile_densify")
+    # a weight must be complete before the first Linear call that uses it: those calls fetch
+    # weights ahead of their predecessors on the stream
+    torch.cuda.current_stream().synchronize()
     return dense
 
 
