@@ -126,15 +126,17 @@ def build_weights(et, tile_sparsity: float = 0.0):
 
 def cpu_sample(et, orc, ws, batch: int, reps: int):
     """Times the oracle's encoder layer (all host threads) on `batch` sequences; returns the
-    BERT-base sequences/s this extrapolates to (12 identical layers) and the best time."""
+    BERT-base sequences/s this extrapolates to (12 identical layers), the best time, and the
+    sample's input and output (the caller checks the GPU layer against them)."""
     import numpy as np
     x = et.synth.normal(SEED, 7, (batch * SEQ, HIDDEN), 1.0).astype(np.float32)
     best = float("inf")
+    out = None
     for _ in range(reps):
         t0 = time.perf_counter()
-        orc.encoder_layer(x, ws[0], batch, SEQ, NHEAD, 2, 0)
+        out = orc.encoder_layer(x, ws[0], batch, SEQ, NHEAD, 2, 0)
         best = min(best, time.perf_counter() - t0)
-    return batch / (best * LAYERS), best
+    return batch / (best * LAYERS), best, x, out
 
 
 def run_reference(args, rank: int):
@@ -496,7 +498,22 @@ def main():
             orc = entry.load_oracle()
             orc.build()
             orc.set_num_threads(len(os.sched_getaffinity(0)))
-            cpu_value, best = cpu_sample(et, orc, ws, 128, 3)
+            cpu_value, best, cx, cy = cpu_sample(et, orc, ws, 128, 3)
+            # the oracle as checker: layer 0 of the benchmarked stack, at the benchmarked shape
+            # (same kernels, same plan), on the sample's first BATCH sequences
+            one = et.EncoderStack([layers[0]], BATCH, SEQ, device=dev)
+            with torch.cuda.stream(stream):
+                gy = one.forward(torch.from_numpy(cx[:T].astype(np.float16)).to(dev)).float()
+                stream.synchronize()
+            gy = gy.cpu().numpy()
+            ref = np.asarray(cy[:T], dtype=np.float32)
+            rel = float(np.linalg.norm(gy - ref) / np.linalg.norm(ref))
+            mx = float(np.abs(gy - ref).max())
+            line["parity"] = {"rel_l2": rel, "max_abs": mx, "tolerance": [5e-3, 2e-2],
+                              "what": f"layer 0 of the benchmarked stack on {BATCH} sequences "
+                                      "against the CPU oracle"}
+            if not (rel <= 5e-3 and mx <= 2e-2) or et.device_error() != 0:
+                raise SystemExit(f"parity check failed: rel-L2 {rel:.3e}, max-abs {mx:.3e}")
             line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": orc.num_threads(),
                                     "kind": "port",
                                     "sample": "best of 3 runs of one encoder layer over 128 sequences "
