@@ -257,10 +257,8 @@ def main():
                           "device_error": et.device_error()}))
         return
 
-    et.lib().et_debug_launch_count.restype = ctypes.c_longlong
-
     def launch_count():
-        return int(et.lib().et_debug_launch_count())
+        return int(et.lib().et_launch_count())
 
     job = et.sharding.Job(rank=rank, world=world, device=dev)
 

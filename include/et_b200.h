@@ -53,6 +53,11 @@ int et_built_for_sm(void);
  * Replaces the reference's cudaChk/assert/exit(1) convention (lib/utils.cu:28-35). */
 int et_device_error(int* code);
 
+/* Kernels launched by this library so far in this process (host-side count; a CUDA graph
+ * replays what was counted while it was captured).  Diagnostic only: lets a caller state how
+ * many kernels one call issued.  The reference has no counterpart (it counts nothing). */
+long long et_launch_count(void);
+
 /* ---- activation / epilogue selectors ------------------------------------------- */
 #define ET_ACT_NONE 0
 #define ET_ACT_RELU 1 /* Encoder/Encoder.h:29-32                                       */
@@ -192,6 +197,18 @@ int et_linear_csr_fwd(const int32_t* indptr, const int32_t* indices, const et_ha
                       int nnz, const et_half* bias, const et_half* X, et_half* Y, int T, int in,
                       int out, int act, et_stream stream);
 
+/* 1x16-vector weights on the tensor cores.  A tensor-core product cannot skip single vectors
+ * inside a 16 x 16 tile, and at 90 % vector sparsity four tiles in five still hold a vector,
+ * so the fast path for this format is the dense GEMM on the expanded weight:
+ * et_1x16_prefer_dense returns 1 when that is expected to beat et_linear_1x16_fwd (unless
+ * fewer than 1 % of the vectors are stored), et_1x16_densify expands the device arrays into
+ * dense[out, in] (pruned vectors zero) for et_linear_dense_fwd.  `dense` must be complete
+ * (stream synchronised) before the first Linear call that uses it.  Same reference call as
+ * et_linear_1x16_fwd (Linear/SPMM1x16.cu:35-124). */
+int et_1x16_prefer_dense(int in, int out, int nvec);
+int et_1x16_densify(const int32_t* tile_idx, const int32_t* row_idx, const et_half* data, int nvec,
+                    int in, int out, et_half* dense, et_stream stream);
+
 /* Host-side validators for index arrays that live in HOST memory (call before upload).
  * Return ET_OK or ET_ERR_INDEX; they never touch the GPU. */
 int et_validate_tile_mat(const int32_t* row_ptr, const int32_t* row_off, int nnz_tiles, int in,
@@ -317,20 +334,36 @@ int et_fused_vo_attention_pruned_fwd(const et_half* Q, const et_half* K, const e
  * With dense weights the layer runs as four kernels where the shapes allow it: Q/K/V
  * projection + attention (et_qkv_attention_fwd), O projection + residual + LN1
  * (et_linear_skip_layernorm_fwd), FFN1 + activation, FFN2 + residual + LN2; the separate
- * calls otherwise.
+ * calls otherwise.  A row-pruned FFN1 followed by a column-pruned FFN2 over the SAME id list
+ * (ffn1.row_ptr == ffn2.row_ptr, the pruned hidden units of the feed-forward block) runs as
+ * two dense products of the kept width: the pruned units are never materialised.
  * ================================================================================= */
 #define ET_FMT_DENSE 0
 #define ET_FMT_TILE 1        /* tile-CSR as the reference stores it                        */
 #define ET_FMT_TILE_PACKED 2 /* re-packed tile-CSR (et_tile_pack_plan / et_tile_pack_tiles) */
+#define ET_FMT_1X16 3        /* 1x16 vectors (mat1x16)                                     */
+#define ET_FMT_ROW 4         /* kept output rows (row_mat)                                 */
+#define ET_FMT_COL 5         /* kept input columns (col_mat)                               */
+#define ET_FMT_CSR 6         /* CSR                                                        */
 
+/* One Linear layer of the encoder in any of the reference's weight formats.  The index and
+ * count fields are shared between formats:
+ *   format            weight                 row_ptr          row_off        nnz_tiles
+ *   DENSE             W[out, in]             -                -              -
+ *   TILE              tiles[nnz][256]        row_ptr          row_off        stored tiles
+ *   TILE_PACKED       packed tiles           row_ptr          -              stored tiles
+ *   1X16              data[nvec][16]         tile_idx         row_idx        nvec
+ *   ROW               rows[nn_row, in]       row_id[nn_row]   -              nn_row
+ *   COL               cols[out, nn_col]      col_id[nn_col]   -              nn_col
+ *   CSR               data[nnz]              indptr[out + 1]  indices[nnz]   nnz
+ * (argument meaning as in the et_linear_*_fwd call of each format). */
 typedef struct {
-    int format;             /* ET_FMT_DENSE, ET_FMT_TILE or ET_FMT_TILE_PACKED          */
+    int format;             /* one of ET_FMT_*                                          */
     int in, out;
-    const et_half* weight;  /* dense: W[out, in]; tile: tiles[nnz][256] (packed order for
-                               ET_FMT_TILE_PACKED)                                       */
-    const int32_t* row_ptr; /* tile formats                                             */
-    const int32_t* row_off; /* ET_FMT_TILE only                                         */
-    int nnz_tiles;          /* tile formats                                             */
+    const et_half* weight;
+    const int32_t* row_ptr; /* first index array of the format                          */
+    const int32_t* row_off; /* second index array of the format                         */
+    int nnz_tiles;          /* stored units of the format                               */
     const et_half* bias;    /* [out] or NULL                                            */
     const uint32_t* pk_mask; /* ET_FMT_TILE_PACKED only                                 */
     const int32_t* pk_off;   /* ET_FMT_TILE_PACKED only                                 */

@@ -13,20 +13,23 @@ from ctypes import c_float, c_int, c_size_t, c_void_p
 from . import sharding, synth, weights  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libet_b200.so")
+# ET_B200_TEST_HOOKS=1 selects the build that also exports the et_debug_* test hooks (forced
+# kernel plans, instruction-rate probes); the product library has none of them.
+LIB_PATH = os.path.join(_HERE, "libet_b200_hooks.so" if os.environ.get("ET_B200_TEST_HOOKS") == "1"
+                        else "libet_b200.so")
 
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_PADDING, MASK_ADDITIVE = 0, 1, 2, 3
-FMT_DENSE, FMT_TILE, FMT_TILE_PACKED = 0, 1, 2
+FMT_DENSE, FMT_TILE, FMT_TILE_PACKED, FMT_1X16, FMT_ROW, FMT_COL, FMT_CSR = range(7)
 
 # Every symbol include/et_b200.h declares (checked by the CPU test-suite against the header).
 ABI_SYMBOLS = [
-    "et_status_string", "et_version", "et_built_for_sm", "et_device_error",
+    "et_status_string", "et_version", "et_built_for_sm", "et_device_error", "et_launch_count",
     "et_linear_dense_fwd", "et_linear_skip_layernorm_fwd", "et_linear_skip_layernorm_pays", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
     "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_tile_prefer_dense", "et_tile_densify",
     "et_linear_row_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
-    "et_linear_1x16_fwd",
+    "et_linear_1x16_fwd", "et_1x16_prefer_dense", "et_1x16_densify",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
     "et_validate_csr", "et_skip_layernorm_fwd", "et_layernorm_fwd", "et_act_fwd",
     "et_bias_add_fwd", "et_attention_fwd", "et_qkv_attention_fwd", "et_attention_pruned_v_fwd",
@@ -68,6 +71,7 @@ def lib() -> ctypes.CDLL:
         L = ctypes.CDLL(LIB_PATH)
         L.et_status_string.restype = ctypes.c_char_p
         L.et_status_string.argtypes = [c_int]
+        L.et_launch_count.restype = ctypes.c_longlong
         L.et_encoder_layer_workspace_bytes.restype = c_size_t
         L.et_encoder_layer_workspace_bytes.argtypes = [c_void_p, c_int, c_int]
         _lib = L
@@ -243,6 +247,24 @@ def linear_1x16(x, tile_idx, row_idx, data, out, bias=None, act=ACT_NONE):
     return y
 
 
+def v1x16_prefer_dense(inn: int, out: int, nvec: int) -> bool:
+    """Plan-time choice for 1x16-vector weights: True when the dense GEMM on the expanded weight
+    is expected to beat the vector kernel."""
+    return bool(lib().et_1x16_prefer_dense(c_int(inn), c_int(out), c_int(nvec)))
+
+
+def v1x16_densify(tile_idx, row_idx, data, inn: int, out: int):
+    """dense[out, in] fp16 from device 1x16 arrays (pruned vectors zero)."""
+    import torch
+    dense = torch.empty((out, inn), dtype=torch.float16, device=tile_idx.device)
+    nvec = 0 if row_idx is None else int(row_idx.shape[0])
+    check(lib().et_1x16_densify(_p(tile_idx), _p(row_idx) if nvec else None,
+                                _p(data) if nvec else None, c_int(nvec), c_int(inn), c_int(out),
+                                _p(dense), _stream()), "et_1x16_densify")
+    torch.cuda.current_stream().synchronize()  # weights must be complete before their first use
+    return dense
+
+
 def linear_csr(x, indptr, indices, data, out, bias=None, act=ACT_NONE):
     T, inn = x.shape
     y = _empty((T, out), x)
@@ -409,25 +431,74 @@ class EncoderLayer:
     returns; tile_sparse=True stores the four Linear layers in re-packed tile-CSR form,
     tile_sparse="unpacked" in the reference's tile-CSR order, and tile_sparse="auto" lets
     et_tile_prefer_dense choose per weight between the packed tile kernel and the dense GEMM
-    on the expanded weight."""
+    on the expanded weight.
+
+    `formats` overrides that per weight ("wqkv", "wo", "w1", "w2"): "dense", "1x16" (the vector
+    kernel), "1x16_auto" (et_1x16_prefer_dense chooses between it and the dense GEMM on the
+    expanded weight), "csr", ("row", ids) (kept output rows) or ("col", ids) (kept input
+    columns).  ("row", ids) on "w1" with ("col", ids) on "w2" over the same `ids` array object
+    describes pruned hidden units of the feed-forward block: both products run at the kept
+    width."""
 
     def __init__(self, weights: dict, nhead: int, act_kind: int = ACT_GELU, device="cuda",
-                 tile_sparse: bool = False):
+                 tile_sparse: bool = False, formats: dict | None = None):
         import numpy as np
         import torch
         self._keep = []
+        formats = formats or {}
+        id_cache = {}  # id(list object) -> device tensor, so that equal lists share one array
 
         def dev(a):
             t = torch.from_numpy(np.ascontiguousarray(a)).to(device)
             self._keep.append(t)
             return t
 
+        def dev_ids(ids):
+            if id(ids) not in id_cache:
+                id_cache[id(ids)] = dev(np.ascontiguousarray(ids, dtype=np.int32))
+            return id_cache[id(ids)]
+
         def lin(wname, bname):
             W = weights[wname]
             d = LinearDesc()
             d.out, d.in_ = int(W.shape[0]), int(W.shape[1])
             d.bias = weights[bname] is not None and dev(weights[bname]).data_ptr() or None
-            if tile_sparse:
+            fmt = formats.get(wname)
+            if fmt is not None and fmt != "dense":
+                kind = fmt if isinstance(fmt, str) else fmt[0]
+                if kind in ("1x16", "1x16_auto"):
+                    tidx, ridx, data = synth.dense_to_1x16(W)
+                    nvec = int(ridx.shape[0])
+                    dt, dr = dev(tidx), dev(ridx) if nvec else None
+                    dd = dev(data) if nvec else None
+                    if kind == "1x16_auto" and v1x16_prefer_dense(d.in_, d.out, nvec):
+                        dense = v1x16_densify(dt, dr, dd, d.in_, d.out)
+                        self._keep.append(dense)
+                        d.format, d.weight = FMT_DENSE, dense.data_ptr()
+                    else:
+                        d.format, d.nnz_tiles = FMT_1X16, nvec
+                        d.row_ptr = dt.data_ptr()
+                        if nvec:
+                            d.row_off, d.weight = dr.data_ptr(), dd.data_ptr()
+                elif kind == "row":
+                    ids = fmt[1]
+                    _, rows = synth.dense_to_row(W, np.asarray(ids))
+                    d.format, d.nnz_tiles = FMT_ROW, int(len(ids))
+                    d.row_ptr, d.weight = dev_ids(ids).data_ptr(), dev(rows).data_ptr()
+                elif kind == "col":
+                    ids = fmt[1]
+                    _, cols = synth.dense_to_col(W, np.asarray(ids))
+                    d.format, d.nnz_tiles = FMT_COL, int(len(ids))
+                    d.row_ptr, d.weight = dev_ids(ids).data_ptr(), dev(cols).data_ptr()
+                elif kind == "csr":
+                    indptr, indices, data = synth.dense_to_csr(W)
+                    d.format, d.nnz_tiles = FMT_CSR, int(indices.shape[0])
+                    d.row_ptr = dev(indptr).data_ptr()
+                    if d.nnz_tiles:
+                        d.row_off, d.weight = dev(indices).data_ptr(), dev(data).data_ptr()
+                else:
+                    raise EtError(f"unknown weight format {fmt!r}")
+            elif tile_sparse and fmt is None:
                 rp, ro, tiles = synth.dense_to_tile(W)
                 d.nnz_tiles = int(tiles.shape[0])
                 # the fused projection + attention kernel needs a dense Q/K/V weight and beats

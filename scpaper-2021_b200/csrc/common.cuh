@@ -38,7 +38,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Programmatic dependent launch: when enabled (default) kernels are launched so that their
 // prologue (barrier set-up, tensor-memory allocation, weight prefetch) may overlap the tail
 // of the previous kernel on the stream; each kernel calls pdl_wait() before it touches data
-// the previous kernel produced.  et_debug_set_pdl(0) falls back to plain launches.
+// the previous kernel produced.  the test-hook build can fall back to plain launches.
 bool pdl_enabled();
 void set_pdl_enabled(bool on);
 
@@ -61,7 +61,7 @@ enum : int {
 
 #if defined(__CUDACC__)
 
-// Every kernel launch of the library is counted on the host (et_debug_launch_count), so that a
+// Every kernel launch of the library is counted on the host (et_launch_count), so that a
 // caller can state how many kernels one call issued.
 void count_launch();
 

@@ -23,9 +23,20 @@ constexpr int kMaxSplits = 4;
 
 struct LayerBuffers {
     __half *qkv, *z, *a, *y, *f;
+    __half* gather;  // [T, widest column-pruned input]: scratch of the column-pruned Linears
+    size_t gather_bytes;
     float* part;  // split-K partial sums [kMaxSplits][T, hidden]
     size_t total;
 };
+
+// A row-pruned FFN1 feeding a column-pruned FFN2 over the same id list: the pruned hidden
+// units of the feed-forward block.  Both products then run at the kept width.
+bool ffn_is_compressed_pair(const et_encoder_layer_t* L) {
+    return L->ffn1.format == ET_FMT_ROW && L->ffn2.format == ET_FMT_COL &&
+           L->ffn1.row_ptr != nullptr && L->ffn1.row_ptr == L->ffn2.row_ptr &&
+           L->ffn1.nnz_tiles == L->ffn2.nnz_tiles && L->ffn1.nnz_tiles > 0 &&
+           L->ffn1.nnz_tiles % 8 == 0;
+}
 
 // Number of K slices for a dense [T, K] x [hidden, K]^T product feeding a LayerNorm: few
 // output tiles and a long K leave most SMs idle unless K is split.
@@ -89,13 +100,39 @@ LayerBuffers carve(const et_encoder_layer_t* L, int batch, int seq, void* base) 
     b.a = take(T * L->hidden);
     b.y = take(T * L->hidden);
     b.f = take(T * L->ff);
+    size_t widest = 0;
+    for (const et_linear_t* lin : {&L->qkv, &L->o, &L->ffn1, &L->ffn2})
+        if (lin->format == ET_FMT_COL && lin->nnz_tiles > 0 &&
+            static_cast<size_t>(lin->nnz_tiles) > widest)
+            widest = static_cast<size_t>(lin->nnz_tiles);
+    if (ffn_is_compressed_pair(L)) widest = 0;  // that pair needs no gather
+    b.gather_bytes = T * widest * sizeof(__half);
+    b.gather = take(T * widest);
     b.part = reinterpret_cast<float*>(take(2 * kMaxSplits * T * L->hidden));
     b.total = off;
     return b;
 }
 
 int run_linear(const et_linear_t& lin, const __half* X, __half* Y, int T, int act,
-               cudaStream_t stream) {
+               const LayerBuffers& buf, cudaStream_t stream) {
+    const et_half* Xe = reinterpret_cast<const et_half*>(X);
+    et_half* Ye = reinterpret_cast<et_half*>(Y);
+    switch (lin.format) {
+        case ET_FMT_1X16:
+            return et_linear_1x16_fwd(lin.row_ptr, lin.row_off, lin.weight, lin.nnz_tiles, lin.bias,
+                                      Xe, Ye, T, lin.in, lin.out, act, stream);
+        case ET_FMT_ROW:
+            return et_linear_row_fwd(lin.row_ptr, lin.weight, lin.nnz_tiles, lin.bias, Xe, Ye, T,
+                                     lin.in, lin.out, act, stream);
+        case ET_FMT_COL:
+            return et_linear_col_fwd(lin.row_ptr, lin.weight, lin.nnz_tiles, lin.bias, Xe, Ye, T,
+                                     lin.in, lin.out, act, reinterpret_cast<et_half*>(buf.gather),
+                                     buf.gather_bytes, stream);
+        case ET_FMT_CSR:
+            return et_linear_csr_fwd(lin.row_ptr, lin.row_off, lin.weight, lin.nnz_tiles, lin.bias,
+                                     Xe, Ye, T, lin.in, lin.out, act, stream);
+        default: break;
+    }
     if (lin.format == ET_FMT_DENSE)
         return launch_gemm_f16(X, lin.in, reinterpret_cast<const __half*>(lin.weight), lin.in,
                                reinterpret_cast<const __half*>(lin.bias), Y, lin.out, nullptr, 0, T,
@@ -132,6 +169,7 @@ int check_layer(const et_encoder_layer_t* L) {
 
 extern "C" {
 
+#ifdef ET_TEST_HOOKS
 // Test hook: number of K slices of the FFN2 product (0 = automatic, 1 = no split, n > 1 = n
 // slices on single-CTA tiles, -2 = K slices on 256 x 256 CTA-pair tiles).
 void et_debug_force_ffn2_splits(int n) { et::g_force_splits = n; }
@@ -139,6 +177,7 @@ void et_debug_force_ffn2_splits(int n) { et::g_force_splits = n; }
 // Test hook: 0 = never fuse the Q/K/V projection into the attention kernel.
 void et_debug_set_qkv_fusion(int on) { et::g_qkv_fusion = on != 0; }
 void et_debug_set_ln_fusion(int mode) { et::g_ln_fusion = mode; }
+#endif  // ET_TEST_HOOKS
 
 size_t et_encoder_layer_workspace_bytes(const et_encoder_layer_t* layer, int batch, int seq) {
     if (et::check_layer(layer) != ET_OK || batch <= 0 || seq <= 0) return 0;
@@ -177,7 +216,7 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                  1.0f / sqrtf(static_cast<float>(dh_qk)), s)) != ET_OK)
             return st;
     } else {
-        if ((st = et::run_linear(layer->qkv, xin, b.qkv, T, ET_ACT_NONE, s)) != ET_OK) return st;
+        if ((st = et::run_linear(layer->qkv, xin, b.qkv, T, ET_ACT_NONE, b, s)) != ET_OK) return st;
         if ((st = et::launch_attention(b.qkv, b.qkv + layer->kdim, b.qkv + 2 * layer->kdim, b.z,
                                        batch, seq, layer->nhead, dh_qk, dh_v, ldqkv, ldqkv, ldqkv,
                                        layer->vdim, mask_kind, reinterpret_cast<const __half*>(mask),
@@ -198,20 +237,36 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                                      layer->hidden, T, layer->hidden, layer->vdim, s)) != ET_OK)
             return st;
     } else {
-        if ((st = et::run_linear(layer->o, b.z, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
+        if ((st = et::run_linear(layer->o, b.z, b.a, T, ET_ACT_NONE, b, s)) != ET_OK) return st;
         if ((st = et::launch_skip_layernorm(b.a, xin,
                                             reinterpret_cast<const __half*>(layer->ln1_gamma),
                                             reinterpret_cast<const __half*>(layer->ln1_beta), b.y,
                                             T, layer->hidden, s)) != ET_OK)
             return st;
     }
-    if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, s)) != ET_OK) return st;
-    if ((ln_fused & 2) && layer->ffn2.format == ET_FMT_DENSE &&
-        et::gemm_ln_applies(T, layer->hidden, layer->ff) &&
+    // ffn2 as the dense product it amounts to: W2 itself, or - for the compressed pair - the
+    // kept columns of W2 on the kept hidden units
+    const __half* w2 = reinterpret_cast<const __half*>(layer->ffn2.weight);
+    int k2 = layer->ff;
+    bool ffn2_dense = layer->ffn2.format == ET_FMT_DENSE;
+    if (et::ffn_is_compressed_pair(layer)) {
+        k2 = layer->ffn1.nnz_tiles;
+        ffn2_dense = true;
+        // f[T, kept] = act(y . rows^T + b1[kept ids]): GEMM with an index-list epilogue
+        if ((st = et::launch_gemm_f16(b.y, layer->hidden,
+                                      reinterpret_cast<const __half*>(layer->ffn1.weight),
+                                      layer->hidden,
+                                      reinterpret_cast<const __half*>(layer->ffn1.bias), b.f, k2,
+                                      layer->ffn1.row_ptr, 0, T, k2, layer->hidden, layer->act,
+                                      s)) != ET_OK)
+            return st;
+    } else if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, b, s)) != ET_OK) {
+        return st;
+    }
+    if ((ln_fused & 2) && ffn2_dense && et::gemm_ln_applies(T, layer->hidden, k2) &&
         reinterpret_cast<const __half*>(out) != b.y) {
         // FFN2, residual and LayerNorm in one kernel
-        return et::launch_gemm_ln(b.f, layer->ff,
-                                  reinterpret_cast<const __half*>(layer->ffn2.weight), layer->ff,
+        return et::launch_gemm_ln(b.f, k2, w2, k2,
                                   reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
                                   layer->hidden,
                                   reinterpret_cast<const __half*>(layer->ln2_gamma),
@@ -219,15 +274,13 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                                   reinterpret_cast<__half*>(out), layer->hidden, T, layer->hidden,
                                   layer->ff, s);
     }
-    const bool ffn2_splittable = layer->ffn2.format == ET_FMT_DENSE && layer->hidden <= 2048;
+    const bool ffn2_splittable = ffn2_dense && layer->hidden <= 2048;
     const int pair_splits =
-        ffn2_splittable ? et::pick_pair_splits(T, layer->hidden, layer->ff) : 0;
+        ffn2_splittable ? et::pick_pair_splits(T, layer->hidden, k2) : 0;
     if (pair_splits > 1) {
         // FFN2 as split-K partial sums on CTA pairs, reduced (with bias and residual) inside
         // the LayerNorm
-        if ((st = et::launch_gemm_pair_splitk(b.f, layer->ff,
-                                              reinterpret_cast<const __half*>(layer->ffn2.weight),
-                                              layer->ff, b.part, T, layer->hidden, layer->ff,
+        if ((st = et::launch_gemm_pair_splitk(b.f, k2, w2, k2, b.part, T, layer->hidden, k2,
                                               pair_splits, s)) != ET_OK)
             return st;
         return et::launch_skip_layernorm_partials(
@@ -237,12 +290,10 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
             reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
             layer->hidden, s);
     }
-    const int splits = ffn2_splittable ? et::pick_splits(T, layer->hidden, layer->ff) : 1;
+    const int splits = ffn2_splittable ? et::pick_splits(T, layer->hidden, k2) : 1;
     if (splits > 1) {
         // FFN2 as split-K partial sums, reduced (with bias and residual) inside the LayerNorm
-        if ((st = et::launch_gemm_f16_splitk(b.f, layer->ff,
-                                             reinterpret_cast<const __half*>(layer->ffn2.weight),
-                                             layer->ff, b.part, T, layer->hidden, layer->ff, splits,
+        if ((st = et::launch_gemm_f16_splitk(b.f, k2, w2, k2, b.part, T, layer->hidden, k2, splits,
                                              s)) != ET_OK)
             return st;
         return et::launch_skip_layernorm_partials(
@@ -252,7 +303,15 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
             reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
             layer->hidden, s);
     }
-    if ((st = et::run_linear(layer->ffn2, b.f, b.a, T, ET_ACT_NONE, s)) != ET_OK) return st;
+    if (ffn2_dense && layer->ffn2.format != ET_FMT_DENSE) {
+        if ((st = et::launch_gemm_f16(b.f, k2, w2, k2,
+                                      reinterpret_cast<const __half*>(layer->ffn2.bias), b.a,
+                                      layer->hidden, nullptr, 0, T, layer->hidden, k2, ET_ACT_NONE,
+                                      s)) != ET_OK)
+            return st;
+    } else if ((st = et::run_linear(layer->ffn2, b.f, b.a, T, ET_ACT_NONE, b, s)) != ET_OK) {
+        return st;
+    }
     return et::launch_skip_layernorm(b.a, b.y, reinterpret_cast<const __half*>(layer->ln2_gamma),
                                      reinterpret_cast<const __half*>(layer->ln2_beta),
                                      reinterpret_cast<__half*>(out), T, layer->hidden, s);

@@ -804,6 +804,7 @@ using et::launch_gemm_f16;
 
 extern "C" {
 
+#ifdef ET_TEST_HOOKS
 // Test hook: 0 = automatic tile width, else 64 / 128 / 256.
 void et_debug_force_gemm_bn(int bn) { et::gemm_force_bn(bn); }
 // Test hook: cap on the number of persistent CTAs (0 = one per SM).
@@ -814,6 +815,7 @@ void et_debug_force_gemm_tall(int mode) { et::gemm_force_tall(mode); }
 void et_debug_force_gemm_pair(int mode) { et::gemm_force_pair(mode); }
 // Test hook: -1 = automatic, 0 = one tile per CTA, 1 = persistent CTAs.
 void et_debug_force_gemm_persist(int mode) { et::gemm_force_persist(mode); }
+#endif  // ET_TEST_HOOKS
 
 int et_linear_dense_fwd(const et_half* X, const et_half* W, const et_half* bias, et_half* Y,
                         int T, int in, int out, int act, et_stream stream) {

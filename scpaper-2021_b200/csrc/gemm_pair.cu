@@ -508,7 +508,9 @@ int launch_gemm_pair_splitk(const __half* X, int ldx, const __half* W, int ldw, 
 
 }  // namespace et
 
+#ifdef ET_TEST_HOOKS
 extern "C" {
 // Test hook: -1 = automatic, 0 = one tile per CTA pair, 1 = persistent CTA pairs.
 void et_debug_force_gemm_pair_persist(int mode) { et::gemm_pair_force_persist(mode); }
 }
+#endif  // ET_TEST_HOOKS

@@ -123,10 +123,58 @@ linear_csr_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     }
 }
 
+// One CTA per 16-row set: dense[set * 16 + q][part * 16 .. + 16] = data[i] for every stored
+// vector i of the set (q = row_idx[i] % 16); thread = (vector slot in a group of 16, element).
+__global__ void densify_1x16_kernel(const int* __restrict__ tile_idx, const int* __restrict__ row_idx,
+                                    const __half* __restrict__ data, int npart, int in,
+                                    __half* __restrict__ dense) {
+    const int rset = blockIdx.x;
+    const int* tidx = tile_idx + static_cast<size_t>(rset) * (npart + 1);
+    const int beg0 = __ldg(tidx), end0 = __ldg(tidx + npart);
+    const int j = threadIdx.x & 15;
+    for (int i = beg0 + (threadIdx.x >> 4); i < end0; i += blockDim.x >> 4) {
+        // the part of vector i: the last p with tile_idx[p] <= i (binary search)
+        int lo = 0, hi = npart - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(tidx + mid) <= i) lo = mid; else hi = mid - 1;
+        }
+        const int q = __ldg(row_idx + i) & 15;
+        dense[(static_cast<size_t>(rset) * 16 + q) * in + lo * 16 + j] = data[static_cast<size_t>(i) * 16 + j];
+    }
+}
+
 }  // namespace
 }  // namespace et
 
 extern "C" {
+
+int et_1x16_prefer_dense(int in, int out, int nvec) {
+    if (in <= 0 || out <= 0 || (in & 15) || (out & 15)) return 0;
+    // a stored vector costs the CUDA-core kernel 16 multiply-adds per token, a dense 16 x 16
+    // tile costs the tensor core a sixteenth of a cycle per token: dense wins unless almost
+    // nothing is stored
+    const double total = static_cast<double>(out) * (in >> 4);
+    return nvec > 0.01 * total ? 1 : 0;
+}
+
+int et_1x16_densify(const int32_t* tile_idx, const int32_t* row_idx, const et_half* data, int nvec,
+                    int in, int out, et_half* dense, et_stream stream) {
+    if (!tile_idx || !dense || in <= 0 || out <= 0 || nvec < 0) return ET_ERR_INVALID_ARG;
+    if ((in & 15) || (out & 15)) return ET_ERR_SHAPE;
+    if (nvec > 0 && (!row_idx || !data)) return ET_ERR_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(dense, 0, static_cast<size_t>(in) * out * sizeof(__half), s) != cudaSuccess)
+        return ET_ERR_CUDA;
+    if (nvec > 0) {
+        et::count_launch();
+        et::densify_1x16_kernel<<<out >> 4, 256, 0, s>>>(tile_idx, row_idx,
+                                                          reinterpret_cast<const __half*>(data),
+                                                          in >> 4, in, reinterpret_cast<__half*>(dense));
+        if (cudaGetLastError() != cudaSuccess) return ET_ERR_CUDA;
+    }
+    return ET_OK;
+}
 
 int et_linear_1x16_fwd(const int32_t* tile_idx, const int32_t* row_idx, const et_half* data,
                        int nvec, const et_half* bias, const et_half* X, et_half* Y, int T, int in,

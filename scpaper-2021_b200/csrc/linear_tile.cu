@@ -554,8 +554,10 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
 
 extern "C" {
 
+#ifdef ET_TEST_HOOKS
 // Test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA (packed weights).
 void et_debug_set_tile_wide(int mode) { et::g_tile_wide = mode; }
+#endif  // ET_TEST_HOOKS
 
 int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,
                        int nnz_tiles, const et_half* bias, const et_half* X, et_half* Y, int T,

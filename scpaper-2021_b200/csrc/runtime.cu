@@ -144,11 +144,12 @@ const char* et_status_string(int status) {
     }
 }
 
+#ifdef ET_TEST_HOOKS
 // Test hook: 0 = plain launches, 1 = programmatic dependent launches (default).
 void et_debug_set_pdl(int on) { et::set_pdl_enabled(on != 0); }
-// Kernels launched by this library so far in this process (host-side count; a replayed CUDA
-// graph launches what was counted while it was captured).
-long long et_debug_launch_count() { return et::g_launches.load(std::memory_order_relaxed); }
+#endif  // ET_TEST_HOOKS
+
+long long et_launch_count(void) { return et::g_launches.load(std::memory_order_relaxed); }
 
 int et_version(void) { return 100; }
 int et_built_for_sm(void) { return 100; }

@@ -11,7 +11,12 @@
 #include <stdexcept>
 #include <string>
 
+// the C ABI header: beside this tree in the repository layout, else on the include path
+#if __has_include("../../../include/et_b200.h")
 #include "../../../include/et_b200.h"
+#else
+#include <et_b200.h>
+#endif
 
 namespace culib {
 namespace util {

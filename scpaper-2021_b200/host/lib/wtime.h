@@ -1,27 +1,34 @@
-// Wall-clock timers with the reference's names (lib/wtime.h:4-35): wtime synchronises the
-// device after every repetition, wtime_new once at the end.  Both return microseconds per
-// repetition.
+// Wall-clock timers with the reference's names and call forms (lib/wtime.h:4-35).
+//   wtime(times, action, prep):     prep() runs untimed before every repetition, action() is
+//                                   timed on its own; nothing synchronises the device unless
+//                                   the caller's action does.
+//   wtime_new(times, action, end):  `times` back-to-back action() calls, then end() once (the
+//                                   reference's drivers pass a device synchronisation there),
+//                                   all inside one timed region.
+// Both return microseconds per repetition.
 #pragma once
-#include <cuda_runtime.h>
-
 #include <chrono>
 
-template <typename F, typename... Args> double wtime(const int reps, F&& f, Args&&... args) {
+#include "range.hpp"
+
+template <typename _Action, typename _Prep>
+double wtime(const int times, _Action action, _Prep prep) {
     using clk = std::chrono::steady_clock;
-    double total = 0;
-    for (int i = 0; i < reps; ++i) {
-        auto t0 = clk::now();
-        f(args...);
-        cudaDeviceSynchronize();
+    double total = 0.0;
+    for (int i = 0; i < times; ++i) {
+        prep();
+        const auto t0 = clk::now();
+        action();
         total += std::chrono::duration<double, std::micro>(clk::now() - t0).count();
     }
-    return total / reps;
+    return total / times;
 }
 
-template <typename F, typename... Args> double wtime_new(const int reps, F&& f, Args&&... args) {
+template <typename _Action, typename _End>
+double wtime_new(const int times, _Action action, _End end) {
     using clk = std::chrono::steady_clock;
-    auto t0 = clk::now();
-    for (int i = 0; i < reps; ++i) f(args...);
-    cudaDeviceSynchronize();
-    return std::chrono::duration<double, std::micro>(clk::now() - t0).count() / reps;
+    const auto t0 = clk::now();
+    for (int i = 0; i < times; ++i) action();
+    end();
+    return std::chrono::duration<double, std::micro>(clk::now() - t0).count() / times;
 }

@@ -1,0 +1,4 @@
+// col_mat under the reference's own include path (mat_type/col_mat/col_mat.hpp); every weight container of the
+// path is defined in mat_type/mat_type.h.
+#pragma once
+#include "../mat_type.h"

@@ -198,3 +198,24 @@ def encoder_layer_weights(seed: int, layer: int, hidden: int, ff: int, kdim: int
             w[name + "_g"] = np.ones(hidden, np.float16)
             w[name + "_b"] = np.zeros(hidden, np.float16)
     return w
+
+
+def mixed_format_layer(seed: int, layer: int, hidden: int, ff: int, vec_sparsity: float = 0.9,
+                       ffn_sparsity: float = 0.5, **kw):
+    """One encoder layer pruned the way the paper's BERT-large configuration is: Q/K/V and O
+    projections as 1x16 vectors (`vec_sparsity` of them dropped), FFN hidden units pruned
+    (`ffn_sparsity`): the first FFN Linear keeps those output rows, the second reads exactly
+    those input columns.  Returns (weights, formats): `weights` are the dense equivalents
+    (pruned entries zero) the CPU oracle evaluates, `formats` the per-weight storage formats
+    for EncoderLayer (the row and column lists are one array object)."""
+    w = encoder_layer_weights(seed, layer, hidden, ff, **kw)
+    base = 1000 * (layer + 1)
+    w["wqkv"] = prune_1x16(w["wqkv"], seed, base + 60, vec_sparsity)
+    w["wo"] = prune_1x16(w["wo"], seed, base + 61, vec_sparsity)
+    ids = choose_ids(seed, base + 62, ff, ffn_sparsity)
+    keep = np.zeros(ff, dtype=bool)
+    keep[ids] = True
+    w["w1"] = np.where(keep[:, None], w["w1"], np.float16(0)).astype(np.float16)
+    w["w2"] = np.where(keep[None, :], w["w2"], np.float16(0)).astype(np.float16)
+    formats = {"wqkv": "1x16_auto", "wo": "1x16_auto", "w1": ("row", ids), "w2": ("col", ids)}
+    return w, formats

@@ -5,6 +5,9 @@ import numpy as np
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the tests force kernel plans and run instruction-rate probes: load the library build that
+# exports the et_debug_* hooks (the product library does not)
+os.environ["ET_B200_TEST_HOOKS"] = "1"
 sys.path.insert(0, ROOT)
 
 import __graft_entry__ as entry  # noqa: E402
