@@ -386,6 +386,45 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                          const int32_t* valid_len, void* workspace, size_t workspace_bytes,
                          et_stream stream);
 
+/* =================================================================================
+ * Head-parallel form of the layer, for ONE long sequence spread over several GPUs (the
+ * reference is single-GPU; this is the tensor-parallel reading of Attention/Attention.h:
+ * 58-142 where each GPU owns some heads' rows of W_Q, W_K, W_V and columns of W_O).  The
+ * attention block is cut into work units (head, range of 128-query blocks); a rank runs its
+ * units and multiplies by its heads' columns of W_O, which gives a partial [T, hidden] sum;
+ * the caller adds the ranks' partial sums with ONE all-reduce and hands the total to the
+ * second call, which every rank runs in full (LayerNorm and the feed-forward block are
+ * replicated).
+ *
+ * et_attention_units_fwd: et_attention_fwd over n_units <= 16 work units given as HOST arrays
+ *   unit_head[u], unit_first_block[u]; each unit covers blocks_per_unit blocks of 128 queries
+ *   against all keys of its head.  Rows of Z outside the units are left untouched.
+ * et_encoder_attention_units_fwd: `layer` describes THIS RANK'S slice: qkv = the rows of the
+ *   fused projection of its heads ([Q | K | V] order, dense), o = the matching columns of W_O
+ *   (in = vdim = local heads * head width), nhead / kdim / vdim local, hidden the model width.
+ *   Writes partial[T, hidden] = attention(units) . o^T as fp16 (+ o.bias if given: pass it on
+ *   one rank only) or, with partial_is_f32, as fp32 without bias.
+ * et_encoder_after_attention_fwd: out = LN2(FFN(y) + y), y = LN1(attn_sum + x) with attn_sum
+ *   the all-reduced total: fp16 (bias already inside), or fp32 (layer->o.bias is added here).
+ *   `layer` is the full layer; only its o.bias, LayerNorm and ffn fields are read.
+ * Both take the workspace of et_encoder_layer_workspace_bytes(layer, batch, seq).
+ * ================================================================================= */
+int et_attention_units_fwd(const et_half* Q, const et_half* K, const et_half* V, et_half* Z, int batch,
+                           int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
+                           int ldz, int mask_kind, const et_half* mask, const int32_t* valid_len,
+                           float scale, const int32_t* unit_head, const int32_t* unit_first_block,
+                           int n_units, int blocks_per_unit, et_stream stream);
+int et_encoder_attention_units_fwd(const et_encoder_layer_t* layer, const et_half* x, void* partial,
+                                   int partial_is_f32, int batch, int seq, int mask_kind,
+                                   const et_half* mask, const int32_t* valid_len,
+                                   const int32_t* unit_head, const int32_t* unit_first_block,
+                                   int n_units, int blocks_per_unit, void* workspace,
+                                   size_t workspace_bytes, et_stream stream);
+int et_encoder_after_attention_fwd(const et_encoder_layer_t* layer, const void* attn_sum,
+                                   int sum_is_f32, const et_half* x, et_half* out, int batch,
+                                   int seq, void* workspace, size_t workspace_bytes,
+                                   et_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

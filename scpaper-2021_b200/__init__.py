@@ -36,6 +36,7 @@ ABI_SYMBOLS = [
     "et_linear_vo_pruned_fwd", "et_fused_vo_attention_pruned_fwd",
     "et_attention_fuse_o_fwd", "et_fused_vo_attention_fwd", "et_linear_vo_fwd",
     "et_encoder_layer_workspace_bytes", "et_encoder_layer_fwd",
+    "et_attention_units_fwd", "et_encoder_attention_units_fwd", "et_encoder_after_attention_fwd",
 ]
 
 
@@ -566,41 +567,104 @@ class EncoderLayer:
 
 class HeadParallelLayer:
     """One encoder layer over `job.world` GPUs for a batch that cannot be sharded (one long
-    sequence): every rank projects and attends over its own heads and multiplies by its heads'
-    columns of the output projection; one all-reduce adds the partial [T, hidden] sums; the
-    LayerNorms and the FFN run replicated.  `weights` is the full layer (numpy fp16)."""
+    sequence).  The attention block is cut into (head, query range) work units dealt out evenly
+    (sharding.head_parallel_plan); every rank projects Q, K, V for the heads its units touch,
+    attends over its units and multiplies by those heads' columns of the output projection
+    (et_encoder_attention_units_fwd); ONE all-reduce adds the partial [T, hidden] sums; the
+    LayerNorms and the FFN run replicated on the full layer (et_encoder_after_attention_fwd,
+    the same fused kernels as et_encoder_layer_fwd).  `weights` is the full layer (numpy fp16).
+    reduce_dtype "fp16" sums fp16 partials (6 MB per 4096 x 768 layer), "fp32" fp32 partials."""
 
-    def __init__(self, weights: dict, nhead: int, job, act_kind: int = ACT_GELU, device="cuda"):
+    def __init__(self, weights: dict, nhead: int, job, act_kind: int = ACT_GELU, device="cuda",
+                 reduce_dtype: str = "fp16"):
         import numpy as np
         import torch
-        self.job, self.act = job, act_kind
-        sl = sharding.head_shard_weights(weights, nhead, job.world, job.rank)
-        self.nh, self.dqk, self.dv = sl["nhead_local"], sl["dh_qk"], sl["dh_v"]
-        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
-        self.wqkv, self.bqkv = dev(sl["wqkv"]), dev(sl["bqkv"])
-        self.wo, self.bo = dev(sl["wo"]), dev(sl["bo"])
-        self.w1, self.b1, self.w2, self.b2 = (dev(weights[k]) for k in ("w1", "b1", "w2", "b2"))
-        self.ln = [dev(weights[k]) for k in ("ln1_g", "ln1_b", "ln2_g", "ln2_b")]
+        if reduce_dtype not in ("fp16", "fp32"):
+            raise EtError("reduce_dtype must be 'fp16' or 'fp32'")
+        self.job, self.nhead, self.f32 = job, nhead, reduce_dtype == "fp32"
+        self.device = device
+        self.full = EncoderLayer(weights, nhead, act_kind, device=device)
+        self.weights = weights
+        self._plans = {}  # seq -> (local layer description, unit arrays, ...)
+        self._keep = []
+        self.hidden = self.full.hidden
+        self.units_per_rank = None
 
-    def forward(self, x, batch: int, seq: int, mask_kind=MASK_NONE, mask=None, valid_len=None):
-        kq, kv = self.nh * self.dqk, self.nh * self.dv
-        a = None
-        if self.nh > 0:
-            qkv = linear_dense(x, self.wqkv, self.bqkv)
-            z = attention(qkv[:, :kq], qkv[:, kq:2 * kq], qkv[:, 2 * kq:], batch, seq, self.nh,
-                          self.dqk, self.dv, mask_kind, mask, valid_len)
-            a = linear_dense(z, self.wo, self.bo)
-        else:  # more ranks than heads: this rank only contributes the bias (rank 0) or zeros
-            import torch
-            a = self.bo.expand(x.shape[0], -1).contiguous() if self.job.rank == 0 else \
-                torch.zeros((x.shape[0], self.wo.shape[0]), dtype=x.dtype, device=x.device)
-        if self.job.world > 1:
+    @staticmethod
+    def units_of(nhead: int, world: int, rank: int, seq: int):
+        return sharding.units_of_rank(nhead, world, rank, seq)
+
+    def _plan(self, seq: int):
+        import numpy as np
+        import torch
+        if seq in self._plans:
+            return self._plans[seq]
+        world, rank = self.job.world, self.job.rank
+        _, per_rank, bpu = sharding.head_parallel_plan(self.nhead, world, seq)
+        units = sharding.units_of_rank(self.nhead, world, rank, seq)
+        heads = sorted({h for h, _ in units})
+        sl = sharding.head_rows(self.weights, self.nhead, heads)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+        wqkv, bqkv, wo = dev(sl["wqkv"]), dev(sl["bqkv"]), dev(sl["wo"])
+        bo = dev(self.weights["bo"]) if (rank == 0 and not self.f32) else None
+        self._keep += [wqkv, bqkv, wo, bo]
+        d = EncoderLayerDesc()
+        ctypes.memmove(ctypes.byref(d), ctypes.byref(self.full.desc), ctypes.sizeof(d))
+        nh = len(heads)
+        d.nhead, d.kdim, d.vdim = nh, nh * sl["dh_qk"], nh * sl["dh_v"]
+        d.qkv.format, d.qkv.in_, d.qkv.out = FMT_DENSE, self.hidden, int(wqkv.shape[0])
+        d.qkv.weight, d.qkv.bias = wqkv.data_ptr(), bqkv.data_ptr()
+        d.o.format, d.o.in_, d.o.out = FMT_DENSE, int(wo.shape[1]), self.hidden
+        d.o.weight, d.o.bias = wo.data_ptr(), (bo.data_ptr() if bo is not None else None)
+        uh = (ctypes.c_int32 * len(units))(*[heads.index(h) for h, _ in units])
+        uf = (ctypes.c_int32 * len(units))(*[f for _, f in units])
+        self.units_per_rank = per_rank
+        plan = (d, uh, uf, len(units), bpu)
+        self._plans[seq] = plan
+        return plan
+
+    def _workspace(self, d, batch, seq, like):
+        import torch
+        ws_bytes = max(int(lib().et_encoder_layer_workspace_bytes(ctypes.byref(d), c_int(batch),
+                                                                  c_int(seq))),
+                       self.full.workspace_bytes(batch, seq))
+        if getattr(self, "_ws", None) is None or self._ws.numel() < ws_bytes:
+            self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=like.device)
+        return self._ws
+
+    def partial_sum(self, x, batch: int, seq: int, mask_kind=MASK_NONE, mask=None, valid_len=None):
+        """This rank's share of the attention block: [T, hidden] (fp16 or fp32)."""
+        import torch
+        d, uh, uf, n_units, bpu = self._plan(seq)
+        ws = self._workspace(d, batch, seq, x)
+        partial = torch.empty((batch * seq, self.hidden),
+                              dtype=torch.float32 if self.f32 else torch.float16, device=x.device)
+        check(lib().et_encoder_attention_units_fwd(
+            ctypes.byref(d), _p(x), _p(partial), c_int(1 if self.f32 else 0), c_int(batch), c_int(seq),
+            c_int(mask_kind), _p(mask), _p(valid_len), uh, uf, c_int(n_units), c_int(bpu),
+            _p(ws), c_size_t(ws.numel()), _stream()), "et_encoder_attention_units_fwd")
+        return partial
+
+    def finish(self, attn_sum, x, batch: int, seq: int):
+        """The replicated rest of the layer on the summed attention block."""
+        d = self._plan(seq)[0]
+        ws = self._workspace(d, batch, seq, x)
+        out = _empty((batch * seq, self.hidden), x)
+        check(lib().et_encoder_after_attention_fwd(
+            ctypes.byref(self.full.desc), _p(attn_sum), c_int(1 if self.f32 else 0), _p(x), _p(out),
+            c_int(batch), c_int(seq), _p(ws), c_size_t(ws.numel()), _stream()),
+            "et_encoder_after_attention_fwd")
+        return out
+
+    def forward(self, x, batch: int, seq: int, mask_kind=MASK_NONE, mask=None, valid_len=None,
+                skip_allreduce: bool = False):
+        """skip_allreduce=True leaves out the exchange step (timing aid: the result is then the
+        layer applied to this rank's partial sum only)."""
+        partial = self.partial_sum(x, batch, seq, mask_kind, mask, valid_len)
+        if self.job.world > 1 and not skip_allreduce:
             import torch.distributed as dist
-            dist.all_reduce(a)  # the layer's one exchange step
-        y = skip_layernorm(a, x, self.ln[0], self.ln[1])
-        f = linear_dense(y, self.w1, self.b1, self.act)
-        a2 = linear_dense(f, self.w2, self.b2)
-        return skip_layernorm(a2, y, self.ln[2], self.ln[3])
+            dist.all_reduce(partial)  # the layer's one exchange step
+        return self.finish(partial, x, batch, seq)
 
 
 class EncoderStack:

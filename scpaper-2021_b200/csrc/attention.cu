@@ -77,6 +77,8 @@ __device__ __forceinline__ float store_probabilities(const uint32_t (&v0)[32],
     return rowsum;
 }
 
+constexpr int ATT_MAX_UNITS = 16;
+
 struct AttnArgs {
     __half* Z;
     const __half* mask;
@@ -92,6 +94,12 @@ struct AttnArgs {
     int nva_max;    // 64-feature atoms reserved for a V block in shared memory
     int tmem_cols;  // tensor-memory columns to allocate (256 or 512)
     int tma_out;    // 1: the output tile is written with TMA stores (dense V, dh_v % 64 == 0)
+    // Work-unit form (n_units > 0): blockIdx.y selects a unit = (head, first 128-query block);
+    // the grid's x extent is the number of query blocks per unit.  Otherwise blockIdx.y is the
+    // head and the grid covers every query block.
+    int n_units;
+    unsigned char unit_head[ATT_MAX_UNITS];
+    unsigned short unit_first[ATT_MAX_UNITS];
 };
 
 // MASK: the mask kind, compiled in (keeps the mask bookkeeping out of the registers of the
@@ -128,8 +136,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int lane = threadIdx.x & 31;
     // causal: the last query blocks have the most key blocks; they are launched first so that
     // the short ones fill the tail of the grid
-    const int q0 = (MASK == ET_MASK_CAUSAL ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * BQ;
-    const int h = blockIdx.y;
+    const int qb_first = a.n_units > 0 ? a.unit_first[blockIdx.y] : 0;
+    const int q0 =
+        (qb_first + (MASK == ET_MASK_CAUSAL ? gridDim.x - 1 - blockIdx.x : blockIdx.x)) * BQ;
+    const int h = a.n_units > 0 ? a.unit_head[blockIdx.y] : blockIdx.y;
     const int b = blockIdx.z;
 
     // V window of this head: feature offset v_x0 (a multiple of 8 so the TMA start is 16-byte
@@ -513,7 +523,16 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
                           int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
                           int ldz, int mask_kind, const __half* mask, const int* valid_len,
                           float scale, const int* col_id, const int* head_ptr, int nnz_col,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const int* unit_head = nullptr,
+                          const int* unit_first = nullptr, int n_units = 0, int blocks_per_unit = 0) {
+    if (n_units < 0 || n_units > ATT_MAX_UNITS) return ET_ERR_SHAPE;
+    if (n_units > 0) {
+        if (!unit_head || !unit_first || blocks_per_unit <= 0) return ET_ERR_INVALID_ARG;
+        for (int u = 0; u < n_units; ++u)
+            if (unit_head[u] < 0 || unit_head[u] >= nhead || unit_head[u] > 255 || unit_first[u] < 0 ||
+                (unit_first[u] + blocks_per_unit - 1) * BQ >= seq || unit_first[u] > 65535)
+                return ET_ERR_INDEX;
+    }
     if (!Q || !K || !V || !Z || batch <= 0 || seq <= 0 || nhead <= 0 || dh_qk <= 0 || dh_v <= 0)
         return ET_ERR_INVALID_ARG;
     if (mask_kind < ET_MASK_NONE || mask_kind > ET_MASK_ADDITIVE) return ET_ERR_INVALID_ARG;
@@ -573,7 +592,13 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     a.nva_max = nva;
     a.tmem_cols = (128 + v_n_max > 256) ? 512 : TMEM_COLS_ATT;
     a.tma_out = tma_out ? 1 : 0;
-    const dim3 grid((seq + BQ - 1) / BQ, nhead, batch);
+    a.n_units = n_units;
+    for (int u = 0; u < ATT_MAX_UNITS; ++u) {
+        a.unit_head[u] = static_cast<unsigned char>(u < n_units ? unit_head[u] : 0);
+        a.unit_first[u] = static_cast<unsigned short>(u < n_units ? unit_first[u] : 0);
+    }
+    const dim3 grid = n_units > 0 ? dim3(blocks_per_unit, n_units, batch)
+                                  : dim3((seq + BQ - 1) / BQ, nhead, batch);
     auto go = [&](auto kern, int slot) -> int {
         static bool attr_set[4][64] = {};
         if (dev >= 0 && dev < 64 && !attr_set[slot][dev]) {
@@ -605,9 +630,33 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
                                  mask_kind, mask, valid_len, scale, nullptr, nullptr, 0, stream);
 }
 
+int launch_attention_units(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
+                           int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
+                           int ldz, int mask_kind, const __half* mask, const int* valid_len,
+                           float scale, const int* unit_head, const int* unit_first, int n_units,
+                           int blocks_per_unit, cudaStream_t stream) {
+    if (n_units <= 0) return ET_ERR_INVALID_ARG;
+    return launch_attention_impl(Q, K, V, Z, batch, seq, nhead, dh_qk, dh_v, ldq, ldk, ldv, ldz,
+                                 mask_kind, mask, valid_len, scale, nullptr, nullptr, 0, stream,
+                                 unit_head, unit_first, n_units, blocks_per_unit);
+}
+
 }  // namespace et
 
 extern "C" {
+
+int et_attention_units_fwd(const et_half* Q, const et_half* K, const et_half* V, et_half* Z, int batch,
+                           int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
+                           int ldz, int mask_kind, const et_half* mask, const int32_t* valid_len,
+                           float scale, const int32_t* unit_head, const int32_t* unit_first_block,
+                           int n_units, int blocks_per_unit, et_stream stream) {
+    return et::launch_attention_units(
+        reinterpret_cast<const __half*>(Q), reinterpret_cast<const __half*>(K),
+        reinterpret_cast<const __half*>(V), reinterpret_cast<__half*>(Z), batch, seq, nhead, dh_qk,
+        dh_v, ldq, ldk, ldv, ldz, mask_kind, reinterpret_cast<const __half*>(mask), valid_len,
+        scale, unit_head, unit_first_block, n_units, blocks_per_unit,
+        static_cast<cudaStream_t>(stream));
+}
 
 int et_attention_fwd(const et_half* Q, const et_half* K, const et_half* V, et_half* Z, int batch,
                      int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,

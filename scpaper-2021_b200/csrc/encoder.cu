@@ -164,6 +164,86 @@ int check_layer(const et_encoder_layer_t* L) {
     return ET_OK;
 }
 
+
+// y = b.y (the first LayerNorm's output) -> out = LN2(W2 act(W1 y + b1) + b2 + y)
+int ffn_block(const et_encoder_layer_t* layer, const LayerBuffers& b, int T, __half* out_h,
+              cudaStream_t s) {
+    int st;
+    et_half* out = reinterpret_cast<et_half*>(out_h);
+    const int ln_fused = ln_fusion_mask(T, layer->hidden);
+    // ffn2 as the dense product it amounts to: W2 itself, or - for the compressed pair - the
+    // kept columns of W2 on the kept hidden units
+    const __half* w2 = reinterpret_cast<const __half*>(layer->ffn2.weight);
+    int k2 = layer->ff;
+    bool ffn2_dense = layer->ffn2.format == ET_FMT_DENSE;
+    if (ffn_is_compressed_pair(layer)) {
+        k2 = layer->ffn1.nnz_tiles;
+        ffn2_dense = true;
+        // f[T, kept] = act(y . rows^T + b1[kept ids]): GEMM with an index-list epilogue
+        if ((st = launch_gemm_f16(b.y, layer->hidden,
+                                      reinterpret_cast<const __half*>(layer->ffn1.weight),
+                                      layer->hidden,
+                                      reinterpret_cast<const __half*>(layer->ffn1.bias), b.f, k2,
+                                      layer->ffn1.row_ptr, 0, T, k2, layer->hidden, layer->act,
+                                      s)) != ET_OK)
+            return st;
+    } else if ((st = run_linear(layer->ffn1, b.y, b.f, T, layer->act, b, s)) != ET_OK) {
+        return st;
+    }
+    if ((ln_fused & 2) && ffn2_dense && gemm_ln_applies(T, layer->hidden, k2) &&
+        reinterpret_cast<const __half*>(out) != b.y) {
+        // FFN2, residual and LayerNorm in one kernel
+        return launch_gemm_ln(b.f, k2, w2, k2,
+                                  reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
+                                  layer->hidden,
+                                  reinterpret_cast<const __half*>(layer->ln2_gamma),
+                                  reinterpret_cast<const __half*>(layer->ln2_beta),
+                                  reinterpret_cast<__half*>(out), layer->hidden, T, layer->hidden,
+                                  k2, s);
+    }
+    const bool ffn2_splittable = ffn2_dense && layer->hidden <= 2048;
+    const int pair_splits =
+        ffn2_splittable ? pick_pair_splits(T, layer->hidden, k2) : 0;
+    if (pair_splits > 1) {
+        // FFN2 as split-K partial sums on CTA pairs, reduced (with bias and residual) inside
+        // the LayerNorm
+        if ((st = launch_gemm_pair_splitk(b.f, k2, w2, k2, b.part, T, layer->hidden, k2,
+                                              pair_splits, s)) != ET_OK)
+            return st;
+        return launch_skip_layernorm_partials(
+            b.part, pair_splits, static_cast<size_t>(T) * layer->hidden,
+            reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
+            reinterpret_cast<const __half*>(layer->ln2_gamma),
+            reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
+            layer->hidden, s);
+    }
+    const int splits = ffn2_splittable ? pick_splits(T, layer->hidden, k2) : 1;
+    if (splits > 1) {
+        // FFN2 as split-K partial sums, reduced (with bias and residual) inside the LayerNorm
+        if ((st = launch_gemm_f16_splitk(b.f, k2, w2, k2, b.part, T, layer->hidden, k2, splits,
+                                             s)) != ET_OK)
+            return st;
+        return launch_skip_layernorm_partials(
+            b.part, splits, static_cast<size_t>(T) * layer->hidden,
+            reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
+            reinterpret_cast<const __half*>(layer->ln2_gamma),
+            reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
+            layer->hidden, s);
+    }
+    if (ffn2_dense && layer->ffn2.format != ET_FMT_DENSE) {
+        if ((st = launch_gemm_f16(b.f, k2, w2, k2,
+                                      reinterpret_cast<const __half*>(layer->ffn2.bias), b.a,
+                                      layer->hidden, nullptr, 0, T, layer->hidden, k2, ET_ACT_NONE,
+                                      s)) != ET_OK)
+            return st;
+    } else if ((st = run_linear(layer->ffn2, b.f, b.a, T, ET_ACT_NONE, b, s)) != ET_OK) {
+        return st;
+    }
+    return launch_skip_layernorm(b.a, b.y, reinterpret_cast<const __half*>(layer->ln2_gamma),
+                                     reinterpret_cast<const __half*>(layer->ln2_beta),
+                                     reinterpret_cast<__half*>(out), T, layer->hidden, s);
+}
+
 }  // namespace
 }  // namespace et
 
@@ -244,77 +324,76 @@ int et_encoder_layer_fwd(const et_encoder_layer_t* layer, const et_half* x, et_h
                                             T, layer->hidden, s)) != ET_OK)
             return st;
     }
-    // ffn2 as the dense product it amounts to: W2 itself, or - for the compressed pair - the
-    // kept columns of W2 on the kept hidden units
-    const __half* w2 = reinterpret_cast<const __half*>(layer->ffn2.weight);
-    int k2 = layer->ff;
-    bool ffn2_dense = layer->ffn2.format == ET_FMT_DENSE;
-    if (et::ffn_is_compressed_pair(layer)) {
-        k2 = layer->ffn1.nnz_tiles;
-        ffn2_dense = true;
-        // f[T, kept] = act(y . rows^T + b1[kept ids]): GEMM with an index-list epilogue
-        if ((st = et::launch_gemm_f16(b.y, layer->hidden,
-                                      reinterpret_cast<const __half*>(layer->ffn1.weight),
-                                      layer->hidden,
-                                      reinterpret_cast<const __half*>(layer->ffn1.bias), b.f, k2,
-                                      layer->ffn1.row_ptr, 0, T, k2, layer->hidden, layer->act,
-                                      s)) != ET_OK)
-            return st;
-    } else if ((st = et::run_linear(layer->ffn1, b.y, b.f, T, layer->act, b, s)) != ET_OK) {
+    return et::ffn_block(layer, b, T, reinterpret_cast<__half*>(out), s);
+}
+
+// ---- head-parallel form: the layer in two halves around the ranks' one exchange step --------
+int et_encoder_attention_units_fwd(const et_encoder_layer_t* layer, const et_half* x, void* partial,
+                                   int partial_is_f32, int batch, int seq, int mask_kind,
+                                   const et_half* mask, const int32_t* valid_len,
+                                   const int32_t* unit_head, const int32_t* unit_first_block,
+                                   int n_units, int blocks_per_unit, void* workspace,
+                                   size_t workspace_bytes, et_stream stream) {
+    int st = et::check_layer(layer);
+    if (st != ET_OK) return st;
+    if (!x || !partial || batch <= 0 || seq <= 0 || n_units <= 0) return ET_ERR_INVALID_ARG;
+    if (layer->qkv.format != ET_FMT_DENSE || layer->o.format != ET_FMT_DENSE) return ET_ERR_SHAPE;
+    if (!workspace) return ET_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return ET_ERR_ALIGNMENT;
+    const et::LayerBuffers b = et::carve(layer, batch, seq, workspace);
+    if (workspace_bytes < b.total) return ET_ERR_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int T = batch * seq;
+    const int ldqkv = 2 * layer->kdim + layer->vdim;
+    const int dh_qk = layer->kdim / layer->nhead, dh_v = layer->vdim / layer->nhead;
+    // rows of z outside this rank's units must contribute nothing to the partial product
+    if (cudaMemsetAsync(b.z, 0, static_cast<size_t>(T) * layer->vdim * sizeof(__half), s) != cudaSuccess)
+        return ET_ERR_CUDA;
+    if ((st = et::run_linear(layer->qkv, reinterpret_cast<const __half*>(x), b.qkv, T, ET_ACT_NONE, b,
+                             s)) != ET_OK)
         return st;
-    }
-    if ((ln_fused & 2) && ffn2_dense && et::gemm_ln_applies(T, layer->hidden, k2) &&
-        reinterpret_cast<const __half*>(out) != b.y) {
-        // FFN2, residual and LayerNorm in one kernel
-        return et::launch_gemm_ln(b.f, k2, w2, k2,
-                                  reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
-                                  layer->hidden,
-                                  reinterpret_cast<const __half*>(layer->ln2_gamma),
-                                  reinterpret_cast<const __half*>(layer->ln2_beta),
-                                  reinterpret_cast<__half*>(out), layer->hidden, T, layer->hidden,
-                                  layer->ff, s);
-    }
-    const bool ffn2_splittable = ffn2_dense && layer->hidden <= 2048;
-    const int pair_splits =
-        ffn2_splittable ? et::pick_pair_splits(T, layer->hidden, k2) : 0;
-    if (pair_splits > 1) {
-        // FFN2 as split-K partial sums on CTA pairs, reduced (with bias and residual) inside
-        // the LayerNorm
-        if ((st = et::launch_gemm_pair_splitk(b.f, k2, w2, k2, b.part, T, layer->hidden, k2,
-                                              pair_splits, s)) != ET_OK)
-            return st;
-        return et::launch_skip_layernorm_partials(
-            b.part, pair_splits, static_cast<size_t>(T) * layer->hidden,
-            reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
-            reinterpret_cast<const __half*>(layer->ln2_gamma),
-            reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
-            layer->hidden, s);
-    }
-    const int splits = ffn2_splittable ? et::pick_splits(T, layer->hidden, k2) : 1;
-    if (splits > 1) {
-        // FFN2 as split-K partial sums, reduced (with bias and residual) inside the LayerNorm
-        if ((st = et::launch_gemm_f16_splitk(b.f, k2, w2, k2, b.part, T, layer->hidden, k2, splits,
-                                             s)) != ET_OK)
-            return st;
-        return et::launch_skip_layernorm_partials(
-            b.part, splits, static_cast<size_t>(T) * layer->hidden,
-            reinterpret_cast<const __half*>(layer->ffn2.bias), b.y,
-            reinterpret_cast<const __half*>(layer->ln2_gamma),
-            reinterpret_cast<const __half*>(layer->ln2_beta), reinterpret_cast<__half*>(out), T,
-            layer->hidden, s);
-    }
-    if (ffn2_dense && layer->ffn2.format != ET_FMT_DENSE) {
-        if ((st = et::launch_gemm_f16(b.f, k2, w2, k2,
-                                      reinterpret_cast<const __half*>(layer->ffn2.bias), b.a,
-                                      layer->hidden, nullptr, 0, T, layer->hidden, k2, ET_ACT_NONE,
-                                      s)) != ET_OK)
-            return st;
-    } else if ((st = et::run_linear(layer->ffn2, b.f, b.a, T, ET_ACT_NONE, b, s)) != ET_OK) {
+    if ((st = et::launch_attention_units(b.qkv, b.qkv + layer->kdim, b.qkv + 2 * layer->kdim, b.z,
+                                         batch, seq, layer->nhead, dh_qk, dh_v, ldqkv, ldqkv, ldqkv,
+                                         layer->vdim, mask_kind, reinterpret_cast<const __half*>(mask),
+                                         valid_len, 1.0f / sqrtf(static_cast<float>(dh_qk)), unit_head,
+                                         unit_first_block, n_units, blocks_per_unit, s)) != ET_OK)
         return st;
+    if (partial_is_f32)
+        return et::launch_gemm_f16_splitk(b.z, layer->vdim,
+                                          reinterpret_cast<const __half*>(layer->o.weight),
+                                          layer->vdim, static_cast<float*>(partial), T,
+                                          layer->hidden, layer->vdim, 1, s);
+    return et::run_linear(layer->o, b.z, static_cast<__half*>(partial), T, ET_ACT_NONE, b, s);
+}
+
+int et_encoder_after_attention_fwd(const et_encoder_layer_t* layer, const void* attn_sum,
+                                   int sum_is_f32, const et_half* x, et_half* out, int batch,
+                                   int seq, void* workspace, size_t workspace_bytes,
+                                   et_stream stream) {
+    int st = et::check_layer(layer);
+    if (st != ET_OK) return st;
+    if (!x || !out || !attn_sum || batch <= 0 || seq <= 0) return ET_ERR_INVALID_ARG;
+    if (!workspace) return ET_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return ET_ERR_ALIGNMENT;
+    const et::LayerBuffers b = et::carve(layer, batch, seq, workspace);
+    if (workspace_bytes < b.total) return ET_ERR_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int T = batch * seq;
+    const __half* xin = reinterpret_cast<const __half*>(x);
+    const __half* g1 = reinterpret_cast<const __half*>(layer->ln1_gamma);
+    const __half* b1 = reinterpret_cast<const __half*>(layer->ln1_beta);
+    if (sum_is_f32) {
+        if (layer->hidden > 2048) return ET_ERR_SHAPE;
+        st = et::launch_skip_layernorm_partials(static_cast<const float*>(attn_sum), 1,
+                                                static_cast<size_t>(T) * layer->hidden,
+                                                reinterpret_cast<const __half*>(layer->o.bias), xin,
+                                                g1, b1, b.y, T, layer->hidden, s);
+    } else {
+        st = et::launch_skip_layernorm(static_cast<const __half*>(attn_sum), xin, g1, b1, b.y, T,
+                                       layer->hidden, s);
     }
-    return et::launch_skip_layernorm(b.a, b.y, reinterpret_cast<const __half*>(layer->ln2_gamma),
-                                     reinterpret_cast<const __half*>(layer->ln2_beta),
-                                     reinterpret_cast<__half*>(out), T, layer->hidden, s);
+    if (st != ET_OK) return st;
+    return et::ffn_block(layer, b, T, reinterpret_cast<__half*>(out), s);
 }
 
 int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,

@@ -65,6 +65,15 @@ int launch_attention(const __half* Q, const __half* K, const __half* V, __half* 
                      int mask_kind, const __half* mask, const int* valid_len, float scale,
                      cudaStream_t stream);
 
+// The same kernel over a list of work units (head, first 128-query block), each covering
+// blocks_per_unit query blocks; query rows outside the units are not written.  unit_head and
+// unit_first are HOST arrays of n_units <= 16 entries.
+int launch_attention_units(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
+                           int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
+                           int ldz, int mask_kind, const __half* mask, const int* valid_len,
+                           float scale, const int* unit_head, const int* unit_first, int n_units,
+                           int blocks_per_unit, cudaStream_t stream);
+
 // out = LN(X W^T + bias + resid) * gamma + beta in one kernel (gemm_ln.cu); N = 256 .. 1024 in
 // steps of 128.
 bool gemm_ln_applies(int M, int N, int K);

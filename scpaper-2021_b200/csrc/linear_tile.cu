@@ -62,7 +62,8 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                    const __grid_constant__ CUtensorMap tmY, const int* __restrict__ row_ptr,
                    const int* __restrict__ row_off, const uint32_t* __restrict__ pk_mask,
                    const int* __restrict__ pk_off, const __half* __restrict__ pk_tiles,
-                   const __half* __restrict__ bias, int T, int in, int out, int* err_word) {
+                   const __half* __restrict__ bias, int T, int in, int out, int n_issuers,
+                   int* err_word) {
     static_assert(NP == 1 || PACKED, "two panels per CTA exist for packed weights only");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
@@ -121,9 +122,9 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         tma_prefetch_desc(&tmW);
         for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], T_EPI_WARPS);
+            mbar_init(&empty_bar[s], n_issuers);
         }
-        mbar_init(acc_bar, T_EPI_WARPS);
+        mbar_init(acc_bar, n_issuers);
         *abort_flag = 0;
         *max_cnt = 0;
         fence_barrier_init();
@@ -274,14 +275,14 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const int half = (warp - 2) >> 2;  // which 64 output columns of a panel
         bool ok = true;
         if (panel_tiles > 0) {
-            if (lane == 0) {
+            // the first n_issuers of these warps issue; warp e takes block rows e, e + n_issuers, ...
+            if (lane == 0 && e < n_issuers) {
                 constexpr uint32_t idesc = make_idesc_f16(TBM, 16, 0, 0);
-                uint32_t started[NP];
+                uint32_t started[NP];  // bit r: block row r of the panel has received a product
 #pragma unroll
                 for (int k = 0; k < NP; ++k) started[k] = 0u;
                 int s = 0, stage_it = 0;
                 uint32_t ph = 0;
-                const uint32_t below_mask = (1u << (4 * e)) - 1u;
                 for (int kc = 0; kc < nchunk; ++kc) {
                     uint32_t m[NP];
                     if (masks_of(kc, m) == 0u) continue;
@@ -296,23 +297,27 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                     bool issued_any = false;
 #pragma unroll
                     for (int k = 0; k < NP; ++k) {
-                        uint32_t nib = (m[k] >> (4 * e)) & 0xFu;
-                        if (nib == 0u) continue;
-                        if (!issued_any) tc_fence_after_sync();
-                        issued_any = true;
-                        const uint32_t x_addr = smem_u32(ring + s * stage_bytes);
-                        // descriptors differ from tile to tile only in their start address
-                        const uint64_t a_base = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
-                        uint64_t bd = make_smem_desc(x_addr + X_STAGE_BYTES + k * nslot * 512 +
-                                                         512u * __popc(m[k] & below_mask),
-                                                     16, 256, SWZ_32B);
-                        while (nib) {
-                            const int kb = __ffs(nib) - 1;
-                            nib &= nib - 1;
-                            mma_f16_ss(tmem_base + k * TBN + e * 16,
-                                       a_base + static_cast<uint64_t>(kb * 2), bd, idesc, started[k]);
-                            started[k] = 1u;
-                            bd += 32;  // next 512-byte slot
+                        for (int r = e; r < PANEL_ROWS; r += n_issuers) {
+                            uint32_t nib = (m[k] >> (4 * r)) & 0xFu;
+                            if (nib == 0u) continue;
+                            if (!issued_any) tc_fence_after_sync();
+                            issued_any = true;
+                            const uint32_t x_addr = smem_u32(ring + s * stage_bytes);
+                            // descriptors differ from tile to tile only in their start address
+                            const uint64_t a_base = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
+                            uint64_t bd = make_smem_desc(
+                                x_addr + X_STAGE_BYTES + k * nslot * 512 +
+                                    512u * __popc(m[k] & ((1u << (4 * r)) - 1u)),
+                                16, 256, SWZ_32B);
+                            while (nib) {
+                                const int kb = __ffs(nib) - 1;
+                                nib &= nib - 1;
+                                mma_f16_ss(tmem_base + k * TBN + r * 16,
+                                           a_base + static_cast<uint64_t>(kb * 2), bd, idesc,
+                                           (started[k] >> r) & 1u);
+                                started[k] |= 1u << r;
+                                bd += 32;  // next 512-byte slot
+                            }
                         }
                     }
                     if (issued_any)
@@ -330,7 +335,9 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 if (e == 0) ET_TL(2);
             }
             __syncwarp();
-            ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
+            // warps that do not issue sleep between polls: they share schedulers with the issuers
+            ok = e < n_issuers ? mbar_wait_bounded(acc_bar, 0, abort_flag)
+                               : mbar_wait_bounded_relaxed(acc_bar, 0, abort_flag);
             if (!ok && lane == 0) report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_EPILOGUE);
         }
         ok = __all_sync(0xffffffffu, ok);
@@ -442,6 +449,7 @@ __global__ void pack_tiles_kernel(const uint4* __restrict__ src, const int* __re
 }
 
 int g_tile_wide = -1;  // test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA
+int g_tile_issuers = 8;  // test hook: threads of a CTA that issue tensor-core products (1..8)
 
 namespace {
 int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, const uint32_t* pk_mask,
@@ -515,7 +523,8 @@ int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, cons
             attr_bytes[slot][dev] = smem_bytes;
         }
         return launch_kernel(kern, grid, dim3(TILE_THREADS), smem_bytes, stream, tmX, tmW, tmY,
-                             row_ptr, row_off, pk_mask, pk_off, tiles, bias, T, in, out, err);
+                             row_ptr, row_off, pk_mask, pk_off, tiles, bias, T, in, out,
+                             g_tile_issuers, err);
     };
     cudaError_t e;
     if (wide) {
@@ -557,6 +566,8 @@ extern "C" {
 #ifdef ET_TEST_HOOKS
 // Test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA (packed weights).
 void et_debug_set_tile_wide(int mode) { et::g_tile_wide = mode; }
+// Test hook: how many threads of a CTA issue the tensor-core products (1, 2, 4 or 8).
+void et_debug_set_tile_issuers(int n) { et::g_tile_issuers = n < 1 ? 1 : (n > 8 ? 8 : n); }
 #endif  // ET_TEST_HOOKS
 
 int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,

@@ -149,14 +149,15 @@ mma_sync_probe_kernel(int iters, const uint32_t* __restrict__ wtiles, long long*
 // issuer and the slowest mma.sync warp took, so that the rates with and without the other
 // path can be compared.
 __global__ void __launch_bounds__(512, 1)
-mixed_probe_kernel(int issuers, int count, int sync_warps, int iters, long long* cycles, int* status,
-                   float* sink) {
+mixed_probe_kernel(int issuers, int count, int sync_warps, int iters, int commit_every,
+                   long long* cycles, int* status, float* sink) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sA = smem;
     uint8_t* sB = smem + 16384;
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + 16384 + 8192);  // one per issuer (<= 8)
-    uint32_t* slot = reinterpret_cast<uint32_t*>(bar + 8);
+    uint64_t* side_bar = bar + 8;  // receives the periodic commits; nobody waits on it
+    uint32_t* slot = reinterpret_cast<uint32_t*>(bar + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(slot + 1);
     long long* s_cycles = reinterpret_cast<long long*>(smem + 16384 + 8192 + 128);  // [16]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -165,6 +166,7 @@ mixed_probe_kernel(int issuers, int count, int sync_warps, int iters, long long*
     if (threadIdx.x < 16) s_cycles[threadIdx.x] = 0;
     if (threadIdx.x == 0) {
         for (int i = 0; i < 8; ++i) mbar_init(&bar[i], 1);
+        mbar_init(side_bar, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -184,9 +186,11 @@ mixed_probe_kernel(int issuers, int count, int sync_warps, int iters, long long*
             const uint64_t a_desc = make_smem_desc(smem_u32(sA), 16, 1024, SWZ_128B);
             const uint64_t b_desc = make_smem_desc(smem_u32(sB), 16, 256, SWZ_32B);
             const long long t0 = clock64();
-            for (int i = 0; i < count; ++i)
+            for (int i = 0; i < count; ++i) {
                 mma_f16_ss(tmem_base + warp * 64 + (i & 3) * 16, a_desc + static_cast<uint64_t>((i & 3) * 2),
                            b_desc, idesc, i >= 4 ? 1u : 0u);
+                if (commit_every > 0 && (i % commit_every) == commit_every - 1) mma_commit(side_bar);
+            }
             mma_commit(&bar[warp]);
             ok = mbar_wait_bounded(&bar[warp], 0, abort_flag);
             s_cycles[warp] = clock64() - t0;
@@ -319,7 +323,9 @@ int et_debug_probe_mma_sync(int warps, int ctas_per_sm, int iters, int mode,
 // in the same CTAs at the same time, one CTA per SM.  Outputs: cycles per tcgen05 product
 // (all issuers together) and multiply-accumulates per clock per SM of the mma.sync warps;
 // either side may be switched off with count = 0 / iters = 0 for the solo figures.
-int et_debug_probe_mixed(int issuers, int count, int sync_warps, int iters,
+// commit_every > 0: every issuer also issues a tcgen05.commit after that many products (what a
+// pipelined kernel does to release an operand stage).
+int et_debug_probe_mixed(int issuers, int count, int sync_warps, int iters, int commit_every,
                          double* cycles_per_product, double* mac_per_clk_per_sm) {
     if (!cycles_per_product || !mac_per_clk_per_sm || issuers < 1 || issuers > 8 || sync_warps < 0 ||
         sync_warps > 8 || count < 0 || count > (1 << 20) || iters < 0 || iters > (1 << 20))
@@ -338,7 +344,8 @@ int et_debug_probe_mixed(int issuers, int count, int sync_warps, int iters,
     cudaMemset(d_status, 0, sizeof(int));
     const int smem = 16384 + 8192 + 128 + 128 + 1024;
     et::mixed_probe_kernel<<<sms, (issuers + sync_warps) * 32, smem>>>(issuers, count, sync_warps, iters,
-                                                                      d_cycles, d_status, d_sink);
+                                                                      commit_every, d_cycles, d_status,
+                                                                      d_sink);
     long long cyc[2] = {0, 0};
     int st = 0, rc = ET_OK;
     if (cudaDeviceSynchronize() != cudaSuccess ||

@@ -85,36 +85,72 @@ class Job:
 
 
 # ---- head-parallel mode: one long sequence over several GPUs --------------------------------
-# The attention block is split by head: rank r projects only its heads' Q, K, V (rows of the
-# fused weight), attends over them and multiplies by its heads' columns of the output projection,
-# which yields a partial [seq, hidden] sum; ONE all-reduce per layer adds the partial sums (the
-# reference has no multi-GPU code; this is the tensor-parallel form of Attention/Attention.h:58-142
-# for a batch that cannot be sharded).  LayerNorm and the FFN run replicated.
+# The attention block is cut into work units (head, range of 128-query blocks).  With `world`
+# ranks and `nhead` heads every head is cut into world / gcd(nhead, world) query ranges, so
+# that the nhead * qsplit units divide evenly over the ranks (12 heads on 8 GPUs: 24 units of
+# half a head each, 3 per rank) and every rank does the same amount of attention work.  A rank
+# projects Q, K, V only for the heads its units touch (rows of the fused weight), attends over
+# its units and multiplies by those heads' columns of the output projection, which yields a
+# partial [seq, hidden] sum; ONE all-reduce per layer adds the partial sums (the reference has no
+# multi-GPU code; this is the tensor-parallel form of Attention/Attention.h:58-142 for a batch
+# that cannot be sharded).  LayerNorm and the FFN run replicated.
+
+QUERY_BLOCK = 128  # rows of one attention work item on the GPU
+
+
+def head_parallel_plan(nhead: int, world: int, seq: int) -> tuple[int, int, int]:
+    """(qsplit, units_per_rank, blocks_per_unit): every head is cut into `qsplit` ranges of
+    `blocks_per_unit` query blocks; rank r owns units [r * units_per_rank, (r + 1) * ...)."""
+    import math
+    if nhead <= 0 or world <= 0 or seq <= 0:
+        raise ValueError("bad head-parallel request")
+    qsplit = world // math.gcd(nhead, world)
+    nblocks = -(-seq // QUERY_BLOCK)
+    if nblocks % qsplit:
+        raise ValueError(f"{nblocks} query blocks of a {seq}-token sequence do not split into "
+                         f"{qsplit} equal ranges for {nhead} heads on {world} ranks")
+    return qsplit, nhead * qsplit // world, nblocks // qsplit
+
+
+def units_of_rank(nhead: int, world: int, rank: int, seq: int) -> list[tuple[int, int]]:
+    """The rank's work units as (head, first query block), in global unit order (unit u = head
+    u // qsplit, query range u % qsplit)."""
+    qsplit, per_rank, bpu = head_parallel_plan(nhead, world, seq)
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    return [(u // qsplit, (u % qsplit) * bpu) for u in range(rank * per_rank, (rank + 1) * per_rank)]
+
 
 def head_slice(nhead: int, world: int, rank: int) -> tuple[int, int]:
-    """[first, last) head of the rank: contiguous blocks, as shard_range."""
+    """[first, last) head of the rank when heads are dealt out whole: contiguous blocks, as
+    shard_range."""
     return shard_range(nhead, world, rank)
 
 
-def head_shard_weights(w: dict, nhead: int, world: int, rank: int) -> dict:
-    """The rank's slice of one layer's attention weights (numpy arrays in, numpy arrays out):
-    wqkv rows of its heads (kept in Q | K | V order), the matching bias entries, wo columns of
-    its heads.  The output bias is kept on rank 0 only (it must be added once)."""
+def head_rows(w: dict, nhead: int, heads) -> dict:
+    """The slice of one layer's attention weights that belongs to `heads` (numpy in, numpy out):
+    wqkv rows of those heads (kept in Q | K | V order), the matching bias entries, wo columns."""
     import numpy as np
     hidden, vdim = w["wo"].shape
     kdim = (w["wqkv"].shape[0] - vdim) // 2
     if kdim % nhead or vdim % nhead:
         raise ValueError("kdim and vdim must be multiples of nhead")
     dqk, dv = kdim // nhead, vdim // nhead
+    heads = list(heads)
+    qk = np.concatenate([np.arange(h * dqk, (h + 1) * dqk) for h in heads]) if heads else np.zeros(0, int)
+    vv = np.concatenate([np.arange(h * dv, (h + 1) * dv) for h in heads]) if heads else np.zeros(0, int)
+    rows = np.concatenate([qk, kdim + qk, 2 * kdim + vv]).astype(np.int64)
+    return {"wqkv": np.ascontiguousarray(w["wqkv"][rows]),
+            "bqkv": np.ascontiguousarray(w["bqkv"][rows]),
+            "wo": np.ascontiguousarray(w["wo"][:, vv.astype(np.int64)]),
+            "nhead_local": len(heads), "dh_qk": dqk, "dh_v": dv}
+
+
+def head_shard_weights(w: dict, nhead: int, world: int, rank: int) -> dict:
+    """Whole heads per rank: the rank's slice of the attention weights.  The output bias is kept
+    on rank 0 only (it must be added once)."""
+    import numpy as np
     h0, h1 = head_slice(nhead, world, rank)
-    rows = np.concatenate([np.arange(h0 * dqk, h1 * dqk),
-                           kdim + np.arange(h0 * dqk, h1 * dqk),
-                           2 * kdim + np.arange(h0 * dv, h1 * dv)])
-    out = {
-        "wqkv": np.ascontiguousarray(w["wqkv"][rows]),
-        "bqkv": np.ascontiguousarray(w["bqkv"][rows]),
-        "wo": np.ascontiguousarray(w["wo"][:, h0 * dv:h1 * dv]),
-        "bo": w["bo"] if rank == 0 else np.zeros_like(w["bo"]),
-        "nhead_local": h1 - h0, "dh_qk": dqk, "dh_v": dv,
-    }
+    out = head_rows(w, nhead, range(h0, h1))
+    out["bo"] = w["bo"] if rank == 0 else np.zeros_like(w["bo"])
     return out

@@ -169,15 +169,25 @@ def head_ptr_for(col_id: np.ndarray, nhead: int, vdim: int) -> np.ndarray:
 # encoder-layer weights
 # ---------------------------------------------------------------------------------------
 
+def normal_fast(seed: int, tensor_id: int, shape, std: float = 1.0, mean: float = 0.0) -> np.ndarray:
+    """N(mean, std^2) fp16 values from numpy's PCG64 keyed by (seed, tensor_id): an order of
+    magnitude faster than the counter-based generator, for large benchmark-only tensors whose
+    values nothing else has to reproduce element by element."""
+    rng = np.random.Generator(np.random.PCG64([int(seed) & 0xFFFFFFFF, int(tensor_id) & 0xFFFFFFFF]))
+    v = rng.standard_normal(int(np.prod(shape)), dtype=np.float32)
+    return (v * np.float32(std) + np.float32(mean)).astype(np.float16).reshape(shape)
+
+
 def encoder_layer_weights(seed: int, layer: int, hidden: int, ff: int, kdim: int | None = None,
                           vdim: int | None = None, std: float = 0.02, bias_std: float = 0.0,
-                          ln_noise: float = 0.0) -> dict:
+                          ln_noise: float = 0.0, fast: bool = False) -> dict:
     """Dense fp16 weights of one post-LN encoder layer: W ~ N(0, std^2), biases 0 (or
     N(0, bias_std^2)), LN gamma 1 and beta 0 (plus optional noise so tests exercise them).
-    wqkv has its output features ordered Q | K | V."""
+    wqkv has its output features ordered Q | K | V.  fast=True draws from normal_fast."""
     kdim = hidden if kdim is None else kdim
     vdim = hidden if vdim is None else vdim
     base = 1000 * (layer + 1)
+    normal = normal_fast if fast else globals()["normal"]
     def b(tid, n):
         return normal(seed, base + tid, (n,), bias_std) if bias_std > 0 else np.zeros(n, np.float16)
     w = {

@@ -162,3 +162,87 @@ def test_two_gloo_ranks_head_parallel_attention_block():
     kind, err = q.get(timeout=10)
     assert kind == "ok", err
     assert err < 1e-4, f"head-parallel partial sums differ from the full block by {err}"
+
+
+def test_work_units_cover_every_head_and_query_block_once():
+    """12 heads on 8 ranks: 24 (head, query half) units, 3 per rank, every (head, query block)
+    pair owned by exactly one rank and every rank with the same amount of attention work."""
+    et = entry.load_package()
+    for nhead, world, seq in ((12, 8, 4096), (12, 2, 1024), (16, 8, 4096), (12, 3, 384), (4, 8, 512)):
+        qsplit, per_rank, bpu = et.sharding.head_parallel_plan(nhead, world, seq)
+        nblocks = -(-seq // 128)
+        owner = np.full((nhead, nblocks), -1)
+        for r in range(world):
+            units = et.sharding.units_of_rank(nhead, world, r, seq)
+            assert len(units) == per_rank
+            for h, first in units:
+                assert (owner[h, first:first + bpu] == -1).all()
+                owner[h, first:first + bpu] = r
+        assert (owner >= 0).all()
+    assert et.sharding.head_parallel_plan(12, 8, 4096) == (2, 3, 16)
+    with pytest.raises(ValueError):
+        et.sharding.head_parallel_plan(12, 8, 128)  # one query block cannot be halved
+
+
+def _hp_units_worker(rank: int, world: int, port: int, out_q):
+    """Work-unit form on `world` gloo ranks with the oracle standing in for the kernels: each
+    rank attends over its (head, query range) units only; the all-reduced partial sums must
+    equal the unsharded attention block."""
+    try:
+        import torch
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        et = entry.load_package()
+        orc = entry.load_oracle()
+        orc.build()
+        orc.set_num_threads(1)
+        hidden, nhead, ff, seq = 96, 12, 128, 256   # 2 query blocks: 24 half-head units on 8 ranks
+        w = et.synth.encoder_layer_weights(5, 0, hidden, ff, std=0.1, bias_std=0.05)
+        x = et.synth.normal(5, 9, (seq, hidden), 1.0).astype(np.float32)
+        _, _, bpu = et.sharding.head_parallel_plan(nhead, world, seq)
+        units = et.sharding.units_of_rank(nhead, world, rank, seq)
+        heads = sorted({h for h, _ in units})
+        sl = et.sharding.head_rows(w, nhead, heads)
+        nh, dqk, dv = sl["nhead_local"], sl["dh_qk"], sl["dh_v"]
+        qkv = orc.linear_dense(x, sl["wqkv"], sl["bqkv"], 0)
+        zfull = orc.attention(qkv[:, :nh * dqk], qkv[:, nh * dqk:2 * nh * dqk], qkv[:, 2 * nh * dqk:],
+                              1, seq, nh, dqk, dv, 0)
+        z = np.zeros_like(zfull)
+        for h, first in units:  # query rows are independent: keep the unit's rows of its head
+            lh = heads.index(h)
+            r0, r1 = first * 128, min(seq, (first + bpu) * 128)
+            z[r0:r1, lh * dv:(lh + 1) * dv] = zfull[r0:r1, lh * dv:(lh + 1) * dv]
+        part = torch.from_numpy(orc.linear_dense(z, sl["wo"], w["bo"] if rank == 0 else None, 0))
+        dist.all_reduce(part)
+        if rank == 0:
+            fq = orc.linear_dense(x, w["wqkv"], w["bqkv"], 0)
+            fz = orc.attention(fq[:, :hidden], fq[:, hidden:2 * hidden], fq[:, 2 * hidden:], 1, seq,
+                               nhead, hidden // nhead, hidden // nhead, 0)
+            full = orc.linear_dense(fz, w["wo"], w["bo"], 0)
+            out_q.put(("ok", float(np.abs(part.numpy() - full).max())))
+        dist.destroy_process_group()
+    except Exception as e:
+        out_q.put(("error", repr(e)))
+        raise
+
+
+def test_eight_gloo_ranks_head_parallel_work_units():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world, port = 8, _free_port()
+    procs = [ctx.Process(target=_hp_units_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("a gloo rank did not finish")
+        assert p.exitcode == 0
+    kind, err = q.get(timeout=10)
+    assert kind == "ok", err
+    assert err < 1e-4, f"work-unit partial sums differ from the full block by {err}"
