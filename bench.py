@@ -577,6 +577,10 @@ def main():
 
         configs = {}
         configs["c2_b64"] = run_config(layers, 64, SEQ, flops_per_sequence())
+        # the reference's own operating point: one sequence, causal mask (latency of the stack)
+        configs["c2_b1_causal"] = run_config(layers, 1, SEQ, flops_per_sequence(),
+                                             mask_kind=et.MASK_CAUSAL)
+        configs["c2_b1_causal"]["us_per_stack_forward"] = configs["c2_b1_causal"]["ms_per_step"] * 1e3
 
         # C3: every Linear tile-pruned at 80 %, a quarter of each head's Q/K features removed
         kq = NHEAD * 48
@@ -723,6 +727,28 @@ def main():
                                     "kind": "port",
                                     "sample": f"best of 2 runs of the full {LAYERS}-layer stack over "
                                               f"{BATCH} sequences ({best:.2f} s each)"}
+
+    # ---- the reference's own CUDA build (recompiled for sm_100a), reported alongside: its
+    # paper-table driver at batch 1, seq 128, 12 layers.  Run last, in a process of its own.
+    if not args.skip_extras and world == 1:
+        import subprocess
+        ref_bin = os.path.join(ROOT, "oracle", "_ref", "ref_table2")
+        if os.path.exists(ref_bin):
+            try:
+                r = subprocess.run([ref_bin, str(LAYERS), "0.8"], capture_output=True, text=True,
+                                   timeout=180)
+                last = [l for l in r.stdout.splitlines() if l.startswith("{")]
+                rec = json.loads(last[-1]) if last else {"unavailable": f"no result line (exit {r.returncode})"}
+                rec["exit_code"] = r.returncode
+            except Exception as e:  # timeout, missing libraries ...
+                rec = {"unavailable": f"{type(e).__name__}: {e}"}
+        else:
+            rec = {"unavailable": "oracle/_ref/ref_table2 not built (needs the reference checkout at build time)"}
+        rec["note"] = ("the reference's kernels, cuBLAS calls and host classes compiled unmodified; "
+                       "constant weights, causal mask, batch 1; outputs not validated")
+        if "configs" in line and "c2_b1_causal" in line["configs"]:
+            rec["this_library_us_same_shape"] = line["configs"]["c2_b1_causal"]["us_per_stack_forward"]
+        line["reference_cuda"] = rec
 
     sampler.stop()
     line["clocks"] = sampler.summary()

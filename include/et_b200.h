@@ -4,7 +4,9 @@
  * Every entry point takes plain device pointers and sizes, launches on the given CUDA
  * stream, returns an int status (0 = ok, negative = error, see et_status_string), never
  * throws, never synchronises the device and never allocates: scratch memory is passed
- * in by the caller.  One host thread per GPU may call into the library concurrently.
+ * in by the caller.  One host thread per GPU may call into the library concurrently; the
+ * per-device state the library caches on a first call (error word address, kernel attributes,
+ * occupancy answers) is published with atomic stores, so first calls may overlap too.
  *
  * Layout conventions (all from the reference, cctry/SCpaper-2021):
  *   - activations: row-major fp16 [tokens, features], tokens = batch * seq, heads are

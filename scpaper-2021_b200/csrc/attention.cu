@@ -600,7 +600,7 @@ int launch_attention_impl(const __half* Q, const __half* K, const __half* V, __h
     const dim3 grid = n_units > 0 ? dim3(blocks_per_unit, n_units, batch)
                                   : dim3((seq + BQ - 1) / BQ, nhead, batch);
     auto go = [&](auto kern, int slot) -> int {
-        static bool attr_set[4][64] = {};
+        static std::atomic<bool> attr_set[4][64] = {};
         if (dev >= 0 && dev < 64 && !attr_set[slot][dev]) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (2 * 2 + 3 + 2) * ATOM_BYTES + EXTRA_BYTES + 1024) !=

@@ -427,7 +427,7 @@ int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half*
 
     const int nqa = (dh_qk + 63) / 64;
     const int smem_bytes = (2 * nqa + MAX_NC / 64 + 2) * ATOM_BYTES + 256 + 1024;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {

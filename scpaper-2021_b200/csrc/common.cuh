@@ -2,6 +2,8 @@
 // wrappers in inline PTX, descriptor builders, bounded waits and the status plumbing.
 #pragma once
 
+#include <atomic>
+
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>

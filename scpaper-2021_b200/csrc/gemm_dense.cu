@@ -14,6 +14,8 @@
 // Output modes: fp16 tile store (Linear layers), index-list store (row-pruned Linear:
 // scattered or compressed columns), grouped rows (per-head V.O projection), and fp32
 // split-K partials (consumed by the partial-sum LayerNorm kernel).
+#include <atomic>
+
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "kernels.h"
@@ -482,7 +484,7 @@ int launch_cfg_epi(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
                    GemmArgs args, int zdim, cudaStream_t stream) {
     using Cfg = GemmCfg<BN, STAGES, PERSIST>;
     auto kern = gemm_f16_kernel<BN, STAGES, PERSIST, B_MN, EPI>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -678,15 +680,18 @@ static __device__ __align__(256) __half g_col_gather_scratch[kNoAllocScratchHalv
 // The array's name is only a host-side handle; kernels need its device address, looked up
 // once per device (with that device current) and cached.
 __half* col_gather_scratch_address() {
-    static __half* cached[64] = {};
+    // several host threads may make their first call on a device at once: they all look up
+    // the same address, and the slot is atomic so that none reads a half-written pointer
+    static std::atomic<__half*> cached[64] = {};
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (cached[dev] != nullptr) return cached[dev];
+    __half* known = cached[dev].load(std::memory_order_acquire);
+    if (known != nullptr) return known;
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_col_gather_scratch) != cudaSuccess || p == nullptr)
         return nullptr;
-    cached[dev] = static_cast<__half*>(p);
-    return cached[dev];
+    cached[dev].store(static_cast<__half*>(p), std::memory_order_release);
+    return static_cast<__half*>(p);
 }
 
 int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __half* bias,
@@ -708,15 +713,18 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
         if (tall_bn != 0)
             return launch_gemm_tall_f16(X, ldx, W, ldw, bias, Y, ldy, M, N, K, act, tall_bn, stream);
     }
+    // An index list that only selects the bias (compressed output: column n of Y is feature
+    // col_map[n]) keeps the coalesced tile store; only a true scatter needs per-element stores.
+    const bool tile_store = col_map == nullptr || (!scatter && N % 8 == 0 && ldy % 8 == 0);
     TilePlan plan = pick_plan(M, N, K, 1);
-    if (plan.bn == 192 && col_map != nullptr) plan.bn = 128;  // 192 exists for the tile store only
+    if (plan.bn == 192 && !tile_store) plan.bn = 128;  // 192 exists for the tile store only
     const int bn = plan.bn;
     CUtensorMap tmA, tmB;
     int st;
     if ((st = encode_operand(&tmA, X, ldx, M, K, BM)) != ET_OK) return st;
     if ((st = encode_operand(&tmB, W, ldw, N, K, bn)) != ET_OK) return st;
     CUtensorMap tmY = tmA;  // placeholder when the index-list epilogue is used
-    if (col_map == nullptr) {
+    if (tile_store) {
         const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
         const uint64_t strides[1] = {static_cast<uint64_t>(ldy) * 2};
         const uint32_t box[2] = {64, 32};
@@ -726,7 +734,7 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
     GemmArgs args = base_args(Y, bias, ldy, M, N, K, act);
     args.col_map = col_map;
     args.scatter = scatter;
-    args.out_mode = col_map == nullptr ? OUT_TILE_F16 : OUT_INDEXED;
+    args.out_mode = tile_store ? OUT_TILE_F16 : OUT_INDEXED;
     return dispatch<false>(plan, tmA, tmB, tmY, args, 1, stream);
 }
 

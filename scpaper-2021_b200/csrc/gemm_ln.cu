@@ -306,7 +306,7 @@ bool gemm_ln_applies(int M, int N, int K) {
 // (a cluster needs that many free SMs inside one GPC, so this is less than SMs / cluster size
 // in general; asked once per device and size).  0 if the question fails.
 int gemm_ln_resident_clusters(int N) {
-    static int known[64][LN_MAX_CLUSTER + 1] = {};  // 0 = not asked, else answer + 1
+    static std::atomic<int> known[64][LN_MAX_CLUSTER + 1] = {};  // 0 = not asked, else answer + 1
     const int csize = N / LN_BN;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -357,7 +357,7 @@ int launch_gemm_ln(const __half* X, int ldx, const __half* W, int ldw, const __h
         st = make_tensor_map_f16(&tmY, out, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != ET_OK) return st;
     }
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {

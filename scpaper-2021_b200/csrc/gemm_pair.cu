@@ -375,7 +375,7 @@ int launch_pair_act(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtens
                     const GemmArgs& args, cudaStream_t stream) {
     using Cfg = PairCfg<BN, STAGES, PERSIST, PARTIAL>;
     auto kern = gemm_pair_kernel<BN, STAGES, PERSIST, PARTIAL, ACT>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {

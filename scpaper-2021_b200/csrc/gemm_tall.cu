@@ -230,7 +230,7 @@ int launch_tall_act(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtens
                     const GemmArgs& args, cudaStream_t stream) {
     using Cfg = TallCfg<BN, STAGES>;
     auto kern = gemm_tall_kernel<BN, STAGES, ACT>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {

@@ -59,6 +59,15 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
                               const __half* X, __half* Y, int T, int in, int out, int act,
                               cudaStream_t stream);
 
+// The packed tile-CSR Linear as a persistent kernel (one CTA per SM walks work items of 128
+// tokens x 256 output features, two items' accumulators in tensor memory); see
+// linear_tile_persist.cu.  nnz_tiles > 0.
+bool tile_persist_enabled();
+int launch_linear_tile_persist(const int* row_ptr, const uint32_t* pk_mask, const int* pk_off,
+                               const __half* pk_tiles, int nnz_tiles, const __half* bias,
+                               const __half* X, __half* Y, int T, int in, int out, int act,
+                               cudaStream_t stream);
+
 // Fused attention (see attention.cu).  Vc_col_id / head_ptr are null for an uncompressed V.
 int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,
                      int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv, int ldz,

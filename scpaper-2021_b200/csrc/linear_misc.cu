@@ -205,7 +205,7 @@ int et_linear_csr_fwd(const int32_t* indptr, const int32_t* indices, const et_ha
     if (in % 8 || in > 8192) return ET_ERR_SHAPE;
     if (!et::aligned16(X)) return ET_ERR_ALIGNMENT;
     const int smem = et::CSR_TOKENS * in * 2;
-    static int attr_bytes[64] = {};
+    static std::atomic<int> attr_bytes[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (smem > 48 * 1024 && dev >= 0 && dev < 64 && attr_bytes[dev] < smem) {

@@ -62,8 +62,7 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                    const __grid_constant__ CUtensorMap tmY, const int* __restrict__ row_ptr,
                    const int* __restrict__ row_off, const uint32_t* __restrict__ pk_mask,
                    const int* __restrict__ pk_off, const __half* __restrict__ pk_tiles,
-                   const __half* __restrict__ bias, int T, int in, int out, int n_issuers,
-                   int* err_word) {
+                   const __half* __restrict__ bias, int T, int in, int out, int* err_word) {
     static_assert(NP == 1 || PACKED, "two panels per CTA exist for packed weights only");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment computed on the shared-window offset, so that the pointer keeps its
@@ -85,6 +84,10 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     uint32_t* chunk_mask = reinterpret_cast<uint32_t*>(s_bias + NP * TBN);  // [NP][nchunk_p]
     // unpacked: tile_at[8][nbc]; packed: [NP][nchunk_p] (first tile of each chunk)
     int* tile_at = reinterpret_cast<int*>(chunk_mask + NP * nchunk_p);
+    // per (panel, block row) and chunk, what the issuing thread of that row needs: bits 0-3
+    // which of the chunk's 4 block columns hold a tile of the row, bits 4-9 the row's first
+    // slot among the panel's tiles of the chunk, bit 15 set when the whole CTA skips the chunk
+    uint16_t* cmd = reinterpret_cast<uint16_t*>(tile_at + (PACKED ? NP * nchunk_p : PANEL_ROWS * nbc));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -122,9 +125,9 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         tma_prefetch_desc(&tmW);
         for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], n_issuers);
+            mbar_init(&empty_bar[s], T_EPI_WARPS);
         }
-        mbar_init(acc_bar, n_issuers);
+        mbar_init(acc_bar, T_EPI_WARPS);
         *abort_flag = 0;
         *max_cnt = 0;
         fence_barrier_init();
@@ -154,6 +157,17 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             mc = cnt > mc ? cnt : mc;
         }
         if (mc > 0) atomicMax(max_cnt, mc);
+        for (int i = threadIdx.x; i < NP * PANEL_ROWS * nchunk; i += TILE_THREADS) {
+            const int kr = i / nchunk, c = i - kr * nchunk;
+            const int k = kr / PANEL_ROWS, r = kr - k * PANEL_ROWS;
+            uint32_t any = 0;
+#pragma unroll
+            for (int kk = 0; kk < NP; ++kk) any |= chunk_mask[kk * nchunk_p + c];
+            const uint32_t m = chunk_mask[k * nchunk_p + c];
+            cmd[kr * nchunk_p + c] = static_cast<uint16_t>(
+                ((m >> (4 * r)) & 0xFu) | (__popc(m & ((1u << (4 * r)) - 1u)) << 4) |
+                (any == 0u ? 0x8000u : 0u));
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -275,17 +289,29 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const int half = (warp - 2) >> 2;  // which 64 output columns of a panel
         bool ok = true;
         if (panel_tiles > 0) {
-            // the first n_issuers of these warps issue; warp e takes block rows e, e + n_issuers, ...
-            if (lane == 0 && e < n_issuers) {
+            // one thread per warp issues: warp e owns block row e of every panel (accumulator
+            // rows e, e + 8, ...) and reads those rows' per-chunk commands
+            if (lane == 0) {
                 constexpr uint32_t idesc = make_idesc_f16(TBM, 16, 0, 0);
-                uint32_t started[NP];  // bit r: block row r of the panel has received a product
-#pragma unroll
-                for (int k = 0; k < NP; ++k) started[k] = 0u;
+                uint32_t started = 0u;  // bit j: this warp's row of panel j has received a product
                 int s = 0, stage_it = 0;
                 uint32_t ph = 0;
+                const uint32_t ring_addr = smem_u32(ring);
+                // descriptors differ from stage to stage and tile to tile only in their start
+                // address field (16-byte units)
+                const uint64_t a_desc0 = make_smem_desc(ring_addr, 16, 1024, SWZ_128B);
+                const uint64_t b_desc0 = make_smem_desc(ring_addr + X_STAGE_BYTES, 16, 256, SWZ_32B);
+                const uint32_t stage_units = static_cast<uint32_t>(stage_bytes) >> 4;
+                const uint32_t panel_units = static_cast<uint32_t>(nslot) * 32u;
                 for (int kc = 0; kc < nchunk; ++kc) {
-                    uint32_t m[NP];
-                    if (masks_of(kc, m) == 0u) continue;
+                    uint32_t c[NP];
+                    uint32_t any = 0u;
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) {
+                        c[j] = cmd[(j * PANEL_ROWS + e) * nchunk_p + kc];
+                        any |= c[j] & 0xFu;
+                    }
+                    if (c[0] & 0x8000u) continue;
                     // a warp without a tile in this chunk still waits: its arrival must not
                     // run ahead into the stage's next use
                     if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) {
@@ -294,36 +320,29 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                         break;
                     }
                     if (e == 0 && stage_it < 12) ET_TL(18 + stage_it * 4);
-                    bool issued_any = false;
+                    if (any) {
+                        tc_fence_after_sync();
+                        const uint64_t a_base = a_desc0 + static_cast<uint64_t>(s) * stage_units;
+                        const uint64_t b_base = b_desc0 + static_cast<uint64_t>(s) * stage_units;
 #pragma unroll
-                    for (int k = 0; k < NP; ++k) {
-                        for (int r = e; r < PANEL_ROWS; r += n_issuers) {
-                            uint32_t nib = (m[k] >> (4 * r)) & 0xFu;
+                        for (int j = 0; j < NP; ++j) {
+                            uint32_t nib = c[j] & 0xFu;
                             if (nib == 0u) continue;
-                            if (!issued_any) tc_fence_after_sync();
-                            issued_any = true;
-                            const uint32_t x_addr = smem_u32(ring + s * stage_bytes);
-                            // descriptors differ from tile to tile only in their start address
-                            const uint64_t a_base = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
-                            uint64_t bd = make_smem_desc(
-                                x_addr + X_STAGE_BYTES + k * nslot * 512 +
-                                    512u * __popc(m[k] & ((1u << (4 * r)) - 1u)),
-                                16, 256, SWZ_32B);
+                            uint64_t bd = b_base + j * panel_units + ((c[j] >> 4) & 0x3Fu) * 32u;
                             while (nib) {
                                 const int kb = __ffs(nib) - 1;
                                 nib &= nib - 1;
-                                mma_f16_ss(tmem_base + k * TBN + r * 16,
+                                mma_f16_ss(tmem_base + j * TBN + e * 16,
                                            a_base + static_cast<uint64_t>(kb * 2), bd, idesc,
-                                           (started[k] >> r) & 1u);
-                                started[k] |= 1u << r;
+                                           (started >> j) & 1u);
+                                started |= 1u << j;
                                 bd += 32;  // next 512-byte slot
                             }
                         }
-                    }
-                    if (issued_any)
                         mma_commit(&empty_bar[s]);
-                    else
+                    } else {
                         mbar_arrive(&empty_bar[s]);
+                    }
                     if (e == 0 && stage_it < 12) ET_TL(19 + stage_it * 4);
                     ++stage_it;
                     if (++s == nstages) {
@@ -335,9 +354,7 @@ linear_tile_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 if (e == 0) ET_TL(2);
             }
             __syncwarp();
-            // warps that do not issue sleep between polls: they share schedulers with the issuers
-            ok = e < n_issuers ? mbar_wait_bounded(acc_bar, 0, abort_flag)
-                               : mbar_wait_bounded_relaxed(acc_bar, 0, abort_flag);
+            ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
             if (!ok && lane == 0) report_error(err_word, abort_flag, DEV_TIMEOUT_TILE_EPILOGUE);
         }
         ok = __all_sync(0xffffffffu, ok);
@@ -449,7 +466,6 @@ __global__ void pack_tiles_kernel(const uint4* __restrict__ src, const int* __re
 }
 
 int g_tile_wide = -1;  // test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA
-int g_tile_issuers = 8;  // test hook: threads of a CTA that issue tensor-core products (1..8)
 
 namespace {
 int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, const uint32_t* pk_mask,
@@ -510,12 +526,13 @@ int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, cons
         packed && g_tile_wide != 0 && (g_tile_wide > 0 || (npanel >= 2 && wide_ctas * 4 >= sms * 5L));
     const int np = wide ? 2 : 1;
     const int smem_bytes = RING_BYTES + 256 + np * TBN * 4 + np * nchunk_p * 4 +
-                           (packed ? np * nchunk_p * 4 : PANEL_ROWS * nbc * 4) + 1024;
+                           (packed ? np * nchunk_p * 4 : PANEL_ROWS * nbc * 4) +
+                           np * PANEL_ROWS * nchunk_p * 2 + 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     dim3 grid((npanel + np - 1) / np, (T + TBM - 1) / TBM);
     auto go = [&](auto kern, int slot) -> cudaError_t {
-        static int attr_bytes[9][64] = {};
+        static std::atomic<int> attr_bytes[9][64] = {};
         if (dev >= 0 && dev < 64 && attr_bytes[slot][dev] < smem_bytes) {
             const cudaError_t ea =
                 cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -523,8 +540,7 @@ int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, cons
             attr_bytes[slot][dev] = smem_bytes;
         }
         return launch_kernel(kern, grid, dim3(TILE_THREADS), smem_bytes, stream, tmX, tmW, tmY,
-                             row_ptr, row_off, pk_mask, pk_off, tiles, bias, T, in, out,
-                             g_tile_issuers, err);
+                             row_ptr, row_off, pk_mask, pk_off, tiles, bias, T, in, out, err);
     };
     cudaError_t e;
     if (wide) {
@@ -555,6 +571,9 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
                               const __half* pk_tiles, int nnz_tiles, const __half* bias,
                               const __half* X, __half* Y, int T, int in, int out, int act,
                               cudaStream_t stream) {
+    if (nnz_tiles > 0 && tile_persist_enabled())
+        return launch_linear_tile_persist(row_ptr, pk_mask, pk_off, pk_tiles, nnz_tiles, bias, X, Y, T,
+                                          in, out, act, stream);
     return launch_tile_common(true, row_ptr, nullptr, pk_mask, pk_off, pk_tiles, nnz_tiles, bias, X, Y,
                               T, in, out, act, stream);
 }
@@ -566,8 +585,6 @@ extern "C" {
 #ifdef ET_TEST_HOOKS
 // Test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA (packed weights).
 void et_debug_set_tile_wide(int mode) { et::g_tile_wide = mode; }
-// Test hook: how many threads of a CTA issue the tensor-core products (1, 2, 4 or 8).
-void et_debug_set_tile_issuers(int n) { et::g_tile_issuers = n < 1 ? 1 : (n > 8 ? 8 : n); }
 #endif  // ET_TEST_HOOKS
 
 int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,

@@ -186,10 +186,16 @@ mixed_probe_kernel(int issuers, int count, int sync_warps, int iters, int commit
             const uint64_t a_desc = make_smem_desc(smem_u32(sA), 16, 1024, SWZ_128B);
             const uint64_t b_desc = make_smem_desc(smem_u32(sB), 16, 256, SWZ_32B);
             const long long t0 = clock64();
-            for (int i = 0; i < count; ++i) {
-                mma_f16_ss(tmem_base + warp * 64 + (i & 3) * 16, a_desc + static_cast<uint64_t>((i & 3) * 2),
-                           b_desc, idesc, i >= 4 ? 1u : 0u);
-                if (commit_every > 0 && (i % commit_every) == commit_every - 1) mma_commit(side_bar);
+            // groups of `commit_every` products, each followed by one commit (no division in the
+            // loop: a single thread's dependent integer chain would dominate the timing)
+            const int group = commit_every > 0 ? commit_every : count;
+            for (int i = 0; i < count; i += group) {
+                const int end = i + group < count ? i + group : count;
+                for (int j = i; j < end; ++j)
+                    mma_f16_ss(tmem_base + warp * 64 + (j & 3) * 16,
+                               a_desc + static_cast<uint64_t>((j & 3) * 2), b_desc, idesc,
+                               j >= 4 ? 1u : 0u);
+                if (commit_every > 0) mma_commit(side_bar);
             }
             mma_commit(&bar[warp]);
             ok = mbar_wait_bounded(&bar[warp], 0, abort_flag);

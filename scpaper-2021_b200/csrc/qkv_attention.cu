@@ -455,7 +455,7 @@ int launch_qkv_attention(const __half* X, const __half* Wqkv, const __half* bqkv
     int dev = 0;
     cudaGetDevice(&dev);
     auto go = [&](auto kern, int slot, const QkvAttnArgs& args) -> int {
-        static bool attr_set[4][64] = {};
+        static std::atomic<bool> attr_set[4][64] = {};
         if (dev >= 0 && dev < 64 && !attr_set[slot][dev]) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QA_SMEM) !=
                 cudaSuccess)

@@ -18,7 +18,7 @@ __device__ int g_device_error_word = 0;
 struct PerDevice {
     int* err_word = nullptr;
     int sm_count = 0;
-    bool ready = false;
+    std::atomic<bool> ready{false};  // published with release order after the fields above
 };
 PerDevice g_dev[kMaxDevices];
 std::mutex g_mutex;
@@ -27,15 +27,15 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn g_encode = nullptr;
+std::atomic<EncodeTiledFn> g_encode{nullptr};
 
 PerDevice* current_device() {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     PerDevice* pd = &g_dev[dev];
-    if (pd->ready) return pd;
+    if (pd->ready.load(std::memory_order_acquire)) return pd;
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (pd->ready) return pd;
+    if (pd->ready.load(std::memory_order_relaxed)) return pd;
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_device_error_word) != cudaSuccess) return nullptr;
     int sms = 0;
@@ -43,7 +43,7 @@ PerDevice* current_device() {
         return nullptr;
     pd->err_word = static_cast<int*>(p);
     pd->sm_count = sms;
-    pd->ready = true;
+    pd->ready.store(true, std::memory_order_release);
     return pd;
 }
 
@@ -91,16 +91,19 @@ namespace {
 int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     CUtensorMapSwizzle swizzle) {
-    if (!g_encode) {
+    EncodeTiledFn encode = g_encode.load(std::memory_order_acquire);
+    if (!encode) {
         std::lock_guard<std::mutex> lock(g_mutex);
-        if (!g_encode) {
+        encode = g_encode.load(std::memory_order_relaxed);
+        if (!encode) {
             void* fn = nullptr;
             cudaDriverEntryPointQueryResult qres;
             if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) !=
                     cudaSuccess ||
                 qres != cudaDriverEntryPointSuccess || fn == nullptr)
                 return ET_ERR_CUDA;
-            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+            encode = reinterpret_cast<EncodeTiledFn>(fn);
+            g_encode.store(encode, std::memory_order_release);
         }
     }
     if (rank < 2 || rank > 3) return ET_ERR_INVALID_ARG;
@@ -117,7 +120,7 @@ int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* bas
         if (strides_bytes[i] % 16 != 0) return ET_ERR_ALIGNMENT;
         gstrides[i] = strides_bytes[i];
     }
-    CUresult r = g_encode(map, dtype, static_cast<cuuint32_t>(rank),
+    CUresult r = encode(map, dtype, static_cast<cuuint32_t>(rank),
                           const_cast<void*>(base), gdims, gstrides, gbox, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -181,7 +184,8 @@ int et_validate_tile_mat(const int32_t* row_ptr, const int32_t* row_off, int nnz
     const int nbr = out / 16, nbc = in / 16;
     if (row_ptr[0] != 0 || row_ptr[nbr] != nnz_tiles) return ET_ERR_INDEX;
     for (int br = 0; br < nbr; ++br) {
-        if (row_ptr[br + 1] < row_ptr[br]) return ET_ERR_INDEX;
+        // monotone and inside the stored range BEFORE any row_off entry is read
+        if (row_ptr[br + 1] < row_ptr[br] || row_ptr[br + 1] > nnz_tiles) return ET_ERR_INDEX;
         for (int i = row_ptr[br]; i < row_ptr[br + 1]; ++i) {
             if (row_off[i] < 0 || row_off[i] >= nbc) return ET_ERR_INDEX;
             if (i > row_ptr[br] && row_off[i] <= row_off[i - 1]) return ET_ERR_INDEX;
@@ -226,7 +230,7 @@ int et_validate_csr(const int32_t* indptr, const int32_t* indices, int nnz, int 
         return ET_ERR_INVALID_ARG;
     if (indptr[0] != 0 || indptr[out] != nnz) return ET_ERR_INDEX;
     for (int o = 0; o < out; ++o) {
-        if (indptr[o + 1] < indptr[o]) return ET_ERR_INDEX;
+        if (indptr[o + 1] < indptr[o] || indptr[o + 1] > nnz) return ET_ERR_INDEX;
         for (int i = indptr[o]; i < indptr[o + 1]; ++i) {
             if (indices[i] < 0 || indices[i] >= in) return ET_ERR_INDEX;
             if (i > indptr[o] && indices[i] <= indices[i - 1]) return ET_ERR_INDEX;

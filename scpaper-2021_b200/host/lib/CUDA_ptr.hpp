@@ -19,25 +19,27 @@ template <typename T> class CUDA_ptr {
     std::size_t size = 0;
 
     CUDA_ptr() = delete;
+    // An empty buffer still owns one element's worth of memory (so get() is never null), but
+    // copies, fills and clears move exactly `size` elements: nothing is read from an empty source.
     explicit CUDA_ptr(const std::size_t n) : size(n) {
-        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), bytes()));
-        cudaChk(cudaMemset(ptr, 0, bytes()));
+        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), alloc_bytes()));
+        cudaChk(cudaMemset(ptr, 0, alloc_bytes()));
     }
     CUDA_ptr(const T* src, const std::size_t n) : size(n) {
-        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), bytes()));
-        cudaChk(cudaMemcpy(ptr, src, bytes(), cudaMemcpyDefault));
+        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), alloc_bytes()));
+        if (n) cudaChk(cudaMemcpy(ptr, src, bytes(), cudaMemcpyDefault));
     }
     CUDA_ptr(const std::vector<T>& v) : size(v.size()) {
-        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), bytes()));
-        cudaChk(cudaMemcpy(ptr, v.data(), bytes(), cudaMemcpyHostToDevice));
+        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), alloc_bytes()));
+        if (size) cudaChk(cudaMemcpy(ptr, v.data(), bytes(), cudaMemcpyHostToDevice));
     }
     CUDA_ptr(const std::size_t n, const T val) : size(n) {
-        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), bytes()));
+        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), alloc_bytes()));
         set(val);
     }
     CUDA_ptr(const CUDA_ptr<T>& o) : size(o.size) {
-        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), bytes()));
-        cudaChk(cudaMemcpy(ptr, o.ptr, bytes(), cudaMemcpyDeviceToDevice));
+        cudaChk(cudaMalloc(reinterpret_cast<void**>(&ptr), alloc_bytes()));
+        if (size) cudaChk(cudaMemcpy(ptr, o.ptr, bytes(), cudaMemcpyDeviceToDevice));
     }
     CUDA_ptr(CUDA_ptr<T>&& o) noexcept : ptr(o.ptr), size(o.size) { o.ptr = nullptr; }
     CUDA_ptr& operator=(const CUDA_ptr&) = delete;
@@ -52,22 +54,26 @@ template <typename T> class CUDA_ptr {
     }
     ~CUDA_ptr() { util::cuda_free_safe(ptr); }
 
-    void clear() { cudaChk(cudaMemset(ptr, 0, bytes())); }
+    void clear() { cudaChk(cudaMemset(ptr, 0, alloc_bytes())); }
     T* get() { return ptr; }
     T* get() const { return ptr; }
-    void dump(T* dst) const { cudaChk(cudaMemcpy(dst, ptr, bytes(), cudaMemcpyDeviceToHost)); }
+    void dump(T* dst) const {
+        if (size) cudaChk(cudaMemcpy(dst, ptr, bytes(), cudaMemcpyDeviceToHost));
+    }
     std::vector<T> to_host() const {
         std::vector<T> h(size);
         if (size) dump(h.data());
         return h;
     }
     void set(const T val) {
+        if (size == 0) return;
         std::vector<T> h(size, val);
         cudaChk(cudaMemcpy(ptr, h.data(), bytes(), cudaMemcpyHostToDevice));
     }
 
   private:
-    std::size_t bytes() const { return sizeof(T) * (size ? size : 1); }
+    std::size_t bytes() const { return sizeof(T) * size; }
+    std::size_t alloc_bytes() const { return sizeof(T) * (size ? size : 1); }
 };
 
 }  // namespace culib
