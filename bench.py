@@ -251,6 +251,10 @@ def main():
     ap.add_argument("--tile-only", action="store_true",
                     help="launch the tile-pruned Linear alone (2048 x 768 -> 3072, 80 %% of the "
                          "tiles pruned, three times) and exit: the small case profilers capture")
+    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "layer"],
+                    help="launch one more small case three times and exit (for profilers): fused V.O "
+                         "attention, the CTA-pair GEMM at 8192^3, skip-LayerNorm, the 1x16 vector "
+                         "kernel, the column-pruned Linear (gather + GEMM), one dense encoder layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
@@ -298,6 +302,44 @@ def main():
         torch.cuda.synchronize()
         print(json.dumps({"tile_only": True, "tokens": _T, "in": HIDDEN, "out": FF,
                           "stored_tiles": pk.nnz, "device_error": et.device_error()}))
+        return
+
+    if args.only:
+        rnd = lambda tid, shape, std=1.0: torch.from_numpy(et.synth.normal_fast(1, tid, shape, std)).to(dev)
+        T = _T
+        if args.only == "vo":      # 16 sequences x 128 tokens, 12 heads
+            q, k = rnd(1, (T, HIDDEN)), rnd(2, (T, HIDDEN))
+            vo = rnd(3, (BATCH * NHEAD * SEQ, HIDDEN))
+            fn = lambda: et.fused_vo_attention(q, k, vo, None, BATCH, SEQ, NHEAD, 64, HIDDEN)
+        elif args.only == "pair":  # 8192^3 on CTA pairs
+            a, w = rnd(1, (8192, 8192)), rnd(2, (8192, 8192), 0.02)
+            y = torch.empty((8192, 8192), dtype=torch.float16, device=dev)
+            fn = lambda: et.linear_dense(a, w, None, 0, out=y)
+        elif args.only == "layernorm":  # 64 x 2048 rows of 768: 600 MB of traffic, beyond L2
+            a, s2 = rnd(1, (64 * T, HIDDEN)), rnd(2, (64 * T, HIDDEN))
+            g = torch.ones(HIDDEN, dtype=torch.float16, device=dev)
+            o = torch.empty_like(a)
+            fn = lambda: et.skip_layernorm(a, s2, g, g, out=o)
+        elif args.only == "1x16":  # 2048 x 768 -> 3072, 90 % of the vectors pruned
+            W = et.synth.prune_1x16(et.synth.normal_fast(1, 2, (FF, HIDDEN), 0.02), 1, 3, 0.9)
+            ti, ri, da = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_1x16(W))
+            x = rnd(1, (T, HIDDEN))
+            fn = lambda: et.linear_1x16(x, ti, ri, da, FF)
+        elif args.only == "col":   # 8192 x 3072 -> 768, half of the input columns kept
+            W = et.synth.normal_fast(1, 2, (HIDDEN, FF), 0.02)
+            ids = et.synth.choose_ids(1, 3, FF, 0.5)
+            cid, cols = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_col(W, ids))
+            x = rnd(1, (4 * T, FF))
+            fn = lambda: et.linear_col(x, cid, cols)
+        else:                      # one dense BERT-base layer, 16 x 128 tokens
+            lw = et.synth.encoder_layer_weights(SEED, 0, HIDDEN, FF, fast=True)
+            st1 = et.EncoderStack([et.EncoderLayer(lw, NHEAD, et.ACT_GELU, device=dev)], BATCH, SEQ, dev)
+            x = rnd(1, (T, HIDDEN))
+            fn = lambda: st1.forward(x)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        print(json.dumps({"only": args.only, "device_error": et.device_error()}))
         return
 
     def launch_count():

@@ -108,14 +108,17 @@ int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_
                        int in, int out, int act, et_stream stream);
 
 /* The same tile-pruned Linear on RE-PACKED weights.  Weights are static, so the operator
- * may reorder its tiles once into the order the kernel consumes them - (panel of 8 block
- * rows, chunk of 4 block columns, row, column) - with one presence mask and one tile offset
- * per (panel, chunk); a chunk's tiles then arrive with a single bulk copy.  The re-packing
- * is a pure permutation of the tile-CSR arrays:
+ * may reorder its tiles once into the order the kernels consume them - (pair of panels of 8
+ * block rows, chunk of 4 block columns, panel of the pair, row, column) - with one presence
+ * mask and one tile offset per (panel, chunk); the tiles a panel pair needs for a chunk then
+ * arrive with a single bulk copy.  The re-packing is a pure permutation of the tile-CSR arrays:
  *   et_tile_pack_dims   sizes of the mask / offset arrays (npanel * nchunk entries each);
  *   et_tile_pack_plan   HOST index arrays in, masks / offsets / permutation out (host);
  *   et_tile_pack_tiles  packed_tiles[i] = tiles[perm[i]] on the GPU (perm: device array);
- *   et_linear_tile_packed_fwd  the forward pass; row_ptr as in et_linear_tile_fwd.
+ *   et_linear_tile_packed_fwd  the forward pass; row_ptr as in et_linear_tile_fwd.  It runs as
+ *     a persistent kernel: one CTA per SM walks work items of 128 tokens x 256 output features
+ *     and keeps two items' accumulators in tensor memory, so that one item's bias / activation
+ *     / store overlaps the next item's products.
  * Stands in for the same reference call as et_linear_tile_fwd (Linear/SPMM_tile.cu:312-324);
  * the reference keeps its tiles in file order. */
 int et_tile_pack_dims(int in, int out, int* npanel, int* nchunk);

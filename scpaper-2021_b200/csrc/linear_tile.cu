@@ -17,7 +17,7 @@
 //
 // Packed form.  Issuing one TMA per 512-byte tile makes the producer the bottleneck at high
 // sparsity, so the operator can re-pack its (static) weights once: tiles are reordered into
-// (panel, chunk, row, column) order - the order in which the kernel consumes them - and
+// (pair of panels, chunk, panel, row, column) order - the order in which the kernels consume them - and
 // stored pre-swizzled, with one presence mask and one tile offset per (panel, chunk).  A
 // chunk's tiles are then one contiguous run fetched by a single bulk copy, and the prologue
 // reads ready-made masks instead of building them.  The re-packing is a pure permutation of
@@ -617,23 +617,32 @@ int et_tile_pack_plan(const int32_t* row_ptr, const int32_t* row_off, int nnz_ti
     const int npanel = (out + et::TBN - 1) / et::TBN, nchunk = (in + et::CHUNK - 1) / et::CHUNK;
     const int nbr = out / 16;
     int next = 0;
-    for (int p = 0; p < npanel; ++p) {
-        // cursor per block row of the panel (columns ascend inside a row)
-        int cur[et::PANEL_ROWS], end[et::PANEL_ROWS];
-        for (int r = 0; r < et::PANEL_ROWS; ++r) {
-            const int br = p * et::PANEL_ROWS + r;
+    // Packed order: (pair of panels, chunk, panel of the pair, row, column).  The tiles of one
+    // (panel, chunk) stay one contiguous run, which is all the one-item kernels rely on, and the
+    // two panels of a pair follow each other inside a chunk, so the persistent kernel fetches a
+    // pair's tiles of a chunk with one bulk copy.
+    for (int p0 = 0; p0 < npanel; p0 += 2) {
+        // cursor per block row of the pair (columns ascend inside a row)
+        int cur[2 * et::PANEL_ROWS], end[2 * et::PANEL_ROWS];
+        for (int r = 0; r < 2 * et::PANEL_ROWS; ++r) {
+            const int br = p0 * et::PANEL_ROWS + r;
             cur[r] = br < nbr ? row_ptr[br] : 0;
             end[r] = br < nbr ? row_ptr[br + 1] : 0;
         }
         for (int c = 0; c < nchunk; ++c) {
-            uint32_t mask = 0;
-            pk_off[p * nchunk + c] = next;
-            for (int r = 0; r < et::PANEL_ROWS; ++r)
-                while (cur[r] < end[r] && row_off[cur[r]] < (c + 1) * 4) {
-                    mask |= 1u << (r * 4 + (row_off[cur[r]] & 3));
-                    perm[next++] = cur[r]++;
+            for (int k = 0; k < 2 && p0 + k < npanel; ++k) {
+                uint32_t mask = 0;
+                pk_off[(p0 + k) * nchunk + c] = next;
+                for (int r = 0; r < et::PANEL_ROWS; ++r) {
+                    int& cu = cur[k * et::PANEL_ROWS + r];
+                    const int en = end[k * et::PANEL_ROWS + r];
+                    while (cu < en && row_off[cu] < (c + 1) * 4) {
+                        mask |= 1u << (r * 4 + (row_off[cu] & 3));
+                        perm[next++] = cu++;
+                    }
                 }
-            pk_mask[p * nchunk + c] = mask;
+                pk_mask[(p0 + k) * nchunk + c] = mask;
+            }
         }
     }
     return next == nnz_tiles ? ET_OK : ET_ERR_INDEX;

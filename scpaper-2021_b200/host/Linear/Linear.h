@@ -218,6 +218,10 @@ template <> class Linear<tile_mat> {
     }
 };
 
+// 1x16-vector weights.  A tensor-core product cannot skip single vectors inside a 16 x 16
+// tile, so at construction the weight is expanded once to a dense matrix when the library
+// expects the dense GEMM to win (et_1x16_prefer_dense: unless almost nothing is stored); the
+// vector kernel serves the rest.  The reference's arrays stay available in `weight`.
 template <> class Linear<mat1x16> {
   public:
     const uint32_t in_size;
@@ -227,15 +231,40 @@ template <> class Linear<mat1x16> {
     culib::CUDA_ptr<half> bias;
 
     Linear(int _in_size, int _out_size, const mat1x16& w, const half* b, int _size)
-        : in_size(_in_size), out_size(_out_size), size(_size), weight(w), bias(b, _out_size) {}
+        : in_size(_in_size), out_size(_out_size), size(_size), weight(w), bias(b, _out_size) {
+        prepare();
+    }
     Linear(int _in_size, int _out_size, mat1x16&& w, const half* b, int _size)
         : in_size(_in_size), out_size(_out_size), size(_size), weight(std::move(w)),
-          bias(b, _out_size) {}
+          bias(b, _out_size) {
+        prepare();
+    }
     void forward(half* output, half* input, cudaStream_t stream = 0) {
+        forward_act(output, input, ET_ACT_NONE, stream);
+    }
+    void forward_act(half* output, const half* input, int act, cudaStream_t stream = 0) {
+        if (dense) {
+            etChk(et_linear_dense_fwd(et_ptr(input), et_ptr(dense->get()), et_ptr(bias.get()),
+                                      et_ptr(output), size, (int)in_size, (int)out_size, act,
+                                      stream));
+            return;
+        }
         etChk(et_linear_1x16_fwd(weight.tile_idx.get(), weight.row_idx.get(),
                                  et_ptr(weight.data.get()), weight.ntile, et_ptr(bias.get()),
                                  et_ptr(input), et_ptr(output), size, (int)in_size, (int)out_size,
-                                 ET_ACT_NONE, stream));
+                                 act, stream));
+    }
+
+  private:
+    std::unique_ptr<culib::CUDA_ptr<half>> dense;  // expanded weight [out, in]
+
+    void prepare() {
+        if (weight.ntile <= 0 || !et_1x16_prefer_dense((int)in_size, (int)out_size, weight.ntile))
+            return;
+        dense = std::make_unique<culib::CUDA_ptr<half>>((size_t)in_size * out_size);
+        etChk(et_1x16_densify(weight.tile_idx.get(), weight.row_idx.get(), et_ptr(weight.data.get()),
+                              weight.ntile, (int)in_size, (int)out_size, et_ptr(dense->get()), 0));
+        cudaChk(cudaStreamSynchronize(0));
     }
 };
 

@@ -25,6 +25,7 @@ void orc_encoder_layer(const float*, float*, int, int, int, int, int, int, int, 
                        const float*, const float*, const float*, const float*, const float*,
                        const float*, int, int, const float*, const int*, int);
 int orc_dense_to_tile(const float*, int, int, int*, int*, float*);
+int orc_dense_to_1x16(const float*, int, int, int*, int*, float*);
 }
 
 static int g_failures = 0;
@@ -364,6 +365,97 @@ static void test_errors() {
     CHECK(device_error() == 0, "device error");
 }
 
+
+// The paper's BERT-large configuration through Encoder<config>: Q | K | V and O projections
+// pruned to 1x16 vectors (90 %), FFN hidden units pruned by half (row-pruned first Linear,
+// column-pruned second Linear over the same units), padding mask with per-sequence lengths,
+// batch 8, seq 384.  The oracle evaluates the dense equivalents (pruned entries zero).
+static void test_encoder_bert_large_mixed_formats() {
+    const int batch = 8, seq = 384, hidden = 1024, nhead = 16, ff = 4096, T = batch * seq;
+    auto model = std::make_shared<Model_t>(Model_t{hidden, hidden, seq, nhead, ff, hidden, 1, batch, ET_MASK_PADDING});
+    LayerW w;
+    auto prune_vectors = [](std::vector<float>& m, int out, int in, float sparsity, uint64_t seed) {
+        const int nvec = out * (in / 16);
+        for (int id : et_host::sample_ids(nvec, (int)(nvec * sparsity), seed)) {
+            float* v = m.data() + (size_t)(id / (in / 16)) * in + (size_t)(id % (in / 16)) * 16;
+            for (int c = 0; c < 16; ++c) v[c] = 0.f;
+        }
+    };
+    auto make_1x16 = [](const std::vector<float>& m, int out, int in) {
+        const int n = orc_dense_to_1x16(m.data(), out, in, nullptr, nullptr, nullptr);
+        std::vector<int> tidx((size_t)(out / 16) * (in / 16 + 1)), ridx(n);
+        std::vector<float> data((size_t)n * 16);
+        orc_dense_to_1x16(m.data(), out, in, tidx.data(), ridx.data(), data.data());
+        CHECK(et_validate_1x16(tidx.data(), ridx.data(), n, in, out) == ET_OK, "1x16 validator");
+        return mat1x16(out, in, tidx, ridx, to_half(data));
+    };
+    w.wqkv = nvec((size_t)3 * hidden * hidden, 0.02f);
+    w.wo = nvec((size_t)hidden * hidden, 0.02f);
+    w.w1 = nvec((size_t)ff * hidden, 0.02f);
+    w.w2 = nvec((size_t)hidden * ff, 0.02f);
+    prune_vectors(w.wqkv, 3 * hidden, hidden, 0.9f, 11);
+    prune_vectors(w.wo, hidden, hidden, 0.9f, 12);
+    std::vector<int> kept = et_host::sample_ids(ff, ff / 2, 13);  // surviving hidden units of the FFN
+    std::sort(kept.begin(), kept.end());
+    std::vector<char> alive(ff, 0);
+    for (int u : kept) alive[u] = 1;
+    std::vector<float> rows((size_t)kept.size() * hidden), cols((size_t)hidden * kept.size());
+    for (int u = 0; u < ff; ++u)
+        if (!alive[u]) {
+            for (int c = 0; c < hidden; ++c) w.w1[(size_t)u * hidden + c] = 0.f;
+            for (int o = 0; o < hidden; ++o) w.w2[(size_t)o * ff + u] = 0.f;
+        }
+    for (size_t k = 0; k < kept.size(); ++k) {
+        for (int c = 0; c < hidden; ++c) rows[k * hidden + c] = w.w1[(size_t)kept[k] * hidden + c];
+        for (int o = 0; o < hidden; ++o) cols[(size_t)o * kept.size() + k] = w.w2[(size_t)o * ff + kept[k]];
+    }
+    w.bqkv = nvec(3 * hidden, 0.02f);
+    w.bo = nvec(hidden, 0.02f);
+    w.b1 = nvec(ff, 0.02f);
+    w.b2 = nvec(hidden, 0.02f);
+    w.g1 = nvec(hidden, 0.1f);
+    w.g2 = nvec(hidden, 0.1f);
+    for (auto& g : w.g1) g = __half2float(__float2half_rn(g + 1.f));
+    for (auto& g : w.g2) g = __half2float(__float2half_rn(g + 1.f));
+    w.be1 = nvec(hidden, 0.1f);
+    w.be2 = nvec(hidden, 0.1f);
+    auto x = nvec((size_t)T * hidden, 1.0f);
+    std::vector<int> vl(batch);
+    for (int b = 0; b < batch; ++b) vl[b] = 128 + (int)(et_host::splitmix64(g_rng) % 257);
+
+    using attn_cfg = Attention_config<mat1x16, mat1x16, mat1x16, mat1x16, OTF_attn_full, true, false>;
+    using enc_cfg = Encoder_config<attn_cfg, row_mat, col_mat, GELU_OP>;
+    auto hb = [&](const std::vector<float>& b) { return to_half(b); };
+    auto lqkv = std::make_unique<Linear<mat1x16>>(hidden, 3 * hidden, make_1x16(w.wqkv, 3 * hidden, hidden), hb(w.bqkv).data(), T);
+    auto lo = std::make_unique<Linear<mat1x16>>(hidden, hidden, make_1x16(w.wo, hidden, hidden), hb(w.bo).data(), T);
+    culib::CUDA_ptr<int> ids(kept);
+    auto l1 = std::make_unique<Linear<row_mat>>(hidden, ff, row_mat(ids, culib::CUDA_ptr<half>(to_half(rows)), ff, hidden), hb(w.b1).data(), T);
+    auto l2 = std::make_unique<Linear<col_mat>>(ff, hidden, col_mat(ids, culib::CUDA_ptr<half>(to_half(cols)), hidden, ff, (int)kept.size()), hb(w.b2).data(), T);
+    auto attn = std::make_unique<Attention<attn_cfg>>(std::move(lqkv), std::move(lo), model);
+    culib::CUDA_ptr<int> dvl(vl);
+    attn->set_valid_len(dvl.get());
+    auto ln1 = std::make_unique<SkipLayerNorm>(hb(w.g1).data(), hb(w.be1).data(), hidden);
+    auto ln2 = std::make_unique<SkipLayerNorm>(hb(w.g2).data(), hb(w.be2).data(), hidden);
+    Encoder<enc_cfg> enc(std::move(attn), std::move(ln1), std::move(ln2), std::move(l1), std::move(l2), model);
+    culib::CUDA_ptr<half> dx(to_half(x)), dout((size_t)T * hidden);
+    enc.forward(dout.get(), dx.get());
+    CHECK(device_error() == 0, "device error");
+    std::vector<float> ref((size_t)T * hidden);
+    orc_encoder_layer(x.data(), ref.data(), batch, seq, hidden, nhead, hidden, hidden, ff, w.wqkv.data(),
+                      w.bqkv.data(), w.wo.data(), w.bo.data(), w.w1.data(), w.b1.data(), w.w2.data(),
+                      w.b2.data(), w.g1.data(), w.be1.data(), w.g2.data(), w.be2.data(), 2, ET_MASK_PADDING,
+                      nullptr, vl.data(), 0);
+    // padded query rows are computed but carry no meaning: compare the valid rows
+    std::vector<float> got = to_float(dout), g2, r2;
+    for (int b = 0; b < batch; ++b)
+        for (int t = 0; t < vl[b]; ++t)
+            for (int c = 0; c < hidden; ++c) {
+                g2.push_back(got[((size_t)b * seq + t) * hidden + c]);
+                r2.push_back(ref[((size_t)b * seq + t) * hidden + c]);
+            }
+    compare(g2, r2, "Encoder<1x16 | row | col> BERT-large b8 s384 padding");
+}
+
 int main() {
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
@@ -386,6 +478,7 @@ int main() {
         test_encoder_dense(3, 100, 0);
         test_attention_variants();
         test_attention_fused_qkv_dense();
+        test_encoder_bert_large_mixed_formats();
         test_errors();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());

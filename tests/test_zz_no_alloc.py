@@ -32,13 +32,39 @@ def test_noalloc_matches_regular_entry_point_twice(et, cuda):
         x, cid, cols, b, act = _case(et, cuda, seed, T, inn, out, sparsity, act)
         ref = et.linear_col(x, cid, cols, b, act)
         y = torch.full((T, out), float("nan"), dtype=torch.float16, device=cuda)
+        et.linear_col_noalloc(x, cid, cols, y, b, act)  # warm call: first use of the device
+        torch.cuda.synchronize()
+        y.fill_(float("nan"))
+        torch.cuda.synchronize()
+        # the driver's own count of free device memory sees an allocation by ANY route
+        # (torch's allocator counter would only see torch's)
+        free_before = torch.cuda.mem_get_info()[0]
         before = torch.cuda.memory_allocated()
         et.linear_col_noalloc(x, cid, cols, y, b, act)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert et.device_error() == 0
         # same kernels, same operands: the tolerance of the other GPU tests is met with 0 error
         assert torch.equal(y, ref)
+
+
+def test_noalloc_accepts_exactly_the_builtin_scratch(et, cuda):
+    """T * nn_col = 4 194 304 values fills the built-in scratch to the last element."""
+    import torch
+    T, inn, out = 2048, 2304, 128
+    x = _dev(et.synth.normal_fast(903, 1, (T, inn), 1.0), cuda)
+    w = et.synth.normal_fast(903, 2, (out, inn), 0.05)
+    ids = et.synth.choose_ids(903, 4, inn, 1.0 - 2048 / 2304)
+    assert len(ids) == 2048
+    cid, cols = et.synth.dense_to_col(w, ids)
+    cid, cols = _dev(cid, cuda), _dev(cols, cuda)
+    ref = et.linear_col(x, cid, cols, None, 0)
+    y = torch.full((T, out), float("nan"), dtype=torch.float16, device=cuda)
+    et.linear_col_noalloc(x, cid, cols, y, None, 0)
+    torch.cuda.synchronize()
+    assert et.device_error() == 0
+    assert torch.equal(y, ref)
 
 
 def test_noalloc_rejects_problems_beyond_the_builtin_scratch(et, cuda):
