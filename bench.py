@@ -39,9 +39,8 @@ WORKLOAD = ("BERT-base 12L h768 12 heads FFN3072 GELU, batch 16 per GPU, seq 128
 HIDDEN, NHEAD, FF, LAYERS, SEQ, BATCH = 768, 12, 3072, 12, 128, 16
 LONG_BATCH, LONG_SEQ = 2, 4096  # secondary per-kernel entry: attention on long sequences
 SEED = 2021
-# The four kernels of one layer at this batch: DRAM bytes (read + write) of one launch, from an
-# ncu capture of one layer (cold operands; results stay in L2), and the operands read / written
-# once (fp16).
+# The four kernels of one layer at this batch: measured DRAM bytes of one launch ("traffic") and
+# the operands read / written once in fp16 ("algorithmic_bytes").
 _T = BATCH * SEQ
 STACK_KERNELS = {
     "qkv_attention_fused": {

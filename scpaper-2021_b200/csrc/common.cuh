@@ -265,6 +265,24 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
         : "memory");
 }
 
+// ---- warp-level tensor path (mma.sync) ------------------------------------------------
+
+// D (16 x 8, fp32) += A (16 x 16 fp16, row-major fragment) * B (16 x 8 fp16, column-major fragment).
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
 // ---- TMEM ---------------------------------------------------------------------------
 
 // Warp-collective.  ncols: power of two, 32..512.  The base address lands in *smem_slot.

@@ -463,18 +463,34 @@ __global__ void fill_bias_kernel(__half* __restrict__ Y, const __half* __restric
     }
 }
 
-// G[t, k] = X[t, col_id[k]]: the kept input features of a column-pruned Linear.
+// G[t, k] = X[t, col_id[k]]: the kept input features of a column-pruned Linear.  A thread owns
+// eight consecutive kept columns (their indices stay in registers) and walks rows: eight
+// independent 2-byte loads and one 16-byte store per row.  blockDim = (gx, gy): gx threads
+// across the column groups, gy rows per CTA and pass.  nn_col % 8 == 0.
 __global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __restrict__ col_id,
                                    __half* __restrict__ G, int T, int in, int nn_col) {
-    pdl_wait();
+    const int ngroup = nn_col >> 3;
+    const unsigned short* Xs = reinterpret_cast<const unsigned short*>(X);
     pdl_launch_dependents();
-    const size_t total = static_cast<size_t>(T) * nn_col;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t t = i / nn_col;
-        const int k = static_cast<int>(i - t * nn_col);
-        G[i] = __ldcg(X + t * in + __ldg(col_id + k));
+    for (int j = threadIdx.x; j < ngroup; j += blockDim.x) {
+        int id[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) id[k] = __ldg(col_id + 8 * j + k);  // weights: before the wait
+        pdl_wait();  // (returns at once after the first time)
+        for (int t = blockIdx.x * blockDim.y + threadIdx.y; t < T; t += gridDim.x * blockDim.y) {
+            const unsigned short* xr = Xs + static_cast<size_t>(t) * in;
+            unsigned short h[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) h[k] = __ldcg(xr + id[k]);
+            uint4 o;
+            o.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
+            o.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
+            o.z = h[4] | (static_cast<uint32_t>(h[5]) << 16);
+            o.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
+            *reinterpret_cast<uint4*>(G + static_cast<size_t>(t) * nn_col + 8 * j) = o;
+        }
     }
+    pdl_wait();  // no CTA retires before the kernels it depends on have completed
 }
 
 int g_max_ctas = 0;  // test hook: cap on the persistent grid (0 = one CTA per SM)
@@ -877,12 +893,18 @@ int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
         return ET_ERR_WORKSPACE;
     if (!et::aligned16(scratch)) return ET_ERR_ALIGNMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const size_t total = static_cast<size_t>(T) * nn_col;
-    const int blocks = static_cast<int>((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
-    if (et::launch_kernel(et::gather_cols_kernel, dim3(blocks), dim3(256), 0, s,
-                          reinterpret_cast<const __half*>(X), col_id,
-                          reinterpret_cast<__half*>(scratch), T, in, nn_col) != cudaSuccess)
-        return ET_ERR_CUDA;
+    {
+        const int ngroup = nn_col / 8;
+        const int gx = ngroup >= 256 ? 256 : ((ngroup + 31) / 32) * 32;
+        const int gy = 256 / gx;
+        const int sms = et::sm_count() > 0 ? et::sm_count() : 148;
+        const int want = (T + gy - 1) / gy;
+        const int blocks = want < 8 * sms ? want : 8 * sms;
+        if (et::launch_kernel(et::gather_cols_kernel, dim3(blocks), dim3(gx, gy), 0, s,
+                              reinterpret_cast<const __half*>(X), col_id,
+                              reinterpret_cast<__half*>(scratch), T, in, nn_col) != cudaSuccess)
+            return ET_ERR_CUDA;
+    }
     return launch_gemm_f16(reinterpret_cast<const __half*>(scratch), nn_col,
                            reinterpret_cast<const __half*>(cols), nn_col,
                            reinterpret_cast<const __half*>(bias), reinterpret_cast<__half*>(Y),

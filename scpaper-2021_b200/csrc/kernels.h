@@ -62,11 +62,20 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
 // The packed tile-CSR Linear as a persistent kernel (one CTA per SM walks work items of 128
 // tokens x 256 output features, two items' accumulators in tensor memory); see
 // linear_tile_persist.cu.  nnz_tiles > 0.
-bool tile_persist_enabled();
+// Which kernel serves packed weights: 0 = one item per CTA, 1 = persistent, -1 = by shape
+// (the default: persistent while one item per CTA would not fill the SMs).
+int tile_packed_mode();
 int launch_linear_tile_persist(const int* row_ptr, const uint32_t* pk_mask, const int* pk_off,
                                const __half* pk_tiles, int nnz_tiles, const __half* bias,
                                const __half* X, __half* Y, int T, int in, int out, int act,
                                cudaStream_t stream);
+
+// The tile-CSR Linear straight from the format's arrays on the warp-level tensor path (every warp
+// walks its block rows' tiles); see linear_tile_rows.cu.  Needs in % 64 == 0; nnz_tiles > 0.
+bool linear_tile_rows_supported(int in, int out);
+int launch_linear_tile_rows(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
+                            const __half* bias, const __half* X, __half* Y, int T, int in, int out,
+                            int act, cudaStream_t stream);
 
 // Fused attention (see attention.cu).  Vc_col_id / head_ptr are null for an uncompressed V.
 int launch_attention(const __half* Q, const __half* K, const __half* V, __half* Z, int batch,

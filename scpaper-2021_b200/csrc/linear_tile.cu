@@ -560,9 +560,14 @@ int launch_tile_common(bool packed, const int* row_ptr, const int* row_off, cons
 }
 }  // namespace
 
+int g_tile_rows = 0;  // test hook: 1 = tile-CSR arrays run on the warp-level kernel (linear_tile_rows.cu)
+
 int launch_linear_tile(const int* row_ptr, const int* row_off, const __half* tiles, int nnz_tiles,
                        const __half* bias, const __half* X, __half* Y, int T, int in, int out,
                        int act, cudaStream_t stream) {
+    if (g_tile_rows != 0 && nnz_tiles > 0 && linear_tile_rows_supported(in, out))
+        return launch_linear_tile_rows(row_ptr, row_off, tiles, nnz_tiles, bias, X, Y, T, in, out, act,
+                                       stream);
     return launch_tile_common(false, row_ptr, row_off, nullptr, nullptr, tiles, nnz_tiles, bias, X, Y,
                               T, in, out, act, stream);
 }
@@ -571,9 +576,20 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
                               const __half* pk_tiles, int nnz_tiles, const __half* bias,
                               const __half* X, __half* Y, int T, int in, int out, int act,
                               cudaStream_t stream) {
-    if (nnz_tiles > 0 && tile_persist_enabled())
-        return launch_linear_tile_persist(row_ptr, pk_mask, pk_off, pk_tiles, nnz_tiles, bias, X, Y, T,
-                                          in, out, act, stream);
+    if (nnz_tiles > 0) {
+        // Measured on B200 (768 / 3072-wide BERT shapes, 2048 and 8192 tokens, 80-95 % of the
+        // tiles pruned): one item per CTA wins once its grid of (two panels x 128 tokens) items
+        // covers every SM; below that the persistent kernel's overlapped epilogue wins.
+        int mode = tile_packed_mode();
+        if (mode < 0) {
+            const int sms = sm_count() > 0 ? sm_count() : 148;
+            const long items = static_cast<long>(((out + TBN - 1) / TBN + 1) / 2) * ((T + TBM - 1) / TBM);
+            mode = items >= sms ? 0 : 1;
+        }
+        if (mode == 1)
+            return launch_linear_tile_persist(row_ptr, pk_mask, pk_off, pk_tiles, nnz_tiles, bias, X, Y, T,
+                                              in, out, act, stream);
+    }
     return launch_tile_common(true, row_ptr, nullptr, pk_mask, pk_off, pk_tiles, nnz_tiles, bias, X, Y,
                               T, in, out, act, stream);
 }
@@ -585,6 +601,8 @@ extern "C" {
 #ifdef ET_TEST_HOOKS
 // Test hook: -1 = automatic, 0 = one panel per CTA, 1 = two panels per CTA (packed weights).
 void et_debug_set_tile_wide(int mode) { et::g_tile_wide = mode; }
+// Test hook: 1 = tile-CSR arrays run on the warp-level kernel, 0 = on the tcgen05 one (default).
+void et_debug_set_tile_rows(int on) { et::g_tile_rows = on; }
 #endif  // ET_TEST_HOOKS
 
 int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_half* tiles,

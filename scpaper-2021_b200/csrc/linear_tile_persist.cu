@@ -475,9 +475,9 @@ linear_tile_persist_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
 
 }  // namespace
 
-int g_tile_persist = 1;  // test hook: 0 = the one-item-per-CTA kernel for packed weights too
+int g_tile_packed_mode = -1;  // test hook, see tile_packed_mode()
 
-bool tile_persist_enabled() { return g_tile_persist != 0; }
+int tile_packed_mode() { return g_tile_packed_mode; }
 
 int launch_linear_tile_persist(const int* row_ptr, const uint32_t* pk_mask, const int* pk_off,
                                const __half* pk_tiles, int nnz_tiles, const __half* bias,
@@ -534,7 +534,8 @@ int launch_linear_tile_persist(const int* row_ptr, const uint32_t* pk_mask, cons
 
 #ifdef ET_TEST_HOOKS
 extern "C" {
-// Test hook: 1 = persistent kernel for packed weights (default), 0 = one item per CTA.
-void et_debug_set_tile_persist(int on) { et::g_tile_persist = on; }
+// Test hook: kernel for packed weights: 0 = one item per CTA, 1 = persistent, -1 = by shape
+// (default).
+void et_debug_set_tile_persist(int mode) { et::g_tile_packed_mode = mode; }
 }
 #endif

@@ -65,21 +65,6 @@ tc_probe_kernel(int M, int N, int nacc, int count, int a_step, long long* cycles
 }
 
 // ---- mma.sync: multiply-accumulates per clock per SM -------------------------------------
-__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
-                                             uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-        "{%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-
 // Every warp runs `iters` rounds of 16 products against 16 independent accumulators (one
 // 16 x 16 weight tile applied to 128 tokens).  MODE 0: both operands stay in registers.
 // MODE 1: the token operand of every product comes from shared memory through ldmatrix

@@ -139,14 +139,31 @@ def test_tile(et, orc, cuda, T, inn, out, act, sparsity):
     if len(ro):
         pk = et.PackedTiles(rp, ro, tiles, inn, out, cuda)
         import torch
-        for wide in (0, 1):  # one / two panels of 128 outputs per CTA
-            et.lib().et_debug_set_tile_wide(ctypes.c_int(wide))
+        L = et.lib()
+        # the packed-weight kernels (one item per CTA with one / two panels of 128 outputs, the
+        # persistent form, the choice by shape) accumulate like the tile-CSR forward: same
+        # result bit for bit
+        for mode, wide in ((0, 0), (0, 1), (1, -1), (-1, -1)):
+            L.et_debug_set_tile_persist(ctypes.c_int(mode))
+            L.et_debug_set_tile_wide(ctypes.c_int(wide))
             try:
                 yp = et.linear_tile_packed(_dev(x, cuda), pk, _dev(b, cuda), act)
                 assert et.device_error() == 0
             finally:
-                et.lib().et_debug_set_tile_wide(ctypes.c_int(-1))
-            assert torch.equal(yp, y), f"packed (wide={wide}) and tile-CSR forward differ"
+                L.et_debug_set_tile_wide(ctypes.c_int(-1))
+                L.et_debug_set_tile_persist(ctypes.c_int(-1))
+            assert torch.equal(yp, y), f"packed (mode={mode}, wide={wide}) and tile-CSR forward differ"
+        # the warp-level kernel (mma.sync, every warp walking its block row's tiles) sums in
+        # another order
+        if inn % 64 == 0:
+            L.et_debug_set_tile_rows(ctypes.c_int(1))
+            try:
+                yr = et.linear_tile(_dev(x, cuda), _dev(rp, cuda), _dev(ro, cuda), _dev(tiles, cuda), out,
+                                    _dev(b, cuda), act)
+                assert et.device_error() == 0
+            finally:
+                L.et_debug_set_tile_rows(ctypes.c_int(0))
+            assert_close(_host(yr), ref, f"tile (warp-level) {T}x{inn}x{out} s={sparsity}")
         assert np.array_equal(np.sort(pk.perm_host), np.arange(len(ro)))
         packed = pk.tiles.cpu().numpy().reshape(-1, 16, 2, 8)
         unsw = packed.copy()
