@@ -250,10 +250,11 @@ def main():
     ap.add_argument("--tile-only", action="store_true",
                     help="launch the tile-pruned Linear alone (2048 x 768 -> 3072, 80 %% of the "
                          "tiles pruned, three times) and exit: the small case profilers capture")
-    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "layer"],
+    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "tile_qkv", "layer"],
                     help="launch one more small case three times and exit (for profilers): fused V.O "
                          "attention, the CTA-pair GEMM at 8192^3, skip-LayerNorm, the 1x16 vector "
-                         "kernel, the column-pruned Linear (gather + GEMM), one dense encoder layer")
+                         "kernel, the column-pruned Linear (gather + GEMM), a tile-pruned Q/K/V projection "
+                         "(persistent tile kernel), one dense encoder layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
@@ -324,6 +325,11 @@ def main():
             ti, ri, da = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_1x16(W))
             x = rnd(1, (T, HIDDEN))
             fn = lambda: et.linear_1x16(x, ti, ri, da, FF)
+        elif args.only == "tile_qkv":  # 2048 x 768 -> 2304, 80 % of the tiles pruned (persistent kernel)
+            W = et.synth.prune_tiles(et.synth.normal_fast(1, 40, (3 * HIDDEN, HIDDEN), 0.02), 1, 41, 0.8)
+            pk = et.PackedTiles(*et.synth.dense_to_tile(W), HIDDEN, 3 * HIDDEN, dev)
+            x = rnd(1, (T, HIDDEN))
+            fn = lambda: et.linear_tile_packed(x, pk, None, et.ACT_NONE)
         elif args.only == "col":   # 8192 x 3072 -> 768, half of the input columns kept
             W = et.synth.normal_fast(1, 2, (HIDDEN, FF), 0.02)
             ids = et.synth.choose_ids(1, 3, FF, 0.5)

@@ -463,10 +463,53 @@ __global__ void fill_bias_kernel(__half* __restrict__ Y, const __half* __restric
     }
 }
 
-// G[t, k] = X[t, col_id[k]]: the kept input features of a column-pruned Linear.  A thread owns
-// eight consecutive kept columns (their indices stay in registers) and walks rows: eight
-// independent 2-byte loads and one 16-byte store per row.  blockDim = (gx, gy): gx threads
-// across the column groups, gy rows per CTA and pass.  nn_col % 8 == 0.
+// G[t, k] = X[t, col_id[k]]: the kept input features of a column-pruned Linear.
+// Row-staged form: a warp copies one row of X into a shared-memory line with coalesced 16-byte
+// loads (every byte of X crosses L2 -> SM once) and, while that copy is in flight, picks the kept
+// columns of the row before it from its second line, eight per lane and step, and stores them as
+// 16 bytes.  The column list sits in shared memory once per CTA.  blockDim = (32, warps); dynamic
+// shared memory = nn_col * 4 + warps * 2 * in * 2 bytes.  in % 8 == 0, nn_col % 8 == 0.
+__global__ void gather_cols_rows_kernel(const __half* __restrict__ X, const int* __restrict__ col_id,
+                                        __half* __restrict__ G, int T, int in, int nn_col) {
+    extern __shared__ uint4 gather_smem[];
+    const int lane = threadIdx.x, warp = threadIdx.y;
+    const int ngroup = nn_col >> 3, npiece = in >> 3;
+    int* ids = reinterpret_cast<int*>(gather_smem);
+    uint4* lines = gather_smem + ((nn_col + 3) >> 2) + static_cast<size_t>(warp) * 2 * npiece;
+    for (int i = warp * 32 + lane; i < nn_col; i += 32 * blockDim.y) ids[i] = __ldg(col_id + i);
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();
+    const int stride = gridDim.x * blockDim.y;
+    int t = blockIdx.x * blockDim.y + warp;
+    auto fetch = [&](int row, int buf) {  // 16-byte pieces of the row into registers' worth of copies
+        const uint4* xr = reinterpret_cast<const uint4*>(X + static_cast<size_t>(row) * in);
+        uint4* line = lines + buf * npiece;
+        for (int i = lane; i < npiece; i += 32) line[i] = __ldcg(xr + i);
+    };
+    int buf = 0;
+    if (t < T) fetch(t, 0);
+    for (; t < T; t += stride, buf ^= 1) {
+        __syncwarp();
+        if (t + stride < T) fetch(t + stride, buf ^ 1);
+        const unsigned short* line_h = reinterpret_cast<const unsigned short*>(lines + buf * npiece);
+        for (int j = lane; j < ngroup; j += 32) {
+            const int4 c0 = *reinterpret_cast<const int4*>(ids + 8 * j);
+            const int4 c1 = *reinterpret_cast<const int4*>(ids + 8 * j + 4);
+            uint4 o;
+            o.x = line_h[c0.x] | (static_cast<uint32_t>(line_h[c0.y]) << 16);
+            o.y = line_h[c0.z] | (static_cast<uint32_t>(line_h[c0.w]) << 16);
+            o.z = line_h[c1.x] | (static_cast<uint32_t>(line_h[c1.y]) << 16);
+            o.w = line_h[c1.z] | (static_cast<uint32_t>(line_h[c1.w]) << 16);
+            *reinterpret_cast<uint4*>(G + static_cast<size_t>(t) * nn_col + 8 * j) = o;
+        }
+    }
+}
+
+// Direct form for rows too long for a shared-memory line: a thread owns eight consecutive kept
+// columns (their indices stay in registers) and walks rows: eight independent 2-byte loads and
+// one 16-byte store per row.  blockDim = (gx, gy): gx threads across the column groups, gy rows
+// per CTA and pass.  nn_col % 8 == 0.
 __global__ void gather_cols_kernel(const __half* __restrict__ X, const int* __restrict__ col_id,
                                    __half* __restrict__ G, int T, int in, int nn_col) {
     const int ngroup = nn_col >> 3;
@@ -891,13 +934,26 @@ int et_linear_col_fwd(const int32_t* col_id, const et_half* cols, int nn_col,
     if (in % 16 || out % 16 || nn_col % 8) return ET_ERR_SHAPE;
     if (!scratch || scratch_bytes < static_cast<size_t>(T) * nn_col * sizeof(et_half))
         return ET_ERR_WORKSPACE;
-    if (!et::aligned16(scratch)) return ET_ERR_ALIGNMENT;
+    if (!et::aligned16(scratch) || !et::aligned16(X)) return ET_ERR_ALIGNMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    {
+    const int sms = et::sm_count() > 0 ? et::sm_count() : 148;
+    const size_t id_bytes = ((static_cast<size_t>(nn_col) + 3) / 4) * 16;
+    const size_t line_pair = static_cast<size_t>(in) * 4;  // two lines of a warp
+    if (id_bytes + 2 * line_pair <= 48 * 1024) {
+        // the column list and at least two warps' line pairs fit: two to eight warps per CTA,
+        // a grid of a few CTAs per SM whose warps walk rows
+        int warps = static_cast<int>((48 * 1024 - id_bytes) / line_pair);
+        warps = warps > 8 ? 8 : warps;
+        const int want = (T + warps - 1) / warps;
+        const int blocks = want < 4 * sms ? want : 4 * sms;
+        if (et::launch_kernel(et::gather_cols_rows_kernel, dim3(blocks), dim3(32, warps),
+                              id_bytes + warps * line_pair, s, reinterpret_cast<const __half*>(X), col_id,
+                              reinterpret_cast<__half*>(scratch), T, in, nn_col) != cudaSuccess)
+            return ET_ERR_CUDA;
+    } else {
         const int ngroup = nn_col / 8;
         const int gx = ngroup >= 256 ? 256 : ((ngroup + 31) / 32) * 32;
         const int gy = 256 / gx;
-        const int sms = et::sm_count() > 0 ? et::sm_count() : 148;
         const int want = (T + gy - 1) / gy;
         const int blocks = want < 8 * sms ? want : 8 * sms;
         if (et::launch_kernel(et::gather_cols_kernel, dim3(blocks), dim3(gx, gy), 0, s,

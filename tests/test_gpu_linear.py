@@ -204,9 +204,10 @@ def test_row(et, orc, cuda, sparsity):
     assert_close(_host(yc), orc.linear_row_compressed(x, rid, rows, b), "row compressed")
 
 
+@pytest.mark.parametrize("T,inn,out", [(260, 512, 256),      # a row of X fits a shared-memory line
+                                       (40, 16384, 64)])      # it does not: direct gather
 @pytest.mark.parametrize("sparsity", [0.0, 0.5, 0.9])
-def test_col(et, orc, cuda, sparsity):
-    T, inn, out = 260, 512, 256
+def test_col(et, orc, cuda, sparsity, T, inn, out):
     x, w, b = _case(et, 41, T, inn, out)
     col_id = et.synth.choose_ids(41, 5, inn, sparsity)
     cid, cols = et.synth.dense_to_col(w, col_id)
