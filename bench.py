@@ -731,15 +731,28 @@ def main():
                 stream.synchronize()
             t_layer = med(timed(lambda: hp.forward(xl, 1, 4096), 10, 3)) / 10
             t_local = med(timed(lambda: hp.forward(xl, 1, 4096, skip_allreduce=True), 10, 3)) / 10
+            # the same layer with the exchange done by the library's kernels over peer memory
+            ex = et.PeerExchange(job, 4096, HIDDEN)
+            job.barrier()
+            with torch.cuda.stream(stream):
+                hp.forward_peer(xl, 1, 4096, ex)
+                stream.synchronize()
+            t_peer = med(timed(lambda: hp.forward_peer(xl, 1, 4096, ex), 10, 3)) / 10
+            job.barrier()
             f_layer = flops_per_sequence(seq=4096, layers=1)
+            best = min(t_layer, t_peer)
             configs["c5_head_parallel_b1_s4096"] = {
                 "ranks": world, "work_units_per_rank": hp.units_per_rank,
-                "ms_per_layer": t_layer * 1e3,
-                "ms_per_layer_without_allreduce": t_local * 1e3,
-                "allreduce_share": max(0.0, 1.0 - t_local / t_layer),
-                "tflops_all_ranks": f_layer / t_layer * 1e-12,
-                "frac_of_burst_roofline": f_layer / t_layer * 1e-12 / (world * peaks["bf16_tflops"]),
-                "sequences_per_s_12_layers": 1.0 / (t_layer * LAYERS)}
+                "ms_per_layer_nccl_allreduce": t_layer * 1e3,
+                "ms_per_layer_peer_memory_exchange": t_peer * 1e3,
+                "ms_per_layer_without_exchange": t_local * 1e3,
+                "exchange_share_nccl": max(0.0, 1.0 - t_local / t_layer),
+                "exchange_share_peer_memory": max(0.0, 1.0 - t_local / t_peer),
+                "tflops_all_ranks": f_layer / best * 1e-12,
+                "frac_of_burst_roofline": f_layer / best * 1e-12 / (world * peaks["bf16_tflops"]),
+                "sequences_per_s_12_layers": 1.0 / (best * LAYERS),
+                "device_error": et.device_error()}
+            ex.close()
         line["configs"] = configs
 
         # ---- CPU baseline and parity of the benchmarked stack (rank 0, N = 1 only) ----

@@ -430,6 +430,45 @@ int et_encoder_after_attention_fwd(const et_encoder_layer_t* layer, const void* 
                                    int seq, void* workspace, size_t workspace_bytes,
                                    et_stream stream);
 
+/* out = LN2(FFN(y) + y): the feed-forward half of the layer on an LN1 output the caller already
+ * holds (the head-parallel exchange below leaves it in the rank's peer buffer). */
+int et_encoder_ffn_fwd(const et_encoder_layer_t* layer, const et_half* y, et_half* out, int batch,
+                       int seq, void* workspace, size_t workspace_bytes, et_stream stream);
+
+/* Head-parallel exchange over PEER MEMORY (instead of a library all-reduce): the ranks' partial
+ * attention outputs are summed, the residual added and LN1 applied by this library's own
+ * kernels writing through peer mappings (NVLink), one rank per GPU.  Every rank owns
+ * ceil(T / world) token rows.
+ *   et_peer_buffer_bytes / _create / _open / _close / _destroy: one exchange buffer per rank
+ *     (cudaMalloc + a 64-byte CUDA IPC handle the caller passes to the other ranks by its own
+ *     means; _open maps a peer's buffer and enables peer access).  Created zeroed.
+ *   peer_buffers[world]: every rank's buffer as seen from THIS rank (own pointer at [rank]).
+ *   epoch: a counter the caller raises by one per layer call, the same on every rank.
+ *   et_peer_buffer_partial      where this rank's partial [T, hidden] (fp16) must be written
+ *                               (pass it as `partial` to et_encoder_attention_units_fwd);
+ *   et_hp_signal_partial_fwd    tells every rank that this rank's partial is complete;
+ *   et_hp_reduce_layernorm_fwd  y[rows of this rank] = LN(sum over ranks of their partials' rows
+ *                               (pulled through the peer mappings) + bias + x) * gamma + beta,
+ *                               written into EVERY rank's y;
+ *   et_hp_wait_fwd              returns (on the stream) once every rank's rows of y have landed
+ *                               here; et_peer_buffer_y gives the rank's y [T, hidden].
+ * A rank calls the three in this order on one stream, then et_encoder_ffn_fwd on y.  Waits are
+ * bounded (about a second): when one runs out, et_device_error reports 501 and the layer's
+ * output is not valid.  hidden % 8 == 0, hidden <= 2048, world <= 16. */
+int et_peer_buffer_bytes(int world, int T, int hidden, size_t* bytes);
+int et_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);
+int et_peer_buffer_open(const unsigned char handle[64], void** ptr);
+int et_peer_buffer_close(void* ptr);
+int et_peer_buffer_destroy(void* ptr);
+int et_peer_buffer_y(void* own_buffer, int world, int T, int hidden, et_half** y);
+int et_peer_buffer_partial(void* own_buffer, et_half** partial);
+int et_hp_signal_partial_fwd(void* const* peer_buffers, int rank, int world, int T, int hidden, int epoch,
+                             et_stream stream);
+int et_hp_reduce_layernorm_fwd(void* const* peer_buffers, const et_half* x, const et_half* bias,
+                               const et_half* gamma, const et_half* beta, int rank, int world, int T,
+                               int hidden, int epoch, et_stream stream);
+int et_hp_wait_fwd(void* own_buffer, int world, int T, int hidden, int epoch, et_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

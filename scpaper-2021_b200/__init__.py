@@ -27,7 +27,9 @@ ABI_SYMBOLS = [
     "et_status_string", "et_version", "et_built_for_sm", "et_device_error", "et_launch_count",
     "et_linear_dense_fwd", "et_linear_skip_layernorm_fwd", "et_linear_skip_layernorm_pays", "et_linear_tile_fwd", "et_tile_pack_dims", "et_tile_pack_plan",
     "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_tile_prefer_dense", "et_tile_densify",
-    "et_linear_row_fwd",
+    "et_linear_row_fwd", "et_encoder_ffn_fwd", "et_peer_buffer_bytes", "et_peer_buffer_create",
+    "et_peer_buffer_open", "et_peer_buffer_close", "et_peer_buffer_destroy", "et_peer_buffer_y",
+    "et_peer_buffer_partial", "et_hp_signal_partial_fwd", "et_hp_reduce_layernorm_fwd", "et_hp_wait_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
     "et_linear_1x16_fwd", "et_1x16_prefer_dense", "et_1x16_densify",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
@@ -632,15 +634,20 @@ class HeadParallelLayer:
             self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=like.device)
         return self._ws
 
-    def partial_sum(self, x, batch: int, seq: int, mask_kind=MASK_NONE, mask=None, valid_len=None):
-        """This rank's share of the attention block: [T, hidden] (fp16 or fp32)."""
+    def partial_sum(self, x, batch: int, seq: int, mask_kind=MASK_NONE, mask=None, valid_len=None,
+                    out_ptr: int | None = None):
+        """This rank's share of the attention block: [T, hidden] (fp16 or fp32), as a new tensor
+        or written at the device address `out_ptr` (then nothing is returned)."""
         import torch
         d, uh, uf, n_units, bpu = self._plan(seq)
         ws = self._workspace(d, batch, seq, x)
-        partial = torch.empty((batch * seq, self.hidden),
-                              dtype=torch.float32 if self.f32 else torch.float16, device=x.device)
+        partial = None
+        if out_ptr is None:
+            partial = torch.empty((batch * seq, self.hidden),
+                                  dtype=torch.float32 if self.f32 else torch.float16, device=x.device)
         check(lib().et_encoder_attention_units_fwd(
-            ctypes.byref(d), _p(x), _p(partial), c_int(1 if self.f32 else 0), c_int(batch), c_int(seq),
+            ctypes.byref(d), _p(x), _p(partial) if out_ptr is None else c_void_p(out_ptr),
+            c_int(1 if self.f32 else 0), c_int(batch), c_int(seq),
             c_int(mask_kind), _p(mask), _p(valid_len), uh, uf, c_int(n_units), c_int(bpu),
             _p(ws), c_size_t(ws.numel()), _stream()), "et_encoder_attention_units_fwd")
         return partial
@@ -665,6 +672,124 @@ class HeadParallelLayer:
             import torch.distributed as dist
             dist.all_reduce(partial)  # the layer's one exchange step
         return self.finish(partial, x, batch, seq)
+
+    # ---- the same layer with the exchange done by this library's kernels over peer memory ----
+    def ffn(self, y_ptr: int, x, batch: int, seq: int):
+        d = self._plan(seq)[0]
+        ws = self._workspace(d, batch, seq, x)
+        out = _empty((batch * seq, self.hidden), x)
+        check(lib().et_encoder_ffn_fwd(ctypes.byref(self.full.desc), c_void_p(y_ptr), _p(out), c_int(batch),
+                                       c_int(seq), _p(ws), c_size_t(ws.numel()), _stream()),
+              "et_encoder_ffn_fwd")
+        return out
+
+    def forward_peer(self, x, batch: int, seq: int, exchange: "PeerExchange", mask_kind=MASK_NONE,
+                     mask=None, valid_len=None):
+        """forward() with the partial sums pulled by their owner ranks through peer mappings,
+        summed, normalised and gathered by peer stores (PeerExchange) instead of a library
+        all-reduce.  fp16 partials."""
+        if self.f32:
+            raise EtError("the peer exchange sums fp16 partials")
+        self.partial_sum(x, batch, seq, mask_kind, mask, valid_len, out_ptr=exchange.partial())
+        exchange.epoch += 1
+        exchange.signal()
+        d = self.full.desc  # (the output projection's bias is inside rank 0's partial)
+        exchange.reduce_layernorm(x, None, c_void_p(d.ln1_gamma), c_void_p(d.ln1_beta))
+        exchange.wait()
+        return self.ffn(exchange.y(), x, batch, seq)
+
+
+class PeerExchange:
+    """The ranks' exchange buffers for the head-parallel layer over peer memory: one buffer per
+    rank (et_peer_buffer_create), every other rank's buffer mapped through its CUDA IPC handle.
+    `handles` may be given by the caller; with a torch.distributed job they are all-gathered.
+    For a single-process emulation of several ranks on one GPU use PeerExchange.local()."""
+
+    def __init__(self, job, T: int, hidden: int):
+        import torch
+        import torch.distributed as dist
+        self.world, self.rank, self.T, self.hidden = job.world, job.rank, T, hidden
+        self.epoch = 0
+        nbytes = ctypes.c_size_t(0)
+        check(lib().et_peer_buffer_bytes(c_int(self.world), c_int(T), c_int(hidden), ctypes.byref(nbytes)),
+              "et_peer_buffer_bytes")
+        own, handle = c_void_p(None), (ctypes.c_ubyte * 64)()
+        check(lib().et_peer_buffer_create(nbytes, ctypes.byref(own), handle), "et_peer_buffer_create")
+        self.own = own.value
+        self._opened = []
+        ptrs = [None] * self.world
+        ptrs[self.rank] = self.own
+        if self.world > 1:
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=job.device)
+            every = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(every, mine)
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                h = (ctypes.c_ubyte * 64)(*every[r].cpu().tolist())
+                p = c_void_p(None)
+                check(lib().et_peer_buffer_open(h, ctypes.byref(p)), "et_peer_buffer_open")
+                ptrs[r] = p.value
+                self._opened.append(p.value)
+        self.ptrs = (c_void_p * self.world)(*ptrs)
+
+    @classmethod
+    def local(cls, world: int, T: int, hidden: int):
+        """`world` exchange objects in ONE process whose buffers all live on the current GPU
+        (tests: the ranks' kernels then run one after the other, phase by phase)."""
+        nbytes = ctypes.c_size_t(0)
+        check(lib().et_peer_buffer_bytes(c_int(world), c_int(T), c_int(hidden), ctypes.byref(nbytes)),
+              "et_peer_buffer_bytes")
+        bufs = []
+        for _ in range(world):
+            own, handle = c_void_p(None), (ctypes.c_ubyte * 64)()
+            check(lib().et_peer_buffer_create(nbytes, ctypes.byref(own), handle), "et_peer_buffer_create")
+            bufs.append(own.value)
+        out = []
+        for r in range(world):
+            ex = cls.__new__(cls)
+            ex.world, ex.rank, ex.T, ex.hidden, ex.epoch = world, r, T, hidden, 0
+            ex.own, ex._opened = bufs[r], []
+            ex.ptrs = (c_void_p * world)(*bufs)
+            out.append(ex)
+        return out
+
+    def y(self):
+        """This rank's copy of the LN1 output [T, hidden] as a torch view of the buffer."""
+        import torch
+        yp = c_void_p(None)
+        check(lib().et_peer_buffer_y(c_void_p(self.own), c_int(self.world), c_int(self.T), c_int(self.hidden),
+                                     ctypes.byref(yp)), "et_peer_buffer_y")
+        return yp.value
+
+    def partial(self):
+        """Device address of this rank's partial [T, hidden] fp16 inside its exchange buffer."""
+        return self.own
+
+    def signal(self):
+        check(lib().et_hp_signal_partial_fwd(self.ptrs, c_int(self.rank), c_int(self.world), c_int(self.T),
+                                             c_int(self.hidden), c_int(self.epoch), _stream()),
+              "et_hp_signal_partial_fwd")
+
+    def reduce_layernorm(self, x, bias, gamma, beta):
+        """bias / gamma / beta: device tensors or raw device addresses (c_void_p)."""
+        vp = lambda a: a if isinstance(a, c_void_p) else _p(a)
+        check(lib().et_hp_reduce_layernorm_fwd(self.ptrs, _p(x), vp(bias), vp(gamma), vp(beta),
+                                               c_int(self.rank), c_int(self.world), c_int(self.T),
+                                               c_int(self.hidden), c_int(self.epoch), _stream()),
+              "et_hp_reduce_layernorm_fwd")
+
+    def wait(self):
+        check(lib().et_hp_wait_fwd(c_void_p(self.own), c_int(self.world), c_int(self.T), c_int(self.hidden),
+                                   c_int(self.epoch), _stream()), "et_hp_wait_fwd")
+
+    def close(self):
+        for p in self._opened:
+            lib().et_peer_buffer_close(c_void_p(p))
+        self._opened = []
+        if self.own:
+            lib().et_peer_buffer_destroy(c_void_p(self.own))
+            self.own = None
 
 
 class EncoderStack:

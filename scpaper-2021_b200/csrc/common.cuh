@@ -59,6 +59,7 @@ enum : int {
     DEV_TIMEOUT_VO_PRODUCER = 401,
     DEV_TIMEOUT_VO_MMA = 402,
     DEV_TIMEOUT_VO_SOFTMAX = 403,
+    DEV_TIMEOUT_PEER = 501,  // a rank's flag did not arrive (head-parallel exchange over peer memory)
 };
 
 #if defined(__CUDACC__)

@@ -396,6 +396,21 @@ int et_encoder_after_attention_fwd(const et_encoder_layer_t* layer, const void* 
     return et::ffn_block(layer, b, T, reinterpret_cast<__half*>(out), s);
 }
 
+int et_encoder_ffn_fwd(const et_encoder_layer_t* layer, const et_half* y, et_half* out, int batch, int seq,
+                       void* workspace, size_t workspace_bytes, et_stream stream) {
+    int st = et::check_layer(layer);
+    if (st != ET_OK) return st;
+    if (!y || !out || batch <= 0 || seq <= 0) return ET_ERR_INVALID_ARG;
+    if (!workspace) return ET_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return ET_ERR_ALIGNMENT;
+    if (!et::aligned16(y)) return ET_ERR_ALIGNMENT;
+    et::LayerBuffers b = et::carve(layer, batch, seq, workspace);
+    if (workspace_bytes < b.total) return ET_ERR_WORKSPACE;
+    b.y = const_cast<__half*>(reinterpret_cast<const __half*>(y));  // read only
+    return et::ffn_block(layer, b, batch * seq, reinterpret_cast<__half*>(out),
+                         static_cast<cudaStream_t>(stream));
+}
+
 int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,
                             const et_half* mask, et_half* Z, const int32_t* o_row_ptr,
                             const int32_t* o_row_off, const et_half* o_tiles, int o_nnz,

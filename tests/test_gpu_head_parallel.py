@@ -52,7 +52,56 @@ def test_head_parallel_ranks_emulated_on_one_gpu(world, reduce_dtype, mask_kind)
     assert_close(y.float().cpu().numpy(), ref, f"head-parallel layer, {world} emulated ranks")
 
 
-def _worker(rank: int, world: int, port: int, out_q):
+@pytest.mark.parametrize("world,seq", [(8, 1024), (3, 1000)])
+def test_peer_exchange_ranks_emulated_on_one_gpu(world, seq):
+    """The exchange over peer memory (signal -> reduce + LayerNorm + gather -> wait) with every
+    rank's buffer on ONE GPU: all ranks' partials and signals run first, then all reductions, then the waits,
+    so no kernel ever waits for a later one.  Every rank must end up with the same y and the
+    same layer output as the all-reduce form; two layers in a row exercise buffer reuse."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from conftest import assert_close
+    et = entry.load_package()
+    orc = entry.load_oracle()
+    orc.build()
+    dev = torch.device("cuda:0")
+    hidden, nhead, ff = 768, 12, 3072
+    w = et.synth.encoder_layer_weights(43, 0, hidden, ff, std=0.03, bias_std=0.02, ln_noise=0.1)
+    x = et.synth.normal(43, 3, (seq, hidden), 1.0)
+    layers = [et.HeadParallelLayer(w, nhead, et.sharding.Job(rank=r, world=world, device=dev),
+                                   et.ACT_GELU, device=dev) for r in range(world)]
+    exs = et.PeerExchange.local(world, seq, hidden)
+    d = layers[0].full.desc
+    import ctypes
+    g, b = ctypes.c_void_p(d.ln1_gamma), ctypes.c_void_p(d.ln1_beta)
+    cur = x
+    try:
+        for _ in range(2):
+            xd = torch.from_numpy(np.ascontiguousarray(cur)).to(dev)
+            for r in range(world):
+                layers[r].partial_sum(xd, 1, seq, out_ptr=exs[r].partial())
+                exs[r].epoch += 1
+                exs[r].signal()
+            for r in range(world):
+                exs[r].reduce_layernorm(xd, None, g, b)
+            outs = []
+            for r in range(world):
+                exs[r].wait()
+                outs.append(layers[r].ffn(exs[r].y(), xd, 1, seq))
+            torch.cuda.synchronize()
+            assert et.device_error() == 0
+            for r in range(1, world):
+                assert torch.equal(outs[r], outs[0]), f"rank {r} differs from rank 0"
+            ref = orc.encoder_layer(cur, w, 1, seq, nhead, 2, 0)
+            assert_close(outs[0].float().cpu().numpy(), ref, f"peer exchange, {world} emulated ranks")
+            cur = outs[0].cpu().numpy()
+    finally:
+        for ex in exs:
+            ex.close()
+
+
+def _worker(rank: int, world: int, port: int, out_q, peer: bool = False):
     try:
         import torch
         import torch.distributed as dist
@@ -67,9 +116,19 @@ def _worker(rank: int, world: int, port: int, out_q):
         x = et.synth.normal(41, 3, (seq, hidden), 1.0)
         job = et.sharding.Job(rank=rank, world=world, device=dev)
         layer = et.HeadParallelLayer(w, nhead, job, et.ACT_GELU, device=dev)
-        y = layer.forward(torch.from_numpy(x).to(dev), 1, seq)
+        xd = torch.from_numpy(x).to(dev)
+        if peer:
+            ex = et.PeerExchange(job, seq, hidden)
+            dist.barrier()
+            y = layer.forward_peer(xd, 1, seq, ex)
+            y = layer.forward_peer(y, 1, seq, ex)  # a second layer call reuses the buffers
+        else:
+            y = layer.forward(xd, 1, seq)
         torch.cuda.synchronize()
         err = et.device_error()
+        if peer:
+            dist.barrier()
+            ex.close()
         if rank == 0:
             out_q.put(("ok", y.float().cpu().numpy(), err))
         dist.barrier()
@@ -79,7 +138,10 @@ def _worker(rank: int, world: int, port: int, out_q):
         raise
 
 
-def test_head_parallel_layer_two_gpus():
+@pytest.mark.parametrize("peer", [False, True])
+def test_head_parallel_layer_two_gpus(peer):
+    """peer=False: one NCCL all-reduce per layer; peer=True: the exchange by this library's
+    kernels over peer memory (CUDA IPC mappings), two layer calls in a row."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -90,7 +152,7 @@ def test_head_parallel_layer_two_gpus():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     world, port = 2, _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, peer)) for r in range(world)]
     for p in procs:
         p.start()
     kind, y, err = q.get(timeout=300)
@@ -103,5 +165,8 @@ def test_head_parallel_layer_two_gpus():
     w = et.synth.encoder_layer_weights(41, 0, hidden, ff, std=0.03, bias_std=0.02, ln_noise=0.1)
     x = et.synth.normal(41, 3, (seq, hidden), 1.0)
     ref = orc.encoder_layer(x, w, 1, seq, nhead, 2, 0)
+    if peer:
+        ref = orc.encoder_layer(np.asarray(ref, dtype=np.float32).astype(np.float16).astype(np.float32), w,
+                                1, seq, nhead, 2, 0)
     from conftest import assert_close
-    assert_close(y, ref, "head-parallel layer on 2 GPUs")
+    assert_close(y, ref, "head-parallel layer on 2 GPUs" + (" over peer memory" if peer else ""))
