@@ -254,7 +254,8 @@ def main():
                     help="launch one more small case three times and exit (for profilers): fused V.O "
                          "attention, the CTA-pair GEMM at 8192^3, skip-LayerNorm, the 1x16 vector "
                          "kernel, the column-pruned Linear (gather + GEMM), a tile-pruned Q/K/V projection "
-                         "(persistent tile kernel), one dense encoder layer")
+                         "(on the persistent tile kernel when ET_B200_TEST_HOOKS=1 selects the hooks "
+                         "library), one dense encoder layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
@@ -325,7 +326,10 @@ def main():
             ti, ri, da = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_1x16(W))
             x = rnd(1, (T, HIDDEN))
             fn = lambda: et.linear_1x16(x, ti, ri, da, FF)
-        elif args.only == "tile_qkv":  # 2048 x 768 -> 2304, 80 % of the tiles pruned (persistent kernel)
+        elif args.only == "tile_qkv":  # 2048 x 768 -> 2304, 80 % of the tiles pruned
+            # (with ET_B200_TEST_HOOKS=1 in the environment: on the persistent tile kernel)
+            if hasattr(et.lib(), "et_debug_set_tile_persist"):
+                et.lib().et_debug_set_tile_persist(1)
             W = et.synth.prune_tiles(et.synth.normal_fast(1, 40, (3 * HIDDEN, HIDDEN), 0.02), 1, 41, 0.8)
             pk = et.PackedTiles(*et.synth.dense_to_tile(W), HIDDEN, 3 * HIDDEN, dev)
             x = rnd(1, (T, HIDDEN))
@@ -732,27 +736,43 @@ def main():
             t_layer = med(timed(lambda: hp.forward(xl, 1, 4096), 10, 3)) / 10
             t_local = med(timed(lambda: hp.forward(xl, 1, 4096, skip_allreduce=True), 10, 3)) / 10
             # the same layer with the exchange done by the library's kernels over peer memory
-            ex = et.PeerExchange(job, 4096, HIDDEN)
-            job.barrier()
-            with torch.cuda.stream(stream):
-                hp.forward_peer(xl, 1, 4096, ex)
-                stream.synchronize()
-            t_peer = med(timed(lambda: hp.forward_peer(xl, 1, 4096, ex), 10, 3)) / 10
-            job.barrier()
+            # (collective set-up: fails on every rank or on none)
+            t_peer, t_sp, peer_note, ex = None, None, None, None
+            try:
+                ex = et.PeerExchange(job, 4096, HIDDEN)
+            except et.EtError as e:
+                peer_note = str(e)
+            if ex is not None:
+                job.barrier()
+                with torch.cuda.stream(stream):
+                    hp.forward_peer(xl, 1, 4096, ex)
+                    stream.synchronize()
+                t_peer = med(timed(lambda: hp.forward_peer(xl, 1, 4096, ex), 10, 3)) / 10
+                job.barrier()
+                # ... and with the feed-forward block on each rank's own token rows (reduce-scatter
+                # after the output projection, all-gather after the layer: one all-reduce's bytes)
+                with torch.cuda.stream(stream):
+                    hp.forward_peer_sharded(xl, 1, 4096, ex)
+                    stream.synchronize()
+                t_sp = med(timed(lambda: hp.forward_peer_sharded(xl, 1, 4096, ex), 10, 3)) / 10
+                job.barrier()
             f_layer = flops_per_sequence(seq=4096, layers=1)
-            best = min(t_layer, t_peer)
+            best = min(t for t in (t_layer, t_peer, t_sp) if t is not None)
             configs["c5_head_parallel_b1_s4096"] = {
                 "ranks": world, "work_units_per_rank": hp.units_per_rank,
                 "ms_per_layer_nccl_allreduce": t_layer * 1e3,
-                "ms_per_layer_peer_memory_exchange": t_peer * 1e3,
+                "ms_per_layer_peer_memory_exchange": None if t_peer is None else t_peer * 1e3,
+                "ms_per_layer_peer_memory_token_sharded_ffn": None if t_sp is None else t_sp * 1e3,
+                "peer_memory_exchange_note": peer_note,
                 "ms_per_layer_without_exchange": t_local * 1e3,
                 "exchange_share_nccl": max(0.0, 1.0 - t_local / t_layer),
-                "exchange_share_peer_memory": max(0.0, 1.0 - t_local / t_peer),
+                "exchange_share_peer_memory": None if t_peer is None else max(0.0, 1.0 - t_local / t_peer),
                 "tflops_all_ranks": f_layer / best * 1e-12,
                 "frac_of_burst_roofline": f_layer / best * 1e-12 / (world * peaks["bf16_tflops"]),
                 "sequences_per_s_12_layers": 1.0 / (best * LAYERS),
                 "device_error": et.device_error()}
-            ex.close()
+            if ex is not None:
+                ex.close()
         line["configs"] = configs
 
         # ---- CPU baseline and parity of the benchmarked stack (rank 0, N = 1 only) ----

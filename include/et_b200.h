@@ -115,10 +115,9 @@ int et_linear_tile_fwd(const int32_t* row_ptr, const int32_t* row_off, const et_
  *   et_tile_pack_dims   sizes of the mask / offset arrays (npanel * nchunk entries each);
  *   et_tile_pack_plan   HOST index arrays in, masks / offsets / permutation out (host);
  *   et_tile_pack_tiles  packed_tiles[i] = tiles[perm[i]] on the GPU (perm: device array);
- *   et_linear_tile_packed_fwd  the forward pass; row_ptr as in et_linear_tile_fwd.  It runs as
- *     a persistent kernel: one CTA per SM walks work items of 128 tokens x 256 output features
- *     and keeps two items' accumulators in tensor memory, so that one item's bias / activation
- *     / store overlaps the next item's products.
+ *   et_linear_tile_packed_fwd  the forward pass; row_ptr as in et_linear_tile_fwd.  One CTA per
+ *     work item of 128 tokens x one or two panels of 128 output features (two once such items
+ *     cover the SMs 1.25 times: the panels then share every activation slab).
  * Stands in for the same reference call as et_linear_tile_fwd (Linear/SPMM_tile.cu:312-324);
  * the reference keeps its tiles in file order. */
 int et_tile_pack_dims(int in, int out, int* npanel, int* nchunk);
@@ -446,10 +445,14 @@ int et_encoder_ffn_fwd(const et_encoder_layer_t* layer, const et_half* y, et_hal
  *   epoch: a counter the caller raises by one per layer call, the same on every rank.
  *   et_peer_buffer_partial      where this rank's partial [T, hidden] (fp16) must be written
  *                               (pass it as `partial` to et_encoder_attention_units_fwd);
- *   et_hp_signal_partial_fwd    tells every rank that this rank's partial is complete;
+ *   et_hp_signal_partial_fwd    tells every rank that this rank's partial is complete (not
+ *                               needed when et_hp_reduce_layernorm_fwd is called with
+ *                               publish_ready = 1, which does the same as its first step; the
+ *                               separate call exists for callers that run several ranks' kernels
+ *                               one after the other on one GPU);
  *   et_hp_reduce_layernorm_fwd  y[rows of this rank] = LN(sum over ranks of their partials' rows
  *                               (pulled through the peer mappings) + bias + x) * gamma + beta,
- *                               written into EVERY rank's y;
+ *                               written into EVERY rank's y (gather = 1);
  *   et_hp_wait_fwd              returns (on the stream) once every rank's rows of y have landed
  *                               here; et_peer_buffer_y gives the rank's y [T, hidden].
  * A rank calls the three in this order on one stream, then et_encoder_ffn_fwd on y.  Waits are
@@ -466,7 +469,15 @@ int et_hp_signal_partial_fwd(void* const* peer_buffers, int rank, int world, int
                              et_stream stream);
 int et_hp_reduce_layernorm_fwd(void* const* peer_buffers, const et_half* x, const et_half* bias,
                                const et_half* gamma, const et_half* beta, int rank, int world, int T,
-                               int hidden, int epoch, et_stream stream);
+                               int hidden, int epoch, int publish_ready, int gather, et_stream stream);
+/* Token-sharded form: with gather = 0 et_hp_reduce_layernorm_fwd keeps y local (only this rank's
+ * rows are valid); the rank runs et_encoder_ffn_fwd on those rows alone, writing into its rows
+ * of et_peer_buffer_out(own, ..., slot), and et_hp_allgather_rows_fwd stores them into every
+ * rank's out[slot]; after et_hp_wait_fwd out[slot] holds the whole layer output on every rank.
+ * The caller alternates slot = 0, 1 from layer to layer. */
+int et_peer_buffer_out(void* own_buffer, int world, int T, int hidden, int slot, et_half** out);
+int et_hp_allgather_rows_fwd(void* const* peer_buffers, int rank, int world, int T, int hidden, int epoch,
+                             int slot, et_stream stream);
 int et_hp_wait_fwd(void* own_buffer, int world, int T, int hidden, int epoch, et_stream stream);
 
 #ifdef __cplusplus

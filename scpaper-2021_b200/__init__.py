@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "et_tile_pack_tiles", "et_linear_tile_packed_fwd", "et_tile_prefer_dense", "et_tile_densify",
     "et_linear_row_fwd", "et_encoder_ffn_fwd", "et_peer_buffer_bytes", "et_peer_buffer_create",
     "et_peer_buffer_open", "et_peer_buffer_close", "et_peer_buffer_destroy", "et_peer_buffer_y",
-    "et_peer_buffer_partial", "et_hp_signal_partial_fwd", "et_hp_reduce_layernorm_fwd", "et_hp_wait_fwd",
+    "et_peer_buffer_partial", "et_hp_signal_partial_fwd", "et_hp_reduce_layernorm_fwd", "et_hp_wait_fwd", "et_peer_buffer_out", "et_hp_allgather_rows_fwd",
     "et_linear_row_compressed_fwd", "et_linear_col_fwd", "et_linear_col_noalloc_fwd",
     "et_linear_1x16_fwd", "et_1x16_prefer_dense", "et_1x16_densify",
     "et_linear_csr_fwd", "et_validate_tile_mat", "et_validate_id_list", "et_validate_1x16",
@@ -692,11 +692,62 @@ class HeadParallelLayer:
             raise EtError("the peer exchange sums fp16 partials")
         self.partial_sum(x, batch, seq, mask_kind, mask, valid_len, out_ptr=exchange.partial())
         exchange.epoch += 1
-        exchange.signal()
         d = self.full.desc  # (the output projection's bias is inside rank 0's partial)
-        exchange.reduce_layernorm(x, None, c_void_p(d.ln1_gamma), c_void_p(d.ln1_beta))
+        exchange.reduce_layernorm(x, None, c_void_p(d.ln1_gamma), c_void_p(d.ln1_beta), publish_ready=True)
         exchange.wait()
         return self.ffn(exchange.y(), x, batch, seq)
+
+    def forward_peer_sharded(self, x, batch: int, seq: int, exchange: "PeerExchange", mask_kind=MASK_NONE,
+                             mask=None, valid_len=None, phase: str = "all"):
+        """forward_peer() with the feed-forward block and the second LayerNorm run on THIS RANK'S
+        token rows only (they act on tokens independently) and the finished rows passed to every
+        rank: a reduce-scatter after the output projection and an all-gather after the layer, the
+        bytes of one all-reduce.  Returns the layer output as a view of the exchange buffer's
+        out[slot] (valid until the layer call after next).  batch must be 1.
+        phase (single-GPU emulation of several ranks): "partial" / "reduce" / "ffn" / "wait" run
+        one step each so that every rank's step can run before the next step of any rank."""
+        if self.f32:
+            raise EtError("the peer exchange sums fp16 partials")
+        if batch != 1:
+            raise EtError("the token-sharded form handles one sequence")
+        T = seq
+        if phase in ("all", "partial"):
+            self.partial_sum(x, batch, seq, mask_kind, mask, valid_len, out_ptr=exchange.partial())
+            exchange.epoch += 1
+            if phase == "partial":
+                exchange.signal()
+        d = self.full.desc
+        if phase in ("all", "reduce"):
+            exchange.reduce_layernorm(x, None, c_void_p(d.ln1_gamma), c_void_p(d.ln1_beta),
+                                      publish_ready=(phase == "all"), gather=False)
+        slot = exchange.epoch & 1
+        first, n = exchange.rows()
+        if phase in ("all", "ffn"):
+            if n > 0:
+                dl = self._plan(seq)[0]
+                ws = self._workspace(dl, batch, seq, x)
+                yp = exchange.y() + first * self.hidden * 2
+                op = exchange.out(slot) + first * self.hidden * 2
+                check(lib().et_encoder_ffn_fwd(ctypes.byref(self.full.desc), c_void_p(yp), c_void_p(op),
+                                               c_int(1), c_int(n), _p(ws), c_size_t(ws.numel()), _stream()),
+                      "et_encoder_ffn_fwd")
+            exchange.allgather_rows(slot)
+        if phase in ("all", "wait"):
+            exchange.wait()
+        return device_view(exchange.out(slot), (T, self.hidden), x.device)
+
+
+class _DeviceArray:
+    """A raw device address as a zero-copy torch tensor (torch.as_tensor on this object)."""
+
+    def __init__(self, ptr: int, shape, typestr: str = "<f2"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr,
+                                         "data": (int(ptr), False), "version": 2}
+
+
+def device_view(ptr: int, shape, device):
+    import torch
+    return torch.as_tensor(_DeviceArray(ptr, shape), device=device)
 
 
 class PeerExchange:
@@ -706,31 +757,51 @@ class PeerExchange:
     For a single-process emulation of several ranks on one GPU use PeerExchange.local()."""
 
     def __init__(self, job, T: int, hidden: int):
+        """Collective over the job's ranks.  Every rank takes part in both collective steps (the
+        all-gather of the handles, the agreement on success) whatever happens locally, so that a
+        failure on one rank (no peer access, IPC refused) raises EtError on ALL ranks instead of
+        leaving the others waiting."""
         import torch
         import torch.distributed as dist
         self.world, self.rank, self.T, self.hidden = job.world, job.rank, T, hidden
         self.epoch = 0
-        nbytes = ctypes.c_size_t(0)
-        check(lib().et_peer_buffer_bytes(c_int(self.world), c_int(T), c_int(hidden), ctypes.byref(nbytes)),
-              "et_peer_buffer_bytes")
-        own, handle = c_void_p(None), (ctypes.c_ubyte * 64)()
-        check(lib().et_peer_buffer_create(nbytes, ctypes.byref(own), handle), "et_peer_buffer_create")
-        self.own = own.value
-        self._opened = []
+        self.own, self._opened = None, []
+        failure = None
+        handle = (ctypes.c_ubyte * 64)()
+        try:
+            nbytes = ctypes.c_size_t(0)
+            check(lib().et_peer_buffer_bytes(c_int(self.world), c_int(T), c_int(hidden), ctypes.byref(nbytes)),
+                  "et_peer_buffer_bytes")
+            own = c_void_p(None)
+            check(lib().et_peer_buffer_create(nbytes, ctypes.byref(own), handle), "et_peer_buffer_create")
+            self.own = own.value
+        except Exception as e:  # noqa: BLE001 - reported after the collective steps
+            failure = e
         ptrs = [None] * self.world
         ptrs[self.rank] = self.own
         if self.world > 1:
             mine = torch.tensor(list(handle), dtype=torch.uint8, device=job.device)
             every = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(every, mine)
-            for r in range(self.world):
-                if r == self.rank:
-                    continue
-                h = (ctypes.c_ubyte * 64)(*every[r].cpu().tolist())
-                p = c_void_p(None)
-                check(lib().et_peer_buffer_open(h, ctypes.byref(p)), "et_peer_buffer_open")
-                ptrs[r] = p.value
-                self._opened.append(p.value)
+            if failure is None:
+                try:
+                    for r in range(self.world):
+                        if r == self.rank:
+                            continue
+                        h = (ctypes.c_ubyte * 64)(*every[r].cpu().tolist())
+                        p = c_void_p(None)
+                        check(lib().et_peer_buffer_open(h, ctypes.byref(p)), "et_peer_buffer_open")
+                        ptrs[r] = p.value
+                        self._opened.append(p.value)
+                except Exception as e:  # noqa: BLE001
+                    failure = e
+            ok = torch.tensor([0 if failure is not None else 1], dtype=torch.int32, device=job.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                self.close()
+                raise EtError(f"peer exchange unavailable on at least one rank (this rank: {failure!r})")
+        elif failure is not None:
+            raise EtError(f"peer exchange unavailable: {failure!r}")
         self.ptrs = (c_void_p * self.world)(*ptrs)
 
     @classmethod
@@ -771,13 +842,35 @@ class PeerExchange:
                                              c_int(self.hidden), c_int(self.epoch), _stream()),
               "et_hp_signal_partial_fwd")
 
-    def reduce_layernorm(self, x, bias, gamma, beta):
-        """bias / gamma / beta: device tensors or raw device addresses (c_void_p)."""
+    def reduce_layernorm(self, x, bias, gamma, beta, publish_ready: bool = False, gather: bool = True):
+        """bias / gamma / beta: device tensors or raw device addresses (c_void_p).
+        publish_ready: also do signal()'s job (one rank per GPU only).  gather=False keeps y
+        local (token-sharded form: only this rank's rows are computed and valid)."""
         vp = lambda a: a if isinstance(a, c_void_p) else _p(a)
         check(lib().et_hp_reduce_layernorm_fwd(self.ptrs, _p(x), vp(bias), vp(gamma), vp(beta),
                                                c_int(self.rank), c_int(self.world), c_int(self.T),
-                                               c_int(self.hidden), c_int(self.epoch), _stream()),
+                                               c_int(self.hidden), c_int(self.epoch),
+                                               c_int(1 if publish_ready else 0), c_int(1 if gather else 0),
+                                               _stream()),
               "et_hp_reduce_layernorm_fwd")
+
+    def rows(self):
+        """(first row, number of rows) this rank owns."""
+        per = (self.T + self.world - 1) // self.world
+        first = self.rank * per
+        return first, max(0, min(per, self.T - first))
+
+    def out(self, slot: int):
+        """Device address of out[slot] [T, hidden] fp16 in this rank's buffer."""
+        op = c_void_p(None)
+        check(lib().et_peer_buffer_out(c_void_p(self.own), c_int(self.world), c_int(self.T), c_int(self.hidden),
+                                       c_int(slot), ctypes.byref(op)), "et_peer_buffer_out")
+        return op.value
+
+    def allgather_rows(self, slot: int):
+        check(lib().et_hp_allgather_rows_fwd(self.ptrs, c_int(self.rank), c_int(self.world), c_int(self.T),
+                                             c_int(self.hidden), c_int(self.epoch), c_int(slot), _stream()),
+              "et_hp_allgather_rows_fwd")
 
     def wait(self):
         check(lib().et_hp_wait_fwd(c_void_p(self.own), c_int(self.world), c_int(self.T), c_int(self.hidden),

@@ -62,8 +62,8 @@ int launch_linear_tile_packed(const int* row_ptr, const uint32_t* pk_mask, const
 // The packed tile-CSR Linear as a persistent kernel (one CTA per SM walks work items of 128
 // tokens x 256 output features, two items' accumulators in tensor memory); see
 // linear_tile_persist.cu.  nnz_tiles > 0.
-// Which kernel serves packed weights: 0 = one item per CTA, 1 = persistent, -1 = by shape
-// (the default: persistent while one item per CTA would not fill the SMs).
+// Which kernel serves packed weights: 1 = persistent, anything else = one item per CTA (the
+// default).
 int tile_packed_mode();
 int launch_linear_tile_persist(const int* row_ptr, const uint32_t* pk_mask, const int* pk_off,
                                const __half* pk_tiles, int nnz_tiles, const __half* bias,

@@ -534,7 +534,7 @@ int launch_linear_tile_persist(const int* row_ptr, const uint32_t* pk_mask, cons
 
 #ifdef ET_TEST_HOOKS
 extern "C" {
-// Test hook: kernel for packed weights: 0 = one item per CTA, 1 = persistent, -1 = by shape
+// Test hook: kernel for packed weights: 1 = persistent, anything else = one item per CTA
 // (default).
 void et_debug_set_tile_persist(int mode) { et::g_tile_packed_mode = mode; }
 }

@@ -5,7 +5,8 @@
 // output projection straight into its exchange buffer, which every other rank has mapped.
 // Three kernels per layer and rank, all on the caller's stream:
 //   1. signal:  one thread publishes the layer's epoch in every peer's flag word for this rank
-//               (release, system scope) once the kernels before it - the projection - are done;
+//               (release, system scope) once the kernels before it - the projection - are done
+//               (a separate small kernel, or the first thing kernel 2 does: `publish_ready`);
 //   2. reduce:  the owner waits (bounded) until all ranks' flags show the epoch, PULLS its rows
 //               of every rank's partial through the peer mappings (NVLink reads, 16 bytes per
 //               lane), sums them in fp32, adds bias and residual, normalises (eps 1e-5, fp32
@@ -13,6 +14,14 @@
 //               by peer stores); the last CTA publishes the epoch in the second flag set;
 //   3. wait:    one small kernel that returns once all ranks' second flags show the epoch; the
 //               feed-forward kernels behind it on the stream then read y locally.
+// Token-sharded form (`gather` = 0 in kernel 2): the feed-forward block and the second LayerNorm
+// act on tokens independently, so a rank may run them on ITS rows only (1 / world of the work)
+// and pass the finished rows on: kernel 2 then keeps y local, the rank's feed-forward kernels
+// write its rows of the layer output into its own out[slot], hp_allgather_rows_kernel stores them
+// into every other rank's out[slot] and publishes the second flag set, kernel 3 waits for it.
+// The bytes moved are those of one all-reduce (a reduce-scatter after the output projection, an
+// all-gather after the layer); two out buffers alternate from layer to layer, so a rank that is
+// already writing layer l + 1's rows never touches rows a slower rank still reads as layer l's.
 // Kernels of different ranks wait on one another only across GPUs (one rank per GPU).  For a
 // single-GPU emulation of several ranks the caller runs every rank's kernel 1, then every kernel
 // 2, then the waits, so that no wait ever has to spin.  Buffer reuse across layers is safe
@@ -36,7 +45,8 @@ struct PeerPtrs {
 struct PeerLayout {
     int rows_r;          // token rows owned by a rank
     size_t y_off;        // y [T, hidden] fp16 (the rank's partial [T, hidden] fp16 sits at 0)
-    size_t flags_off;    // int partial_ready[16], y_ready[16], counters[4]
+    size_t out_off[2];   // two layer-output buffers [T, hidden] fp16 (token-sharded form)
+    size_t flags_off;    // int partial_ready[16], rows_ready[16], counters[4]
     size_t total;
 };
 
@@ -44,7 +54,9 @@ __host__ __device__ inline PeerLayout peer_layout(int world, int T, int hidden) 
     PeerLayout l;
     l.rows_r = (T + world - 1) / world;
     l.y_off = (static_cast<size_t>(T) * hidden * 2 + 255) & ~static_cast<size_t>(255);
-    l.flags_off = 2 * l.y_off;
+    l.out_off[0] = 2 * l.y_off;
+    l.out_off[1] = 3 * l.y_off;
+    l.flags_off = 4 * l.y_off;
     l.total = l.flags_off + 256;
     return l;
 }
@@ -105,12 +117,19 @@ template <int NCH>
 __global__ void __launch_bounds__(256)
 hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* __restrict__ bias,
                     const __half* __restrict__ gamma, const __half* __restrict__ beta, int rank, int world,
-                    int T, int hidden, int epoch, float eps, int* err_word) {
+                    int T, int hidden, int epoch, float eps, int publish_ready, int gather, int* err_word) {
     __shared__ int s_ok;
     const PeerLayout l = peer_layout(world, T, hidden);
     uint8_t* mine = peers.p[rank];
     pdl_launch_dependents();
     pdl_wait();
+    // publish_ready: this kernel also tells the peers that this rank's partial is complete (the
+    // kernels before it on the stream have ended), which saves the separate signal launch
+    if (publish_ready && blockIdx.x == 0 && threadIdx.x == 0) {
+        __threadfence_system();
+        for (int d = 0; d < world; ++d)
+            st_release_sys(reinterpret_cast<int*>(peers.p[d] + l.flags_off) + rank, epoch);
+    }
     const bool ok = wait_flags(reinterpret_cast<const int*>(mine + l.flags_off), world, epoch, &s_ok);
     if (!ok && threadIdx.x == 0 && err_word) atomicCAS(err_word, 0, DEV_TIMEOUT_PEER);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -187,14 +206,44 @@ hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* 
                                       fmaf((v[i][2 * j + 1] - mean) * rstd, fg.y, ft.y));
                 }
                 const uint4 q = make_uint4(o[0], o[1], o[2], o[3]);
-                for (int d = 0; d < world; ++d)
-                    *(reinterpret_cast<uint4*>(peers.p[d] + l.y_off) + static_cast<size_t>(row) * vec_per_row + c) = q;
+                if (gather) {
+                    for (int d = 0; d < world; ++d)
+                        *(reinterpret_cast<uint4*>(peers.p[d] + l.y_off) + static_cast<size_t>(row) * vec_per_row + c) = q;
+                } else {
+                    *(reinterpret_cast<uint4*>(mine + l.y_off) + static_cast<size_t>(row) * vec_per_row + c) = q;
+                }
             }
         }
     int* counters = reinterpret_cast<int*>(mine + l.flags_off) + 32;
-    if (last_cta_done(counters + 1)) {
+    if (gather && last_cta_done(counters + 1)) {
         // published even after a give-up: the peers' waits then end at once and the code in the
         // error word tells the host that this layer's output is not valid
+        for (int d = 0; d < world; ++d)
+            st_release_sys(reinterpret_cast<int*>(peers.p[d] + l.flags_off) + 16 + rank, epoch);
+    }
+}
+
+// Token-sharded form: this rank's rows of the layer output (in its own out[slot]) go into every
+// other rank's out[slot]; the last CTA publishes the epoch in the second flag set.
+__global__ void __launch_bounds__(256)
+hp_allgather_rows_kernel(PeerPtrs peers, int rank, int world, int T, int hidden, int epoch, int slot) {
+    const PeerLayout l = peer_layout(world, T, hidden);
+    const int vec_per_row = hidden >> 3;
+    const int row0 = rank * l.rows_r;
+    const int nrows = (T - row0) < l.rows_r ? (T - row0 > 0 ? T - row0 : 0) : l.rows_r;
+    const size_t total = static_cast<size_t>(nrows) * vec_per_row;
+    const size_t base = static_cast<size_t>(row0) * vec_per_row;
+    const uint4* src = reinterpret_cast<const uint4*>(peers.p[rank] + l.out_off[slot]) + base;
+    pdl_launch_dependents();
+    pdl_wait();  // the rows belong to the kernels before this one
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < total;
+         v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint4 q = __ldcg(src + v);
+        for (int d = 0; d < world; ++d)
+            if (d != rank) *(reinterpret_cast<uint4*>(peers.p[d] + l.out_off[slot]) + base + v) = q;
+    }
+    int* counters = reinterpret_cast<int*>(peers.p[rank] + l.flags_off) + 32;
+    if (last_cta_done(counters + 2)) {
         for (int d = 0; d < world; ++d)
             st_release_sys(reinterpret_cast<int*>(peers.p[d] + l.flags_off) + 16 + rank, epoch);
     }
@@ -303,9 +352,35 @@ int et_hp_signal_partial_fwd(void* const* peer_buffers, int rank, int world, int
                : ET_ERR_CUDA;
 }
 
+int et_peer_buffer_out(void* own_buffer, int world, int T, int hidden, int slot, et_half** out) {
+    if (!own_buffer || !out || world < 1 || world > et::PEER_MAX_WORLD || T <= 0 || hidden <= 0 || slot < 0 ||
+        slot > 1)
+        return ET_ERR_INVALID_ARG;
+    *out = reinterpret_cast<et_half*>(static_cast<uint8_t*>(own_buffer) +
+                                      et::peer_layout(world, T, hidden).out_off[slot]);
+    return ET_OK;
+}
+
+int et_hp_allgather_rows_fwd(void* const* peer_buffers, int rank, int world, int T, int hidden, int epoch,
+                             int slot, et_stream stream) {
+    int st = et::check_args(peer_buffers, rank, world, T, hidden);
+    if (st != ET_OK) return st;
+    if (slot < 0 || slot > 1) return ET_ERR_INVALID_ARG;
+    const int rows_r = (T + world - 1) / world;
+    const size_t vecs = static_cast<size_t>(rows_r) * (hidden / 8);
+    const int sms = et::sm_count() > 0 ? et::sm_count() : 148;
+    const size_t want = (vecs + 255) / 256;
+    const int blocks = static_cast<int>(want < 1 ? 1 : (want < static_cast<size_t>(4 * sms) ? want : 4 * sms));
+    return et::launch_kernel(et::hp_allgather_rows_kernel, dim3(blocks), dim3(256), 0,
+                             static_cast<cudaStream_t>(stream), et::pack(peer_buffers, world), rank, world, T,
+                             hidden, epoch, slot) == cudaSuccess
+               ? ET_OK
+               : ET_ERR_CUDA;
+}
+
 int et_hp_reduce_layernorm_fwd(void* const* peer_buffers, const et_half* x, const et_half* bias,
                                const et_half* gamma, const et_half* beta, int rank, int world, int T,
-                               int hidden, int epoch, et_stream stream) {
+                               int hidden, int epoch, int publish_ready, int gather, et_stream stream) {
     int st = et::check_args(peer_buffers, rank, world, T, hidden);
     if (st != ET_OK) return st;
     if (!x || !gamma || !beta) return ET_ERR_INVALID_ARG;
@@ -327,7 +402,7 @@ int et_hp_reduce_layernorm_fwd(void* const* peer_buffers, const et_half* x, cons
     cudaError_t e;
     auto go = [&](auto kern) {
         return et::launch_kernel(kern, dim3(blocks), dim3(256), 0, s, peers, xh, bh, gh, th, rank, world, T,
-                                 hidden, epoch, 1e-5f, err);
+                                 hidden, epoch, 1e-5f, publish_ready, gather, err);
     };
     if (nch <= 3)
         e = go(et::hp_reduce_ln_kernel<3>);

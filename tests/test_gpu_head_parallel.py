@@ -101,7 +101,46 @@ def test_peer_exchange_ranks_emulated_on_one_gpu(world, seq):
             ex.close()
 
 
-def _worker(rank: int, world: int, port: int, out_q, peer: bool = False):
+@pytest.mark.parametrize("world,seq", [(8, 1024), (3, 1000)])
+def test_token_sharded_ffn_ranks_emulated_on_one_gpu(world, seq):
+    """The token-sharded form (reduce-scatter after the output projection, feed-forward block on
+    the rank's own rows, all-gather of the finished rows), every rank's buffer on ONE GPU and
+    every rank's step run before the next step of any rank.  Two layers chained through the
+    exchange buffers' alternating out slots; all ranks must hold the same output."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from conftest import assert_close
+    et = entry.load_package()
+    orc = entry.load_oracle()
+    orc.build()
+    dev = torch.device("cuda:0")
+    hidden, nhead, ff = 768, 12, 3072
+    w = et.synth.encoder_layer_weights(47, 0, hidden, ff, std=0.03, bias_std=0.02, ln_noise=0.1)
+    x = et.synth.normal(47, 3, (seq, hidden), 1.0)
+    layers = [et.HeadParallelLayer(w, nhead, et.sharding.Job(rank=r, world=world, device=dev),
+                                   et.ACT_GELU, device=dev) for r in range(world)]
+    exs = et.PeerExchange.local(world, seq, hidden)
+    try:
+        xs = [torch.from_numpy(x).to(dev) for _ in range(world)]
+        ref = x
+        for _ in range(2):
+            for phase in ("partial", "reduce", "ffn", "wait"):
+                outs = [layers[r].forward_peer_sharded(xs[r], 1, seq, exs[r], phase=phase) for r in range(world)]
+            torch.cuda.synchronize()
+            assert et.device_error() == 0
+            for r in range(1, world):
+                assert torch.equal(outs[r], outs[0]), f"rank {r} differs from rank 0"
+            ref = orc.encoder_layer(ref, w, 1, seq, nhead, 2, 0)
+            assert_close(outs[0].float().cpu().numpy(), ref, f"token-sharded form, {world} emulated ranks")
+            ref = outs[0].cpu().numpy()
+            xs = outs
+    finally:
+        for ex in exs:
+            ex.close()
+
+
+def _worker(rank: int, world: int, port: int, out_q, peer=False):
     try:
         import torch
         import torch.distributed as dist
@@ -120,8 +159,9 @@ def _worker(rank: int, world: int, port: int, out_q, peer: bool = False):
         if peer:
             ex = et.PeerExchange(job, seq, hidden)
             dist.barrier()
-            y = layer.forward_peer(xd, 1, seq, ex)
-            y = layer.forward_peer(y, 1, seq, ex)  # a second layer call reuses the buffers
+            fwd = layer.forward_peer_sharded if peer == "sharded" else layer.forward_peer
+            y = fwd(xd, 1, seq, ex)
+            y = fwd(y, 1, seq, ex).clone()  # a second layer call reuses the buffers
         else:
             y = layer.forward(xd, 1, seq)
         torch.cuda.synchronize()
@@ -138,10 +178,11 @@ def _worker(rank: int, world: int, port: int, out_q, peer: bool = False):
         raise
 
 
-@pytest.mark.parametrize("peer", [False, True])
+@pytest.mark.parametrize("peer", [False, True, "sharded"])
 def test_head_parallel_layer_two_gpus(peer):
     """peer=False: one NCCL all-reduce per layer; peer=True: the exchange by this library's
-    kernels over peer memory (CUDA IPC mappings), two layer calls in a row."""
+    kernels over peer memory (CUDA IPC mappings), two layer calls in a row; "sharded": the same
+    with the feed-forward block on each rank's own token rows."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
