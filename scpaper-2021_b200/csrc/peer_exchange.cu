@@ -70,11 +70,13 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     return v;
 }
 
-// Last-CTA-done: every thread's stores are ordered before the caller's fence; returns true in
-// thread 0 of the CTA that arrives last (and resets the counter for the next launch).
+// Last-CTA-done: the CTA's stores are ordered before thread 0's system-scope fence by the CTA
+// barrier (one fence per CTA: a system-scope fence costs microseconds, so launches that end with
+// this use about one CTA per SM); returns true in thread 0 of the CTA that arrives last (and
+// resets the counter for the next launch).
 __device__ __forceinline__ bool last_cta_done(int* counter) {
     __syncthreads();
-    if (threadIdx.x != 0) return false;
+    if (threadIdx.x != 0 || threadIdx.y != 0) return false;
     __threadfence_system();
     const int before = atomicAdd(counter, 1);
     if (before != static_cast<int>(gridDim.x) - 1) return false;
@@ -112,42 +114,62 @@ __global__ void hp_signal_kernel(PeerPtrs peers, int rank, int world, size_t fla
     }
 }
 
-// One warp per owned row; NCH = ceil(hidden / 256) chunks of 8 values per lane.
-template <int NCH>
-__global__ void __launch_bounds__(256)
+// One thread per 16-byte vector of an owned row: blockDim = (threads per row: hidden / 8 rounded up
+// to a warp multiple, rows per CTA).  Every thread has `world` remote loads in flight at once and
+// all rows of the launch are resident together, which is what hides the NVLink round trip.
+__global__ void __launch_bounds__(512)
 hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* __restrict__ bias,
                     const __half* __restrict__ gamma, const __half* __restrict__ beta, int rank, int world,
                     int T, int hidden, int epoch, float eps, int publish_ready, int gather, int* err_word) {
     __shared__ int s_ok;
+    __shared__ float2 s_part[16][16];  // [row of the CTA][warp of the row]
     const PeerLayout l = peer_layout(world, T, hidden);
     uint8_t* mine = peers.p[rank];
+    const int tid = threadIdx.y * blockDim.x + threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     // publish_ready: this kernel also tells the peers that this rank's partial is complete (the
     // kernels before it on the stream have ended), which saves the separate signal launch
-    if (publish_ready && blockIdx.x == 0 && threadIdx.x == 0) {
+    if (publish_ready && blockIdx.x == 0 && tid == 0) {
         __threadfence_system();
         for (int d = 0; d < world; ++d)
             st_release_sys(reinterpret_cast<int*>(peers.p[d] + l.flags_off) + rank, epoch);
     }
-    const bool ok = wait_flags(reinterpret_cast<const int*>(mine + l.flags_off), world, epoch, &s_ok);
-    if (!ok && threadIdx.x == 0 && err_word) atomicCAS(err_word, 0, DEV_TIMEOUT_PEER);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // bounded wait until every rank's partial is ready: thread i < world polls flag i
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < world) {
+        const int* flags = reinterpret_cast<const int*>(mine + l.flags_off);
+        bool seen = false;
+        for (uint32_t it = 0; it < PEER_POLL_LIMIT; ++it) {
+            if (ld_acquire_sys(flags + tid) - epoch >= 0) {
+                seen = true;
+                break;
+            }
+            __nanosleep(200);
+        }
+        if (!seen) s_ok = 0;
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    if (!ok && tid == 0 && err_word) atomicCAS(err_word, 0, DEV_TIMEOUT_PEER);
+
     const int row0 = rank * l.rows_r;
     const int nrows = (T - row0) < l.rows_r ? (T - row0 > 0 ? T - row0 : 0) : l.rows_r;
     const int vec_per_row = hidden >> 3;
+    const int c = threadIdx.x, ty = threadIdx.y;
+    const int lane = threadIdx.x & 31, wrow = threadIdx.x >> 5, nwrow = blockDim.x >> 5;
     const float inv_n = 1.0f / static_cast<float>(hidden);
     if (ok)
-        for (int lrow = blockIdx.x * (blockDim.x >> 5) + warp; lrow < nrows; lrow += gridDim.x * (blockDim.x >> 5)) {
+        for (int base = blockIdx.x * blockDim.y; base < nrows; base += gridDim.x * blockDim.y) {
+            const int lrow = base + ty;
+            const bool live = lrow < nrows && c < vec_per_row;
             const int row = row0 + lrow;
-            float v[NCH][8];
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
             float sum = 0.f, sq = 0.f;
-#pragma unroll
-            for (int i = 0; i < NCH; ++i) {
-                const int c = lane + 32 * i;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
-                if (c >= vec_per_row) continue;
+            if (live) {
                 const size_t off = static_cast<size_t>(row) * vec_per_row + c;
                 for (int s0 = 0; s0 < world; s0 += 4) {  // four ranks' loads in flight together
                     uint4 q[4];
@@ -161,8 +183,8 @@ hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* 
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float2 f = __half22float2(h[j]);
-                            v[i][2 * j] += f.x;
-                            v[i][2 * j + 1] += f.y;
+                            v[2 * j] += f.x;
+                            v[2 * j + 1] += f.y;
                         }
                     }
                 }
@@ -174,13 +196,13 @@ hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* 
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 fx = __half22float2(hx[j]), fb = __half22float2(hb[j]);
-                    v[i][2 * j] += fx.x + fb.x;
-                    v[i][2 * j + 1] += fx.y + fb.y;
+                    v[2 * j] += fx.x + fb.x;
+                    v[2 * j + 1] += fx.y + fb.y;
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    sum += v[i][j];
-                    sq = fmaf(v[i][j], v[i][j], sq);
+                    sum += v[j];
+                    sq = fmaf(v[j], v[j], sq);
                 }
             }
 #pragma unroll
@@ -188,12 +210,17 @@ hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* 
                 sum += __shfl_xor_sync(0xffffffffu, sum, d);
                 sq += __shfl_xor_sync(0xffffffffu, sq, d);
             }
-            const float mean = sum * inv_n;
-            const float rstd = rsqrtf(fmaxf(sq * inv_n - mean * mean, 0.f) + eps);
-#pragma unroll
-            for (int i = 0; i < NCH; ++i) {
-                const int c = lane + 32 * i;
-                if (c >= vec_per_row) continue;
+            if (lane == 0) s_part[ty][wrow] = make_float2(sum, sq);
+            __syncthreads();
+            float tsum = 0.f, tsq = 0.f;
+            for (int k = 0; k < nwrow; ++k) {
+                tsum += s_part[ty][k].x;
+                tsq += s_part[ty][k].y;
+            }
+            __syncthreads();  // s_part is rewritten by the next pass
+            if (live) {
+                const float mean = tsum * inv_n;
+                const float rstd = rsqrtf(fmaxf(tsq * inv_n - mean * mean, 0.f) + eps);
                 const uint4 qg = __ldg(reinterpret_cast<const uint4*>(gamma) + c);
                 const uint4 qt = __ldg(reinterpret_cast<const uint4*>(beta) + c);
                 const __half2* hg = reinterpret_cast<const __half2*>(&qg);
@@ -202,30 +229,32 @@ hp_reduce_ln_kernel(PeerPtrs peers, const __half* __restrict__ x, const __half* 
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 fg = __half22float2(hg[j]), ft = __half22float2(ht[j]);
-                    o[j] = pack_half2(fmaf((v[i][2 * j] - mean) * rstd, fg.x, ft.x),
-                                      fmaf((v[i][2 * j + 1] - mean) * rstd, fg.y, ft.y));
+                    o[j] = pack_half2(fmaf((v[2 * j] - mean) * rstd, fg.x, ft.x),
+                                      fmaf((v[2 * j + 1] - mean) * rstd, fg.y, ft.y));
                 }
                 const uint4 q = make_uint4(o[0], o[1], o[2], o[3]);
+                const size_t off = static_cast<size_t>(row) * vec_per_row + c;
                 if (gather) {
-                    for (int d = 0; d < world; ++d)
-                        *(reinterpret_cast<uint4*>(peers.p[d] + l.y_off) + static_cast<size_t>(row) * vec_per_row + c) = q;
+                    for (int d = 0; d < world; ++d) *(reinterpret_cast<uint4*>(peers.p[d] + l.y_off) + off) = q;
                 } else {
-                    *(reinterpret_cast<uint4*>(mine + l.y_off) + static_cast<size_t>(row) * vec_per_row + c) = q;
+                    *(reinterpret_cast<uint4*>(mine + l.y_off) + off) = q;
                 }
             }
         }
     int* counters = reinterpret_cast<int*>(mine + l.flags_off) + 32;
-    if (gather && last_cta_done(counters + 1)) {
-        // published even after a give-up: the peers' waits then end at once and the code in the
-        // error word tells the host that this layer's output is not valid
-        for (int d = 0; d < world; ++d)
-            st_release_sys(reinterpret_cast<int*>(peers.p[d] + l.flags_off) + 16 + rank, epoch);
+    if (gather) {
+        if (last_cta_done(counters + 1)) {
+            // published even after a give-up: the peers' waits then end at once and the code in
+            // the error word tells the host that this layer's output is not valid
+            for (int d = 0; d < world; ++d)
+                st_release_sys(reinterpret_cast<int*>(peers.p[d] + l.flags_off) + 16 + rank, epoch);
+        }
     }
 }
 
 // Token-sharded form: this rank's rows of the layer output (in its own out[slot]) go into every
 // other rank's out[slot]; the last CTA publishes the epoch in the second flag set.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 hp_allgather_rows_kernel(PeerPtrs peers, int rank, int world, int T, int hidden, int epoch, int slot) {
     const PeerLayout l = peer_layout(world, T, hidden);
     const int vec_per_row = hidden >> 3;
@@ -369,9 +398,9 @@ int et_hp_allgather_rows_fwd(void* const* peer_buffers, int rank, int world, int
     const int rows_r = (T + world - 1) / world;
     const size_t vecs = static_cast<size_t>(rows_r) * (hidden / 8);
     const int sms = et::sm_count() > 0 ? et::sm_count() : 148;
-    const size_t want = (vecs + 255) / 256;
-    const int blocks = static_cast<int>(want < 1 ? 1 : (want < static_cast<size_t>(4 * sms) ? want : 4 * sms));
-    return et::launch_kernel(et::hp_allgather_rows_kernel, dim3(blocks), dim3(256), 0,
+    const size_t want = (vecs + 511) / 512;
+    const int blocks = static_cast<int>(want < 1 ? 1 : (want < static_cast<size_t>(sms) ? want : sms));
+    return et::launch_kernel(et::hp_allgather_rows_kernel, dim3(blocks), dim3(512), 0,
                              static_cast<cudaStream_t>(stream), et::pack(peer_buffers, world), rank, world, T,
                              hidden, epoch, slot) == cudaSuccess
                ? ET_OK
@@ -390,26 +419,16 @@ int et_hp_reduce_layernorm_fwd(void* const* peer_buffers, const et_half* x, cons
     if (!err) return ET_ERR_NO_DEVICE;
     const int rows_r = (T + world - 1) / world;
     const int sms = et::sm_count() > 0 ? et::sm_count() : 148;
-    int blocks = (rows_r + 7) / 8;
+    const int tpr = ((hidden / 8 + 31) / 32) * 32;  // threads per row (<= 256)
+    int rpb = 384 / tpr;                             // rows per CTA
+    rpb = rpb < 1 ? 1 : (rpb > 16 ? 16 : rpb);
+    int blocks = (rows_r + rpb - 1) / rpb;
     blocks = blocks < 1 ? 1 : (blocks > 2 * sms ? 2 * sms : blocks);
-    const et::PeerPtrs peers = et::pack(peer_buffers, world);
-    const __half* xh = reinterpret_cast<const __half*>(x);
-    const __half* bh = reinterpret_cast<const __half*>(bias);
-    const __half* gh = reinterpret_cast<const __half*>(gamma);
-    const __half* th = reinterpret_cast<const __half*>(beta);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int nch = (hidden + 255) / 256;
-    cudaError_t e;
-    auto go = [&](auto kern) {
-        return et::launch_kernel(kern, dim3(blocks), dim3(256), 0, s, peers, xh, bh, gh, th, rank, world, T,
-                                 hidden, epoch, 1e-5f, publish_ready, gather, err);
-    };
-    if (nch <= 3)
-        e = go(et::hp_reduce_ln_kernel<3>);
-    else if (nch <= 4)
-        e = go(et::hp_reduce_ln_kernel<4>);
-    else
-        e = go(et::hp_reduce_ln_kernel<8>);
+    const cudaError_t e = et::launch_kernel(
+        et::hp_reduce_ln_kernel, dim3(blocks), dim3(tpr, rpb), 0, static_cast<cudaStream_t>(stream),
+        et::pack(peer_buffers, world), reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(bias),
+        reinterpret_cast<const __half*>(gamma), reinterpret_cast<const __half*>(beta), rank, world, T, hidden, epoch,
+        1e-5f, publish_ready, gather, err);
     return e == cudaSuccess ? ET_OK : ET_ERR_CUDA;
 }
 
