@@ -659,6 +659,23 @@ def main():
                 c3["dense_same_shapes"]["ms_per_step"] / c3[key]["ms_per_step"]
             c3[key]["speedup_vs_c2_b64"] = configs["c2_b64"]["ms_per_step"] / c3[key]["ms_per_step"]
         c3["stored_tiles_per_layer"] = stored / LAYERS
+        # the same shapes at higher tile sparsity: how the tile kernels' time falls with the tiles
+        sweep = {"80": {"ms_per_step": c3["tile_kernel"]["ms_per_step"],
+                        "speedup_vs_dense_same_shapes": c3["tile_kernel"]["speedup_vs_dense_same_shapes"]}}
+        for pct, sp in ((90, 0.9), (95, 0.95)):
+            wsp = []
+            for l, w in enumerate(base3):
+                w = dict(w)
+                for i, name in enumerate(("wqkv", "wo", "w1", "w2")):
+                    w[name] = et.synth.prune_tiles(w[name], SEED, 100 * (l + 1) + 50 + i, sp)
+                wsp.append(w)
+            ls = [et.EncoderLayer(w, NHEAD, et.ACT_GELU, device=dev, tile_sparse=True) for w in wsp]
+            r = run_config(ls, 64, SEQ, flops_per_sequence(kdim=kq, lin_flops_per_token=512.0 * stored_tiles(wsp) / LAYERS),
+                           f3_dense)
+            sweep[str(pct)] = {"ms_per_step": r["ms_per_step"],
+                               "speedup_vs_dense_same_shapes": c3["dense_same_shapes"]["ms_per_step"] / r["ms_per_step"]}
+            del ls, wsp
+        c3["tile_kernel_by_sparsity_pct"] = sweep
         configs["c3_b64_tile80_qk25"] = c3
         del base3, c3w
 
