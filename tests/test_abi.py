@@ -87,3 +87,25 @@ def test_argument_checks_need_no_gpu(et):
     assert lib.et_linear_dense_fwd(None, None, None, None, 4, 20, 16, 0, None) == -3
     assert lib.et_skip_layernorm_fwd(None, None, None, None, None, 1, 8, None) == -1
     assert lib.et_encoder_layer_workspace_bytes(None, 1, 1) == 0
+
+
+def test_peer_exchange_argument_checks(et):
+    """The head-parallel exchange entry points reject bad arguments before touching a device."""
+    lib = et.lib()
+    lib.et_peer_buffer_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                         ctypes.POINTER(ctypes.c_size_t)]
+    n = ctypes.c_size_t(0)
+    assert lib.et_peer_buffer_bytes(8, 4096, 768, ctypes.byref(n)) == 0
+    # partial + y + two output buffers of T x hidden fp16, plus the flag words
+    assert n.value >= 4 * 4096 * 768 * 2 and n.value < 4 * 4096 * 768 * 2 + 4096
+    assert lib.et_peer_buffer_bytes(17, 4096, 768, ctypes.byref(n)) == -1
+    assert lib.et_peer_buffer_bytes(8, 0, 768, ctypes.byref(n)) == -1
+    bufs = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    # world out of range, rank out of range, a null buffer, an odd hidden size, misalignment
+    assert lib.et_hp_signal_partial_fwd(bufs, 0, 17, 128, 768, 1, None) == -1
+    assert lib.et_hp_signal_partial_fwd(bufs, 2, 2, 128, 768, 1, None) == -1
+    assert lib.et_hp_signal_partial_fwd((ctypes.c_void_p * 2)(0x1000, None), 0, 2, 128, 768, 1, None) == -1
+    assert lib.et_hp_signal_partial_fwd(bufs, 0, 2, 128, 772, 1, None) == -3
+    assert lib.et_hp_signal_partial_fwd((ctypes.c_void_p * 2)(0x1000, 0x2010), 0, 2, 128, 768, 1, None) == -2
+    assert lib.et_hp_allgather_rows_fwd(bufs, 0, 2, 128, 768, 1, 2, None) == -1
+    assert lib.et_peer_buffer_open(None, None) == -1
