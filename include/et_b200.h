@@ -286,8 +286,11 @@ int et_attention_pruned_v_fwd(const et_half* Q, const et_half* K, const et_half*
                               const int32_t* valid_len, float scale, et_stream stream);
 
 /* Attention followed by a tile-CSR output projection in one call:
- * out = tileLinear_O( attention(Q, K, V) ) + bias_o.  Z[T, nhead*dh_v] is caller scratch.
- * Stands in for Multihead_atttion_fuseO (Attention/kernel_fuseO.cu:254-290). */
+ * out = tileLinear_O( attention(Q, K, V) ) + bias_o.  Z[T, nhead*dh_v] receives the heads'
+ * outputs (the reference's Z argument).  Stands in for Multihead_atttion_fuseO
+ * (Attention/kernel_fuseO.cu:254-290).  Runs the attention kernel and the tile Linear as two
+ * launches chained by programmatic dependent launch: on B200 that is the faster of the two
+ * forms (see et_attention_fuse_o_single_launch_fwd). */
 int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,
                             const et_half* mask, et_half* Z, const int32_t* o_row_ptr,
                             const int32_t* o_row_off, const et_half* o_tiles, int o_nnz,
@@ -295,6 +298,26 @@ int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V
                             int dh_qk, int dh_v, int ldq, int ldk, int ldv, int emdim,
                             int mask_kind, const int32_t* valid_len, float scale,
                             et_stream stream);
+
+/* The same operator as ONE cooperative kernel launch, the form of the reference's
+ * __kernel_multi_head_full_fuseO (Attention/kernel_fuseO.cu:138-243) with its grid-wide barrier
+ * replaced by one completion counter per (sequence, 128-query block): a CTA first runs its
+ * share of the (sequence, query block, head) attention units, then its share of the
+ * (128-token block, 128 output features) projection items, each of which starts as soon as
+ * the query blocks it reads are complete.  Same arguments and bit-identical results.  The
+ * counters live in the library image: at most 16 such calls may be in flight on one GPU at
+ * once, and batch * ceil(seq / 128) must stay below 4096 (beyond that, or when W_O stores no
+ * tile, the call runs the two-launch form).  A counter wait is bounded (about a second); when
+ * it runs out et_device_error reports 304.  Measured on B200 it is slower than the two-launch
+ * form (the driver admits one CTA per SM to a cooperative launch of a kernel that allocates
+ * tensor memory; both phases are built for two). */
+int et_attention_fuse_o_single_launch_fwd(const et_half* Q, const et_half* K, const et_half* V,
+                                          const et_half* mask, et_half* Z, const int32_t* o_row_ptr,
+                                          const int32_t* o_row_off, const et_half* o_tiles, int o_nnz,
+                                          const et_half* o_bias, et_half* out, int batch, int seq,
+                                          int nhead, int dh_qk, int dh_v, int ldq, int ldk, int ldv,
+                                          int emdim, int mask_kind, const int32_t* valid_len,
+                                          float scale, et_stream stream);
 
 /* Pre-multiplied V.O attention: out[t, :] = sum_h P_h[t, :] . VO_h + bias_o with
  * VO given as [batch][nhead][seq][emdim] (Fused_attention/Linear_VO.h:38-58).

@@ -36,7 +36,8 @@ ABI_SYMBOLS = [
     "et_validate_csr", "et_skip_layernorm_fwd", "et_layernorm_fwd", "et_act_fwd",
     "et_bias_add_fwd", "et_attention_fwd", "et_qkv_attention_fwd", "et_attention_pruned_v_fwd",
     "et_linear_vo_pruned_fwd", "et_fused_vo_attention_pruned_fwd",
-    "et_attention_fuse_o_fwd", "et_fused_vo_attention_fwd", "et_linear_vo_fwd",
+    "et_attention_fuse_o_fwd", "et_attention_fuse_o_single_launch_fwd",
+    "et_fused_vo_attention_fwd", "et_linear_vo_fwd",
     "et_encoder_layer_workspace_bytes", "et_encoder_layer_fwd",
     "et_attention_units_fwd", "et_encoder_attention_units_fwd", "et_encoder_after_attention_fwd",
 ]
@@ -367,11 +368,15 @@ def attention_pruned_v(q, k, vc, col_id, head_ptr, batch, seq, nhead, dh_qk, dh_
 
 
 def attention_fuse_o(q, k, v, o_row_ptr, o_row_off, o_tiles, o_bias, batch, seq, nhead, dh_qk,
-                     dh_v, emdim, mask_kind=MASK_NONE, mask=None, valid_len=None, scale=None):
+                     dh_v, emdim, mask_kind=MASK_NONE, mask=None, valid_len=None, scale=None,
+                     single_launch=False):
+    """Attention + tile-CSR output projection (Attention/kernel_fuseO.cu:254-290);
+    single_launch=True runs both in one cooperative kernel."""
     z = _empty((batch * seq, nhead * dh_v), q)
     out = _empty((batch * seq, emdim), q)
     scale = (1.0 / dh_qk ** 0.5) if scale is None else scale
-    check(lib().et_attention_fuse_o_fwd(_p(q), _p(k), _p(v), _p(mask), _p(z), _p(o_row_ptr),
+    fn = lib().et_attention_fuse_o_single_launch_fwd if single_launch else lib().et_attention_fuse_o_fwd
+    check(fn(_p(q), _p(k), _p(v), _p(mask), _p(z), _p(o_row_ptr),
                                         _p(o_row_off), _p(o_tiles), c_int(int(o_tiles.shape[0])),
                                         _p(o_bias), _p(out), c_int(batch), c_int(seq),
                                         c_int(nhead), c_int(dh_qk), c_int(dh_v),

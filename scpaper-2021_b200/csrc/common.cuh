@@ -59,6 +59,7 @@ enum : int {
     DEV_TIMEOUT_VO_PRODUCER = 401,
     DEV_TIMEOUT_VO_MMA = 402,
     DEV_TIMEOUT_VO_SOFTMAX = 403,
+    DEV_TIMEOUT_FUSE_O = 304,  // the output projection waited for attention outputs that never came
     DEV_TIMEOUT_PEER = 501,  // a rank's flag did not arrive (head-parallel exchange over peer memory)
 };
 
@@ -122,6 +123,11 @@ __device__ __forceinline__ bool elect_one() {
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+// Ends the life of a barrier object: its memory may be used for anything, a new barrier included.
+__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -249,6 +255,15 @@ __device__ __forceinline__ void tma_store_commit() {
 }
 __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Waits until this thread's bulk stores have completed, their writes to global memory included.
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Orders accesses of the generic proxy (plain loads, stores and atomics) and of the async proxy
+// (TMA) of this thread against each other, in both directions, for every state space.
+__device__ __forceinline__ void fence_proxy_async_all() {
+    asm volatile("fence.proxy.async;" ::: "memory");
 }
 // Waits until at most N of this thread's bulk store groups still read their shared memory.
 template <int N>

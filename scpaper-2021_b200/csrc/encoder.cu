@@ -411,26 +411,4 @@ int et_encoder_ffn_fwd(const et_encoder_layer_t* layer, const et_half* y, et_hal
                          static_cast<cudaStream_t>(stream));
 }
 
-int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,
-                            const et_half* mask, et_half* Z, const int32_t* o_row_ptr,
-                            const int32_t* o_row_off, const et_half* o_tiles, int o_nnz,
-                            const et_half* o_bias, et_half* out, int batch, int seq, int nhead,
-                            int dh_qk, int dh_v, int ldq, int ldk, int ldv, int emdim,
-                            int mask_kind, const int32_t* valid_len, float scale,
-                            et_stream stream) {
-    if (!Z || !out) return ET_ERR_INVALID_ARG;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int vdim = nhead * dh_v;
-    int st = et::launch_attention(reinterpret_cast<const __half*>(Q),
-                                  reinterpret_cast<const __half*>(K),
-                                  reinterpret_cast<const __half*>(V), reinterpret_cast<__half*>(Z),
-                                  batch, seq, nhead, dh_qk, dh_v, ldq, ldk, ldv, vdim, mask_kind,
-                                  reinterpret_cast<const __half*>(mask), valid_len, scale, s);
-    if (st != ET_OK) return st;
-    return et::launch_linear_tile(o_row_ptr, o_row_off, reinterpret_cast<const __half*>(o_tiles),
-                                  o_nnz, reinterpret_cast<const __half*>(o_bias),
-                                  reinterpret_cast<const __half*>(Z), reinterpret_cast<__half*>(out),
-                                  batch * seq, vdim, emdim, ET_ACT_NONE, s);
-}
-
 }  // extern "C"

@@ -41,6 +41,10 @@ using namespace gemm;
 template <int BN, int STAGES, bool PERSIST>
 struct GemmCfg {
     static constexpr int B_STAGE_BYTES = BN * BK * 2;
+    // One tcgen05.mma covers at most 256 columns and one TMA box at most 256 rows: a wider tile
+    // is two halves side by side, in shared memory and in the accumulator.
+    static constexpr int MMA_N = BN > 256 ? BN / 2 : BN;
+    static constexpr int N_HALVES = BN / MMA_N;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
     // staging tiles of the epilogue: one 4 KB tile per (quadrant, 64 fp16 columns) or, for fp32
     // partials (BN <= 128 only), per (quadrant, 32 fp32 columns)
@@ -161,7 +165,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         tma_load_3d(sB + s * Cfg::B_STAGE_BYTES + t * (BK * 128), &tmB, &full_bar[s],
                                     c.n0 + t * 64, kb * BK, c.z);
                 } else {
-                    tma_load_2d(sB + s * Cfg::B_STAGE_BYTES, &tmB, &full_bar[s], kb * BK, c.n0);
+#pragma unroll
+                    for (int h = 0; h < Cfg::N_HALVES; ++h)
+                        tma_load_2d(sB + s * Cfg::B_STAGE_BYTES + h * (Cfg::MMA_N * 128), &tmB,
+                                    &full_bar[s], kb * BK, c.n0 + h * Cfg::MMA_N);
                 }
             };
             for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
@@ -208,7 +215,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
-            constexpr uint32_t idesc = make_idesc_f16(BM, BN, 0, B_MN ? 1 : 0);
+            constexpr uint32_t idesc = make_idesc_f16(BM, Cfg::MMA_N, 0, B_MN ? 1 : 0);
             int it = 0, tile_iter = 0;
             bool ok = true;
             for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_iter) {
@@ -241,10 +248,15 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024, SWZ_128B);
                         // MN-major: 16 K-rows = two 8-row groups of 128 bytes (SBO 1024); the
                         // next 64-column atom sits BK * 128 bytes further (LBO).
-                        const uint64_t bd =
-                            B_MN ? make_smem_desc(b_addr + k * 2048, BK * 128, 1024, SWZ_128B)
-                                 : make_smem_desc(b_addr + k * 32, 16, 1024, SWZ_128B);
-                        mma_f16_ss(d_tmem, ad, bd, idesc, (i | k) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < Cfg::N_HALVES; ++h) {
+                            const uint32_t bh = b_addr + h * (Cfg::MMA_N * 128);
+                            const uint64_t bd =
+                                B_MN ? make_smem_desc(bh + k * 2048, BK * 128, 1024, SWZ_128B)
+                                     : make_smem_desc(bh + k * 32, 16, 1024, SWZ_128B);
+                            mma_f16_ss(d_tmem + h * Cfg::MMA_N, ad, bd, idesc,
+                                       (i | k) != 0 ? 1u : 0u);
+                        }
                     }
                     mma_commit(&empty_bar[s]);
                 }
@@ -578,7 +590,7 @@ int launch_cfg(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap
     return launch_cfg_epi<BN, STAGES, PERSIST, B_MN, 0>(tmA, tmB, tmY, args, zdim, stream);
 }
 
-int g_force_bn = 0;       // test hook: 0 = automatic, else 64 / 128 / 256
+int g_force_bn = 0;       // test hook: 0 = automatic, else 64 / 128 / 192 / 256 / 384
 int g_force_persist = -1;  // test hook: -1 = automatic, 0 = single-tile CTAs, 1 = persistent
 
 struct TilePlan {
@@ -593,6 +605,15 @@ TilePlan pick_plan(int M, int N, int K, int zdim) {
     const long mt = (M + BM - 1) / BM;
     auto tiles = [&](int bn) { return mt * ((N + bn - 1) / bn) * zdim; };
     TilePlan p;
+    // One 128 x 384 tile per CTA (two 192-column products per K step, 3 x 64 KB stages) covers
+    // 2048 x 3072 in one round of 128 CTAs.  Measured on B200 for FFN1 (2048 x 768 -> 3072, GELU):
+    // 13.6 us against 13.0 for two rounds of persistent 128 x 192 tiles - the 384-column GELU
+    // epilogue is exposed after the single round - so only the test hook selects it.
+    if (g_force_bn == 384) {
+        p.bn = 384;
+        p.persist = false;
+        return p;
+    }
     if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 192 || g_force_bn == 256) {
         p.bn = g_force_bn;
         p.persist = g_force_persist >= 0 ? g_force_persist != 0 : tiles(p.bn) > (p.bn == 256 ? sms : 2 * sms);
@@ -630,6 +651,10 @@ TilePlan pick_plan(int M, int N, int K, int zdim) {
     }
     if (g_force_persist >= 0) p.persist = g_force_persist != 0;
     return p;
+}
+
+long plan_tiles(int M, int N, int bn) {
+    return static_cast<long>((M + BM - 1) / BM) * ((N + bn - 1) / bn);
 }
 
 int g_force_pair = -1;  // test hook: -1 = automatic, 0 = never, 128 / 256 = always that width
@@ -689,6 +714,14 @@ int dispatch(const TilePlan& p, const CUtensorMap& tmA, const CUtensorMap& tmB,
              const CUtensorMap& tmY, const GemmArgs& args, int zdim, cudaStream_t stream) {
     if (p.bn == 192 && args.out_mode == OUT_TILE_F16 && !B_MN)
         return launch_cfg<192, 4, true, false>(tmA, tmB, tmY, args, zdim, stream);
+    if (p.bn == 384 && args.out_mode == OUT_TILE_F16 && !B_MN) {
+        // one 128 x 384 tile per CTA; only the compiled-in epilogues exist for this width
+        if (args.act == ET_ACT_GELU)
+            return launch_cfg_epi<384, 3, false, false, 1 + ET_ACT_GELU>(tmA, tmB, tmY, args, zdim, stream);
+        if (args.act == ET_ACT_RELU)
+            return launch_cfg_epi<384, 3, false, false, 1 + ET_ACT_RELU>(tmA, tmB, tmY, args, zdim, stream);
+        return launch_cfg_epi<384, 3, false, false, 1 + ET_ACT_NONE>(tmA, tmB, tmY, args, zdim, stream);
+    }
     if (p.persist) {
         if (p.bn == 256 && args.out_mode != OUT_PARTIAL_F32)
             return launch_cfg<256, 3, true, B_MN>(tmA, tmB, tmY, args, zdim, stream);
@@ -776,12 +809,13 @@ int launch_gemm_f16(const __half* X, int ldx, const __half* W, int ldw, const __
     // col_map[n]) keeps the coalesced tile store; only a true scatter needs per-element stores.
     const bool tile_store = col_map == nullptr || (!scatter && N % 8 == 0 && ldy % 8 == 0);
     TilePlan plan = pick_plan(M, N, K, 1);
-    if (plan.bn == 192 && !tile_store) plan.bn = 128;  // 192 exists for the tile store only
+    if (plan.bn == 384 && !tile_store) plan = TilePlan{128, plan_tiles(M, N, 128) > sm_count()};
+    if (plan.bn == 192 && !tile_store) plan.bn = 128;  // 192 and 384 exist for the tile store only
     const int bn = plan.bn;
     CUtensorMap tmA, tmB;
     int st;
     if ((st = encode_operand(&tmA, X, ldx, M, K, BM)) != ET_OK) return st;
-    if ((st = encode_operand(&tmB, W, ldw, N, K, bn)) != ET_OK) return st;
+    if ((st = encode_operand(&tmB, W, ldw, N, K, bn > 256 ? bn / 2 : bn)) != ET_OK) return st;
     CUtensorMap tmY = tmA;  // placeholder when the index-list epilogue is used
     if (tile_store) {
         const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
@@ -843,6 +877,7 @@ int launch_gemm_f16_grouped_kn(const __half* X, int ldx, const __half* W, const 
     if (ldx % 8 || K % 8 || N % 8 || groups > 65535) return ET_ERR_SHAPE;
     if (!device_error_word()) return ET_ERR_NO_DEVICE;
     TilePlan plan = pick_plan(M, N, K, groups);
+    if (plan.bn == 384) plan = TilePlan{128, plan_tiles(M, N, 128) * groups > sm_count()};
     if (plan.bn == 256 || plan.bn == 192) plan.bn = 128;
     const int bn = plan.bn;
     CUtensorMap tmA, tmB;

@@ -92,6 +92,16 @@ int launch_attention_units(const __half* Q, const __half* K, const __half* V, __
                            float scale, const int* unit_head, const int* unit_first, int n_units,
                            int blocks_per_unit, cudaStream_t stream);
 
+// Attention over every head, then out = Z W_O^T + bias with tile-CSR W_O (attention_fuse_o.cu);
+// Z [batch * seq, nhead * dh_v] receives the heads' outputs.  single_launch: one cooperative
+// kernel with per-block completion counters instead of the two stand-alone kernels.
+int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, const __half* mask,
+                            __half* Z, const int* o_row_ptr, const int* o_row_off,
+                            const __half* o_tiles, int o_nnz, const __half* o_bias, __half* out,
+                            int batch, int seq, int nhead, int dh_qk, int dh_v, int ldq, int ldk,
+                            int ldv, int emdim, int mask_kind, const int* valid_len, float scale,
+                            bool single_launch, cudaStream_t stream);
+
 // out = LN(X W^T + bias + resid) * gamma + beta in one kernel (gemm_ln.cu); N = 256 .. 1024 in
 // steps of 128.
 bool gemm_ln_applies(int M, int N, int K);

@@ -174,19 +174,45 @@ def test_fused_vo_attention(et, orc, cuda, batch, seq, nhead, dh, emdim, mask_ki
     assert torch.equal(out, out2), "head reduction must be deterministic"
 
 
-def test_attention_fuse_o(et, orc, cuda):
-    """Attention followed by the tile-CSR output projection in one call (kernel_fuseO.cu)."""
-    batch, seq, nhead, dh, em = 2, 128, 4, 64, 256
-    q, k, v = _qkv(et, 500, batch, seq, nhead, dh, dh)
-    wo = et.synth.prune_tiles(et.synth.normal(500, 4, (em, nhead * dh), 0.05), 500, 5, 0.6)
+@pytest.mark.parametrize("batch,seq,nhead,dh,em,mask_kind,sparsity", [
+    (1, 128, 12, 64, 768, 0, 0.8),    # the reference's own shape: one sequence, BERT-base heads
+    (2, 128, 4, 64, 256, 1, 0.6),
+    (3, 100, 4, 64, 256, 2, 0.6),     # token blocks of the projection span two sequences
+    (9, 16, 2, 32, 64, 0, 0.5),       # eight sequences per token block; heads narrower than a TMA box
+    (4, 512, 12, 64, 768, 1, 0.8),    # several query blocks per sequence, causal
+    (40, 128, 12, 64, 768, 2, 0.9),   # more work than CTAs resident at once
+    (2, 200, 3, 48, 144, 3, 0.5),     # ragged blocks, additive mask, 48-wide heads
+    (1, 128, 2, 64, 128, 0, 0.97),    # output block rows without any stored tile
+])
+def test_attention_fuse_o(et, orc, cuda, batch, seq, nhead, dh, em, mask_kind, sparsity):
+    """Attention and the tile-CSR output projection (kernel_fuseO.cu) as one cooperative kernel
+    and as two chained kernels: against the oracle, and bit for bit against each other."""
+    import torch
+    q, k, v = _qkv(et, 500 + seq, batch, seq, nhead, dh, dh)
+    wo = et.synth.prune_tiles(et.synth.normal(500, 4, (em, nhead * dh), 0.05), 500, 5, sparsity)
     bo = et.synth.normal(500, 6, (em,), 0.1)
     rp, ro, tiles = et.synth.dense_to_tile(wo)
-    out = et.attention_fuse_o(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), _dev(rp, cuda),
-                              _dev(ro, cuda), _dev(tiles, cuda), _dev(bo, cuda), batch, seq, nhead,
-                              dh, dh, em, 1)
+    vl = np.array([(37 * i + 5) % seq + 1 for i in range(batch)], dtype=np.int32)
+    mask = None
+    if mask_kind == 3:
+        mask = np.where(et.synth.normal(500, 7, (seq, seq), 1.0).astype(np.float32) > 0.8,
+                        -np.inf, 0.0).astype(np.float16)
+        mask[np.arange(seq), np.arange(seq)] = 0
+    d = lambda a: None if a is None else _dev(a, cuda)
+    args = (d(q), d(k), d(v), d(rp), d(ro), d(tiles), d(bo), batch, seq, nhead, dh, dh, em,
+            mask_kind, d(mask), d(vl) if mask_kind == 2 else None)
+    out = et.attention_fuse_o(*args, single_launch=True)
     assert et.device_error() == 0
-    z = orc.round_fp16(orc.attention(q, k, v, batch, seq, nhead, dh, dh, 1))
-    assert_close(out.float().cpu().numpy(), orc.linear_dense(z, wo, bo), "attention + tile O")
+    again = et.attention_fuse_o(*args, single_launch=True)  # the counters are zero again after a call
+    assert et.device_error() == 0
+    two = et.attention_fuse_o(*args)
+    assert et.device_error() == 0
+    assert torch.equal(out, two), "one kernel and two kernels must agree bit for bit"
+    assert torch.equal(out, again)
+    z = orc.round_fp16(orc.attention(q, k, v, batch, seq, nhead, dh, dh, mask_kind, mask,
+                                     vl if mask_kind == 2 else None))
+    assert_close(out.float().cpu().numpy(), orc.linear_dense(z, wo, bo),
+                 f"attention + tile O b{batch} s{seq} m{mask_kind}")
 
 
 @pytest.mark.parametrize("batch,seq,hidden,nhead", [

@@ -26,7 +26,7 @@ def _case(et, seed, T, inn, out, std=0.05):
     return x, w, b
 
 
-@pytest.mark.parametrize("bn", [0, 64, 128, 192, 256])
+@pytest.mark.parametrize("bn", [0, 64, 128, 192, 256, 384])
 @pytest.mark.parametrize("T,inn,out,act", [
     (128, 64, 128, 0), (256, 768, 768, 0), (2048, 768, 2304, 0), (512, 768, 3072, 2),
     (512, 3072, 768, 0), (100, 80, 48, 1), (1, 16, 16, 0), (333, 1024, 1008, 2),
