@@ -250,7 +250,7 @@ def main():
     ap.add_argument("--tile-only", action="store_true",
                     help="launch the tile-pruned Linear alone (2048 x 768 -> 3072, 80 %% of the "
                          "tiles pruned, three times) and exit: the small case profilers capture")
-    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "tile_qkv", "layer"],
+    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "tile_qkv", "fuse_o", "layer"],
                     help="launch one more small case three times and exit (for profilers): fused V.O "
                          "attention, the CTA-pair GEMM at 8192^3, skip-LayerNorm, the 1x16 vector "
                          "kernel, the column-pruned Linear (gather + GEMM), a tile-pruned Q/K/V projection "
@@ -334,6 +334,13 @@ def main():
             pk = et.PackedTiles(*et.synth.dense_to_tile(W), HIDDEN, 3 * HIDDEN, dev)
             x = rnd(1, (T, HIDDEN))
             fn = lambda: et.linear_tile_packed(x, pk, None, et.ACT_NONE)
+        elif args.only == "fuse_o":  # attention + 80 %-pruned O projection, one cooperative kernel
+            qkv = rnd(1, (T, 3 * HIDDEN))
+            Wo = et.synth.prune_tiles(et.synth.normal_fast(1, 45, (HIDDEN, HIDDEN), 0.02), 1, 46, 0.8)
+            rp_o, ro_o, tl_o = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_tile(Wo))
+            fn = lambda: et.attention_fuse_o(qkv[:, :HIDDEN], qkv[:, HIDDEN:2 * HIDDEN],
+                                             qkv[:, 2 * HIDDEN:], rp_o, ro_o, tl_o, None, BATCH, SEQ,
+                                             NHEAD, 64, 64, HIDDEN, single_launch=True)
         elif args.only == "col":   # 8192 x 3072 -> 768, half of the input columns kept
             W = et.synth.normal_fast(1, 2, (HIDDEN, FF), 0.02)
             ids = et.synth.choose_ids(1, 3, FF, 0.5)
@@ -577,6 +584,20 @@ def main():
             sec = time_kernel([lambda i=i: et.skip_layernorm(a[i], a[i], g, g, out=o[i])
                                for i in range(4 * NSETS)], rounds=2)
             per_kernel["skip_layernorm"] = {"us": sec * 1e6, "gbs": 6.0 * T * HIDDEN / sec * 1e-9}
+            # attention + tile-pruned output projection (80 % of W_O's tiles pruned): one
+            # cooperative kernel against the two kernels chained by dependent launch
+            qkv = [rnd(70 + i, (T, 3 * HIDDEN), 1.0) for i in range(NSETS)]
+            Wo = et.synth.prune_tiles(et.synth.normal_fast(1, 45, (HIDDEN, HIDDEN), 0.02), 1, 46, 0.8)
+            rp_o, ro_o, tl_o = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_tile(Wo))
+            fo = {}
+            for single in (True, False):
+                fo[single] = time_kernel([lambda i=i: et.attention_fuse_o(
+                    qkv[i][:, :HIDDEN], qkv[i][:, HIDDEN:2 * HIDDEN], qkv[i][:, 2 * HIDDEN:], rp_o, ro_o,
+                    tl_o, bqz[:HIDDEN], BATCH, SEQ, NHEAD, 64, 64, HIDDEN, single_launch=single)
+                    for i in range(NSETS)]) * 1e6
+            per_kernel["attention_fuse_o_tile80"] = {
+                "single_cooperative_launch_us": fo[True], "two_chained_kernels_us": fo[False],
+                "product_path": "two chained kernels"}
             per_kernel["note"] = ("each kernel timed inside one CUDA graph that rotates over buffer "
                                   "sets larger than L2")
             del a, w, y, qkv, z, o
