@@ -55,6 +55,7 @@ struct FuseOArgs {
     int T, in, out;
     int* done;    // [batch][nqb] counters, zero at launch; the last CTA to finish zeroes them
     int* exited;  // CTAs that have finished, zero at launch
+    int* ticket;  // next piece of work to hand out, zero at launch
     int n_done;   // batch * nqb
     int nqb;      // 128-query blocks per sequence
     int n_att;    // batch * nqb * nhead attention units
@@ -93,6 +94,7 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     __shared__ int s_last;
+    __shared__ int s_ticket;
     volatile int* abort_flag = &s_abort;
     const int warp = threadIdx.x >> 5;
 
@@ -106,44 +108,54 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     tc_fence_after_sync();
     const uint32_t tmem_base = s_tmem;
 
-    // ---------------- phase 1: attention units, heads of one query block next to each other
-    for (int u = blockIdx.x; u < f.n_att && !*abort_flag; u += gridDim.x) {
-        const int h = u % a.nhead;
-        const int rest = u / a.nhead;
-        int qb = rest % f.nqb;
-        const int b = rest / f.nqb;
-        // causal: a sequence's last query blocks have the most key blocks and go first
-        if (MASK == ET_MASK_CAUSAL) qb = f.nqb - 1 - qb;
-        attention_cta<MASK, true>(tmQ, tmK, tmV, tmZ, a, smem, qb * BQ, h, b, tmem_base, abort_flag);
-        // (the body ends with a CTA-wide barrier after its stores to Z have completed)
-        if (threadIdx.x == 0 && !*abort_flag) {
-            __threadfence();
-            atomicAdd(f.done + b * f.nqb + qb, 1);
-        }
-    }
+    pdl_launch_dependents();
+    pdl_wait();  // Q, K, V come from earlier kernels; Z and out may still be read by them
 
-    // ---------------- phase 2: projection items, in the order their inputs become ready
-    for (int i = blockIdx.x; i < f.n_items; i += gridDim.x) {
-        const int panel0 = i % f.npanel;
-        const int m0 = (i / f.npanel) * TBM;
-        if (threadIdx.x == 0 && !*abort_flag) {
-            const int t1 = m0 + TBM < f.T ? m0 + TBM : f.T;
-            bool ok = true;
-            for (int b = m0 / a.seq; ok && b <= (t1 - 1) / a.seq; ++b) {
-                const int lo = m0 - b * a.seq > 0 ? m0 - b * a.seq : 0;
-                const int hi = t1 - b * a.seq < a.seq ? t1 - b * a.seq : a.seq;
-                for (int qb = lo / BQ; ok && qb <= (hi - 1) / BQ; ++qb)
-                    ok = wait_count(f.done + b * f.nqb + qb, a.nhead, abort_flag, a.err_word);
-            }
-            if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_FUSE_O);
-            fence_proxy_async_all();
-        }
+    // Work is handed out by ticket: attention units first (heads of one query block next to
+    // each other), then projection items in the order their inputs become ready.
+    const int n_work = f.n_att + f.n_items;
+    for (;;) {
+        if (threadIdx.x == 0) s_ticket = atomicAdd(f.ticket, 1);
         __syncthreads();
-        if (*abort_flag) break;
-        linear_tile_cta<false, ET_ACT_NONE, 1, true>(tmX, tmW, tmY, f.row_ptr, f.row_off, nullptr,
-                                                    nullptr, f.tiles, f.bias, f.T, f.in, f.out,
-                                                    a.err_word, smem, panel0, m0, tmem_base,
-                                                    abort_flag);
+        const int t = s_ticket;
+        if (t >= n_work || *abort_flag) break;
+        if (t < f.n_att) {
+            const int h = t % a.nhead;
+            const int rest = t / a.nhead;
+            int qb = rest % f.nqb;
+            const int b = rest / f.nqb;
+            // causal: a sequence's last query blocks have the most key blocks and go first
+            if (MASK == ET_MASK_CAUSAL) qb = f.nqb - 1 - qb;
+            attention_cta<MASK, true>(tmQ, tmK, tmV, tmZ, a, smem, qb * BQ, h, b, tmem_base,
+                                      abort_flag);
+            // (the body ends with a CTA-wide barrier after its stores to Z have completed)
+            if (threadIdx.x == 0 && !*abort_flag) {
+                __threadfence();
+                atomicAdd(f.done + b * f.nqb + qb, 1);
+            }
+        } else {
+            const int i = t - f.n_att;
+            const int panel0 = i % f.npanel;
+            const int m0 = (i / f.npanel) * TBM;
+            if (threadIdx.x == 0) {
+                const int t1 = m0 + TBM < f.T ? m0 + TBM : f.T;
+                bool ok = true;
+                for (int b = m0 / a.seq; ok && b <= (t1 - 1) / a.seq; ++b) {
+                    const int lo = m0 - b * a.seq > 0 ? m0 - b * a.seq : 0;
+                    const int hi = t1 - b * a.seq < a.seq ? t1 - b * a.seq : a.seq;
+                    for (int qb = lo / BQ; ok && qb <= (hi - 1) / BQ; ++qb)
+                        ok = wait_count(f.done + b * f.nqb + qb, a.nhead, abort_flag, a.err_word);
+                }
+                if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_FUSE_O);
+                fence_proxy_async_all();
+            }
+            __syncthreads();
+            if (*abort_flag) break;
+            linear_tile_cta<false, ET_ACT_NONE, 1, true>(tmX, tmW, tmY, f.row_ptr, f.row_off, nullptr,
+                                                        nullptr, f.tiles, f.bias, f.T, f.in, f.out,
+                                                        a.err_word, smem, panel0, m0, tmem_base,
+                                                        abort_flag);
+        }
     }
 
     tc_fence_before_sync();
@@ -159,7 +171,10 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     __syncthreads();
     if (s_last) {
         for (int i = threadIdx.x; i < f.n_done; i += ATT_THREADS) f.done[i] = 0;
-        if (threadIdx.x == 0) *f.exited = 0;
+        if (threadIdx.x == 0) {
+            *f.exited = 0;
+            *f.ticket = 0;
+        }
     }
 }
 
@@ -168,7 +183,7 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 // zero again at the end of every launch.  Calls take the slots in turn, so up to FUSE_SLOTS
 // calls may be in flight on one GPU (in different streams) at once.
 constexpr int FUSE_SLOTS = 16;
-constexpr int FUSE_SLOT_INTS = 4096;  // batch * ceil(seq / 128) must stay below this
+constexpr int FUSE_SLOT_INTS = 4096;  // batch * ceil(seq / 128) + 2 may not exceed this
 static __device__ int g_fuse_o_done[FUSE_SLOTS * FUSE_SLOT_INTS];
 
 int* fuse_o_counters() {
@@ -199,7 +214,7 @@ int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, c
     // Without a stored tile there is no projection to fuse; beyond the counter array the two
     // stand-alone kernels do the work.
     const bool fused = single_launch && o_nnz > 0 && batch > 0 && seq > 0 && nhead > 0 &&
-                       dh_v > 0 && dh_v % 16 == 0 && batch * nqb_l < FUSE_SLOT_INTS &&
+                       dh_v > 0 && dh_v % 16 == 0 && batch * nqb_l < FUSE_SLOT_INTS - 1 &&
                        vdim_l <= MAX_IN;
     if (!fused) {
         int st = launch_attention(Q, K, V, Z, batch, seq, nhead, dh_qk, dh_v, ldq, ldk, ldv,
@@ -298,6 +313,7 @@ int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, c
     f.n_items = f.npanel * ((T + TBM - 1) / TBM);
     f.done = counters + (g_next_slot.fetch_add(1, std::memory_order_relaxed) % FUSE_SLOTS) * FUSE_SLOT_INTS;
     f.exited = f.done + FUSE_SLOT_INTS - 1;
+    f.ticket = f.done + FUSE_SLOT_INTS - 2;
     f.n_done = batch * nqb;
 
     const int att_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + EXTRA_BYTES;
@@ -313,32 +329,16 @@ int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, c
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      smem_bytes) != cudaSuccess)
                 return ET_ERR_CUDA;
-            // two CTAs per SM need the largest shared-memory carve-out
-            cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared);
             attr_bytes[slot][dev] = smem_bytes;
         }
-        // every CTA must be resident at once: the grid is what the device holds, at most
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, ATT_THREADS, smem_bytes) !=
-                cudaSuccess ||
-            per_sm <= 0)
-            return ET_ERR_CUDA;
+        // two CTAs fit an SM (registers, shared memory, 256 of the 512 tensor-memory columns
+        // each); more CTAs than that would only queue behind them
         const int sms = sm_count() > 0 ? sm_count() : 148;
-        const long want = f.n_att > f.n_items ? f.n_att : f.n_items;
-        const long cap = static_cast<long>(per_sm) * sms;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(want < cap ? want : cap));
-        cfg.blockDim = dim3(ATT_THREADS);
-        cfg.dynamicSmemBytes = smem_bytes;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeCooperative;
-        attr[0].val.cooperative = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        count_launch();
-        return cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmZ, a, tmX, tmW, tmY, f) == cudaSuccess
+        const long want = static_cast<long>(f.n_att) + f.n_items;
+        const long cap = 2L * sms;
+        return launch_kernel(kern, dim3(static_cast<unsigned>(want < cap ? want : cap)),
+                             dim3(ATT_THREADS), smem_bytes, stream, tmQ, tmK, tmV, tmZ, a, tmX, tmW,
+                             tmY, f) == cudaSuccess
                    ? ET_OK
                    : ET_ERR_CUDA;
     };
