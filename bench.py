@@ -334,7 +334,7 @@ def main():
             pk = et.PackedTiles(*et.synth.dense_to_tile(W), HIDDEN, 3 * HIDDEN, dev)
             x = rnd(1, (T, HIDDEN))
             fn = lambda: et.linear_tile_packed(x, pk, None, et.ACT_NONE)
-        elif args.only == "fuse_o":  # attention + 80 %-pruned O projection, one cooperative kernel
+        elif args.only == "fuse_o":  # attention + 80 %-pruned O projection in one kernel
             qkv = rnd(1, (T, 3 * HIDDEN))
             Wo = et.synth.prune_tiles(et.synth.normal_fast(1, 45, (HIDDEN, HIDDEN), 0.02), 1, 46, 0.8)
             rp_o, ro_o, tl_o = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_tile(Wo))
@@ -585,7 +585,8 @@ def main():
                                for i in range(4 * NSETS)], rounds=2)
             per_kernel["skip_layernorm"] = {"us": sec * 1e6, "gbs": 6.0 * T * HIDDEN / sec * 1e-9}
             # attention + tile-pruned output projection (80 % of W_O's tiles pruned): one
-            # cooperative kernel against the two kernels chained by dependent launch
+            # kernel (work tickets and completion counters) against the two kernels chained by
+            # dependent launch
             qkv = [rnd(70 + i, (T, 3 * HIDDEN), 1.0) for i in range(NSETS)]
             Wo = et.synth.prune_tiles(et.synth.normal_fast(1, 45, (HIDDEN, HIDDEN), 0.02), 1, 46, 0.8)
             rp_o, ro_o, tl_o = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_tile(Wo))
@@ -596,7 +597,7 @@ def main():
                     tl_o, bqz[:HIDDEN], BATCH, SEQ, NHEAD, 64, 64, HIDDEN, single_launch=single)
                     for i in range(NSETS)]) * 1e6
             per_kernel["attention_fuse_o_tile80"] = {
-                "single_cooperative_launch_us": fo[True], "two_chained_kernels_us": fo[False],
+                "single_launch_us": fo[True], "two_chained_kernels_us": fo[False],
                 "product_path": "two chained kernels"}
             per_kernel["note"] = ("each kernel timed inside one CUDA graph that rotates over buffer "
                                   "sets larger than L2")

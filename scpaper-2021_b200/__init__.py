@@ -371,7 +371,7 @@ def attention_fuse_o(q, k, v, o_row_ptr, o_row_off, o_tiles, o_bias, batch, seq,
                      dh_v, emdim, mask_kind=MASK_NONE, mask=None, valid_len=None, scale=None,
                      single_launch=False):
     """Attention + tile-CSR output projection (Attention/kernel_fuseO.cu:254-290);
-    single_launch=True runs both in one cooperative kernel."""
+    single_launch=True runs both in one kernel."""
     z = _empty((batch * seq, nhead * dh_v), q)
     out = _empty((batch * seq, emdim), q)
     scale = (1.0 / dh_qk ** 0.5) if scale is None else scale

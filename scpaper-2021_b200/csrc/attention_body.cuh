@@ -519,7 +519,7 @@ __device__ __forceinline__ void attention_cta(const CUtensorMap& tmQ, const CUte
             tma_store_commit();
             if (FUSED) {
                 tma_store_wait_all();  // complete in global memory, not only read out
-                fence_proxy_async_all();
+                fence_proxy_async_global();
             }
             else tma_store_wait_read();
         }

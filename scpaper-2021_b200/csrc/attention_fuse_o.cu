@@ -2,35 +2,44 @@
 //
 // Stands in for the cooperative kernel of Attention/kernel_fuseO.cu:138-243, which runs every
 // head's attention, a grid-wide barrier and then the tile SpMM over Z.  Here the grid-wide
-// barrier is replaced by one counter per (sequence, 128-query block):
+// barrier is replaced by one counter per (sequence, 128-query block) and work is handed out by
+// ticket (one global counter):
 //
-//   phase 1  every CTA walks its share of the (sequence, query block, head) attention units
-//            (attention_cta, the body of the stand-alone attention kernel), and after each unit -
-//            once the unit's rows of Z are complete in global memory - adds one to the counter
-//            of the unit's (sequence, query block);
-//   phase 2  every CTA walks its share of the (128-token block, panel of 128 output features)
-//            items of the projection (linear_tile_cta, the body of the stand-alone tile Linear):
-//            one thread waits until the counters of the query blocks that overlap the token
-//            block have reached the number of heads, then the item runs with Z as its input.
+//   tickets 0 .. n_att - 1   the (sequence, query block, head) attention units (attention_cta,
+//            the body of the stand-alone attention kernel).  After a unit - once its rows of Z
+//            are complete in global memory - the CTA adds one to the counter of the unit's
+//            (sequence, query block);
+//   tickets n_att ..         the (128-token block, panel of 128 output features) items of the
+//            projection (linear_tile_cta, the body of the stand-alone tile Linear).  An item
+//            builds its index tables, then one thread waits until the counters of the query
+//            blocks that overlap the token block have reached the number of heads, then the
+//            item runs with Z as its input.
 //
 // A projection item therefore starts as soon as ITS rows of Z exist, while other CTAs are
-// still busy with other sequences' heads; no CTA ever waits during phase 1, and the launch is
-// cooperative (every CTA resident at once), so every counter is reached.  The wait is bounded:
-// when it runs out the kernel reports DEV_TIMEOUT_FUSE_O and skips the remaining items.
+// still busy with other sequences' heads.  Forward progress needs no co-residency guarantee:
+// a CTA takes a ticket only while it runs, attention units never wait, and an item waits only
+// for attention units, all of which have lower tickets - i.e. have already been taken by
+// running CTAs - by the time any item ticket is handed out.  (A cooperative launch is not
+// used: the driver admits one CTA per SM to a cooperative launch of any kernel that allocates
+// tensor memory - cudaOccupancyMaxActiveBlocksPerMultiprocessor returns 1 whatever the
+// registers and shared memory - and both bodies are built for two co-resident CTAs per SM that
+// overlap each other's phases; a first, cooperative form of this kernel took twice the time.)
+// The wait is bounded: when it runs out the kernel reports DEV_TIMEOUT_FUSE_O and abandons
+// the remaining work.  The last CTA to leave zeroes the counters, so a launch needs no memset.
 //
-// Standing (measured on B200, 80 % of W_O's tiles pruned, BERT-base heads, calls replayed back to
-// back from a CUDA graph): the driver admits ONE CTA per SM to a cooperative launch of any kernel
-// that allocates tensor memory (cudaOccupancyMaxActiveBlocksPerMultiprocessor returns 1 for both
-// bodies whatever their registers and shared memory; launched on their own, two CTAs of either
-// body share an SM and overlap each other's phases).  With half the CTAs per SM this kernel
-// takes 19.5 / 26.5 / 73 us at 1 / 16 / 64 sequences of 128 tokens and 183 us at 32 x 512,
-// against 13.7 / 15.5 / 39 / 100 us for the two stand-alone kernels chained by programmatic
-// dependent launch, which also hides the second launch.  et_attention_fuse_o_fwd therefore runs
-// the two kernels; this kernel is et_attention_fuse_o_single_launch_fwd.
+// Z travels through global memory (L2) between the two kinds of work, written and read by TMA:
+// the writer waits for its bulk stores to complete, fences the async proxy and releases at GPU
+// scope; the reader acquires at GPU scope and fences the async proxy before its loads.
 //
-// Z travels through global memory (L2) between the phases, written and read by TMA: the writer
-// waits for its bulk stores to complete, fences the async proxy and releases at GPU scope; the
-// reader acquires at GPU scope and fences the async proxy before its loads.
+// Standing (measured on B200, 80 % of W_O's tiles pruned, 12 heads of 64, calls replayed back to
+// back from a CUDA graph; one kernel / the two stand-alone kernels chained by programmatic
+// dependent launch): 1 x 128 tokens 17.2 / 13.7 us, 16 x 128 20.1 / 15.6, 64 x 128 43.1 / 39.3,
+// 4 x 512 causal 27.5 / 23.8, 32 x 512 103.3 / 99.1, 1 x 4096 121.2 / 120.4.  Inside the kernel
+// the two kinds of work take what the stand-alone kernels take; what is left is the ticket and
+// counter traffic (a global atomic before each piece of work, bulk-store completion, fence and
+// atomic after each attention unit) and the counter clean-up at the end, none of which a
+// dependent launch pays.  et_attention_fuse_o_fwd therefore runs the two kernels; this kernel
+// is et_attention_fuse_o_single_launch_fwd.
 #include <atomic>
 
 #include "attention_body.cuh"
@@ -56,6 +65,7 @@ struct FuseOArgs {
     int* done;    // [batch][nqb] counters, zero at launch; the last CTA to finish zeroes them
     int* exited;  // CTAs that have finished, zero at launch
     int* ticket;  // next piece of work to hand out, zero at launch
+    unsigned long long* trace;  // bring-up builds: [ticket][4] = start ns, end ns, SM, CTA (else null)
     int n_done;   // batch * nqb
     int nqb;      // 128-query blocks per sequence
     int n_att;    // batch * nqb * nhead attention units
@@ -95,6 +105,7 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     __shared__ int s_abort;
     __shared__ int s_last;
     __shared__ int s_ticket;
+    __shared__ unsigned long long s_t0;
     volatile int* abort_flag = &s_abort;
     const int warp = threadIdx.x >> 5;
 
@@ -106,37 +117,68 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem_base = s_tmem;
-
-    pdl_launch_dependents();
-    pdl_wait();  // Q, K, V come from earlier kernels; Z and out may still be read by them
 
     // Work is handed out by ticket: attention units first (heads of one query block next to
-    // each other), then projection items in the order their inputs become ready.
-    const int n_work = f.n_att + f.n_items;
-    for (;;) {
-        if (threadIdx.x == 0) s_ticket = atomicAdd(f.ticket, 1);
+    // each other), then projection items in the order their inputs become ready.  The two kinds
+    // of work have loops of their own (in one loop the compiler spills registers in both bodies),
+    // and nothing but the ticket, in shared memory, lives across a piece of work.
+    const volatile int* ticket = &s_ticket;
+    auto take_ticket = [&]() {
+        if (threadIdx.x == 0) {
+            s_ticket = atomicAdd(f.ticket, 1);
+            if (f.trace) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(s_t0));
+        }
         __syncthreads();
-        const int t = s_ticket;
-        if (t >= n_work || *abort_flag) break;
-        if (t < f.n_att) {
+    };
+    auto trace_done = [&]() {
+        if (f.trace && threadIdx.x == 0) {
+            unsigned long long t_end;
+            unsigned smid;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            unsigned long long* rec = f.trace + 4 * static_cast<size_t>(*ticket);
+            rec[0] = s_t0;
+            rec[1] = t_end;
+            rec[2] = smid;
+            rec[3] = blockIdx.x;
+        }
+    };
+
+    pdl_launch_dependents();
+    // Q, K, V come from earlier kernels, Z and out may still be read by them - and an earlier
+    // launch that uses the same counters must have left them at zero before a ticket is taken
+    // (kernels launched as dependents start before their predecessors finish).
+    pdl_wait();
+    take_ticket();
+    while (*ticket < f.n_att && !*abort_flag) {
+        {
+            const int t = *ticket;
             const int h = t % a.nhead;
             const int rest = t / a.nhead;
             int qb = rest % f.nqb;
-            const int b = rest / f.nqb;
             // causal: a sequence's last query blocks have the most key blocks and go first
             if (MASK == ET_MASK_CAUSAL) qb = f.nqb - 1 - qb;
-            attention_cta<MASK, true>(tmQ, tmK, tmV, tmZ, a, smem, qb * BQ, h, b, tmem_base,
+            attention_cta<MASK, true>(tmQ, tmK, tmV, tmZ, a, smem, qb * BQ, h, rest / f.nqb, s_tmem,
                                       abort_flag);
-            // (the body ends with a CTA-wide barrier after its stores to Z have completed)
-            if (threadIdx.x == 0 && !*abort_flag) {
-                __threadfence();
-                atomicAdd(f.done + b * f.nqb + qb, 1);
-            }
-        } else {
-            const int i = t - f.n_att;
-            const int panel0 = i % f.npanel;
-            const int m0 = (i / f.npanel) * TBM;
+        }
+        // (the body ends with a CTA-wide barrier after its stores to Z have completed)
+        if (threadIdx.x == 0 && !*abort_flag) {
+            const int rest = *ticket / a.nhead;
+            int qb = rest % f.nqb;
+            if (MASK == ET_MASK_CAUSAL) qb = f.nqb - 1 - qb;
+            __threadfence();
+            atomicAdd(f.done + (rest / f.nqb) * f.nqb + qb, 1);
+        }
+        trace_done();
+        take_ticket();
+    }
+    // the ticket in hand is the CTA's first projection item (or past the end)
+    while (*ticket < f.n_att + f.n_items && !*abort_flag) {
+        const int i = *ticket - f.n_att;
+        const int m0 = (i / f.npanel) * TBM;
+        // called inside the item once its index tables are built: one thread waits for the
+        // query blocks the token block overlaps, then every thread passes the barrier
+        auto wait_inputs = [&]() {
             if (threadIdx.x == 0) {
                 const int t1 = m0 + TBM < f.T ? m0 + TBM : f.T;
                 bool ok = true;
@@ -147,20 +189,21 @@ attention_fuse_o_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                         ok = wait_count(f.done + b * f.nqb + qb, a.nhead, abort_flag, a.err_word);
                 }
                 if (!ok) report_error(a.err_word, abort_flag, DEV_TIMEOUT_FUSE_O);
-                fence_proxy_async_all();
+                fence_proxy_async_global();
             }
             __syncthreads();
-            if (*abort_flag) break;
-            linear_tile_cta<false, ET_ACT_NONE, 1, true>(tmX, tmW, tmY, f.row_ptr, f.row_off, nullptr,
-                                                        nullptr, f.tiles, f.bias, f.T, f.in, f.out,
-                                                        a.err_word, smem, panel0, m0, tmem_base,
-                                                        abort_flag);
-        }
+        };
+        linear_tile_cta<false, ET_ACT_NONE, 1, true>(tmX, tmW, tmY, f.row_ptr, f.row_off, nullptr,
+                                                    nullptr, f.tiles, f.bias, f.T, f.in, f.out,
+                                                    a.err_word, smem, i % f.npanel, m0, s_tmem,
+                                                    abort_flag, wait_inputs);
+        trace_done();
+        take_ticket();
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, a.tmem_cols);
+    if (warp == 1) tmem_dealloc(s_tmem, a.tmem_cols);
 
     // The last CTA to get here leaves the counters as it found them (every other CTA is past
     // its last wait), also when the run was abandoned after an error.
@@ -199,6 +242,7 @@ int* fuse_o_counters() {
 }
 
 std::atomic<unsigned> g_next_slot{0};
+unsigned long long* g_fuse_o_trace = nullptr;  // test hook
 
 }  // namespace
 
@@ -314,6 +358,7 @@ int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, c
     f.done = counters + (g_next_slot.fetch_add(1, std::memory_order_relaxed) % FUSE_SLOTS) * FUSE_SLOT_INTS;
     f.exited = f.done + FUSE_SLOT_INTS - 1;
     f.ticket = f.done + FUSE_SLOT_INTS - 2;
+    f.trace = g_fuse_o_trace;
     f.n_done = batch * nqb;
 
     const int att_bytes = (2 * nqa + nva + 2) * ATOM_BYTES + EXTRA_BYTES;
@@ -353,6 +398,12 @@ int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, c
 }  // namespace et
 
 extern "C" {
+
+#ifdef ET_TEST_HOOKS
+// Test hook: device array of 4 x (work items) 64-bit words that receives each item's start and
+// end time (ns), SM and CTA; null switches the trace off.
+void et_debug_set_fuse_o_trace(void* p) { et::g_fuse_o_trace = static_cast<unsigned long long*>(p); }
+#endif  // ET_TEST_HOOKS
 
 int et_attention_fuse_o_fwd(const et_half* Q, const et_half* K, const et_half* V,
                             const et_half* mask, et_half* Z, const int32_t* o_row_ptr,

@@ -260,10 +260,10 @@ __device__ __forceinline__ void tma_store_wait_read() {
 __device__ __forceinline__ void tma_store_wait_all() {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
-// Orders accesses of the generic proxy (plain loads, stores and atomics) and of the async proxy
-// (TMA) of this thread against each other, in both directions, for every state space.
-__device__ __forceinline__ void fence_proxy_async_all() {
-    asm volatile("fence.proxy.async;" ::: "memory");
+// Orders this thread's accesses to global memory through the generic proxy (plain loads, stores
+// and atomics) and through the async proxy (TMA) against each other, in both directions.
+__device__ __forceinline__ void fence_proxy_async_global() {
+    asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 // Waits until at most N of this thread's bulk store groups still read their shared memory.
 template <int N>

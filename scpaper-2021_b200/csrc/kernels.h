@@ -93,8 +93,8 @@ int launch_attention_units(const __half* Q, const __half* K, const __half* V, __
                            int blocks_per_unit, cudaStream_t stream);
 
 // Attention over every head, then out = Z W_O^T + bias with tile-CSR W_O (attention_fuse_o.cu);
-// Z [batch * seq, nhead * dh_v] receives the heads' outputs.  single_launch: one cooperative
-// kernel with per-block completion counters instead of the two stand-alone kernels.
+// Z [batch * seq, nhead * dh_v] receives the heads' outputs.  single_launch: one kernel with
+// work tickets and per-block completion counters instead of the two stand-alone kernels.
 int launch_attention_fuse_o(const __half* Q, const __half* K, const __half* V, const __half* mask,
                             __half* Z, const int* o_row_ptr, const int* o_row_off,
                             const __half* o_tiles, int o_nnz, const __half* o_bias, __half* out,

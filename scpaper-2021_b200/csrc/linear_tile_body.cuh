@@ -65,15 +65,20 @@ constexpr int MAX_IN = 8192;
 // the abort flag and takes part in programmatic dependent launch.
 // FUSED == true: one of several pieces of work a CTA runs in turn - tensor memory (tmem_in) and
 // the abort flag (abort_in) belong to the caller, the activations may have been written by
-// other CTAs of the same grid (the caller has observed their completion), and the barriers are
-// invalidated at the end so that the next piece of work may lay out shared memory afresh.
-template <bool PACKED, int ACT, int NP, bool FUSED>
+// other CTAs of the same grid - wait_inputs(), called by every thread once the index tables
+// (weights only) are built, returns when they are complete - and the barriers are invalidated
+// at the end so that the next piece of work may lay out shared memory afresh.
+struct NoInputWait {
+    __device__ __forceinline__ void operator()() const {}
+};
+template <bool PACKED, int ACT, int NP, bool FUSED, typename WaitFn = NoInputWait>
 __device__ __forceinline__ void linear_tile_cta(
     const CUtensorMap& tmX, const CUtensorMap& tmW, const CUtensorMap& tmY,
     const int* __restrict__ row_ptr, const int* __restrict__ row_off,
     const uint32_t* __restrict__ pk_mask, const int* __restrict__ pk_off,
     const __half* __restrict__ pk_tiles, const __half* __restrict__ bias, int T, int in, int out,
-    int* err_word, uint8_t* smem, int panel0, int m0, uint32_t tmem_in, volatile int* abort_in) {
+    int* err_word, uint8_t* smem, int panel0, int m0, uint32_t tmem_in, volatile int* abort_in,
+    WaitFn wait_inputs = WaitFn()) {
     static_assert(NP == 1 || PACKED, "two panels per CTA exist for packed weights only");
     const int nbc = in >> 4;  // input block columns
     const int nchunk = (in + CHUNK - 1) / CHUNK;
@@ -190,6 +195,8 @@ __device__ __forceinline__ void linear_tile_cta(
     if (!FUSED) {
         pdl_launch_dependents();
         pdl_wait();  // the tables above are weights; activations and Y need the wait
+    } else {
+        wait_inputs();
     }
 
     // all panels' masks of one chunk
@@ -211,9 +218,9 @@ __device__ __forceinline__ void linear_tile_cta(
         // incrementally (no divisions on the path).
         int s = 0, issued = 0;
         uint32_t ph = 0;
-        // activations written by other CTAs of this grid: the caller's acquire comes before
-        // this thread's TMA reads
-        if (FUSED) fence_proxy_async_all();
+        // activations written by other CTAs of this grid: the acquire in wait_inputs() comes
+        // before the TMA reads of the threads that fetch activation slabs
+        if (FUSED && lane == 0) fence_proxy_async_global();
         if (PACKED) {
             if (lane == 0) {
                 for (int kc = 0; kc < nchunk; ++kc) {

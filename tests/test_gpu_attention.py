@@ -180,13 +180,13 @@ def test_fused_vo_attention(et, orc, cuda, batch, seq, nhead, dh, emdim, mask_ki
     (3, 100, 4, 64, 256, 2, 0.6),     # token blocks of the projection span two sequences
     (9, 16, 2, 32, 64, 0, 0.5),       # eight sequences per token block; heads narrower than a TMA box
     (4, 512, 12, 64, 768, 1, 0.8),    # several query blocks per sequence, causal
-    (40, 128, 12, 64, 768, 2, 0.9),   # more work than CTAs resident at once
+    (40, 128, 12, 64, 768, 2, 0.9),   # more pieces of work than CTAs
     (2, 200, 3, 48, 144, 3, 0.5),     # ragged blocks, additive mask, 48-wide heads
     (1, 128, 2, 64, 128, 0, 0.97),    # output block rows without any stored tile
 ])
 def test_attention_fuse_o(et, orc, cuda, batch, seq, nhead, dh, em, mask_kind, sparsity):
-    """Attention and the tile-CSR output projection (kernel_fuseO.cu) as one cooperative kernel
-    and as two chained kernels: against the oracle, and bit for bit against each other."""
+    """Attention and the tile-CSR output projection (kernel_fuseO.cu) as one kernel and as two
+    chained kernels: against the oracle, and bit for bit against each other."""
     import torch
     q, k, v = _qkv(et, 500 + seq, batch, seq, nhead, dh, dh)
     wo = et.synth.prune_tiles(et.synth.normal(500, 4, (em, nhead * dh), 0.05), 500, 5, sparsity)
