@@ -215,6 +215,35 @@ def test_attention_fuse_o(et, orc, cuda, batch, seq, nhead, dh, em, mask_kind, s
                  f"attention + tile O b{batch} s{seq} m{mask_kind}")
 
 
+def test_attention_fuse_o_work_order(et, cuda):
+    """The one-kernel form's per-ticket trace (test hook): every piece of work ran once, and no
+    projection item finished before the attention units whose rows it reads."""
+    import ctypes
+    import torch
+    batch, seq, nhead, dh, em = 24, 128, 12, 64, 768
+    q, k, v = _qkv(et, 640, batch, seq, nhead, dh, dh)
+    wo = et.synth.prune_tiles(et.synth.normal(640, 4, (em, nhead * dh), 0.05), 640, 5, 0.8)
+    rp, ro, tiles = et.synth.dense_to_tile(wo)
+    n_att, npanel = batch * nhead, em // 128
+    n_items = npanel * batch
+    trace = torch.zeros((n_att + n_items, 4), dtype=torch.int64, device=cuda)
+    L = et.lib()
+    L.et_debug_set_fuse_o_trace(ctypes.c_void_p(trace.data_ptr()))
+    try:
+        et.attention_fuse_o(_dev(q, cuda), _dev(k, cuda), _dev(v, cuda), _dev(rp, cuda), _dev(ro, cuda),
+                            _dev(tiles, cuda), None, batch, seq, nhead, dh, dh, em, 0,
+                            single_launch=True)
+        torch.cuda.synchronize()
+    finally:
+        L.et_debug_set_fuse_o_trace(ctypes.c_void_p(0))
+    assert et.device_error() == 0
+    t = trace.cpu().numpy()
+    assert (t[:, 0] > 0).all() and (t[:, 1] >= t[:, 0]).all(), "a piece of work left no record"
+    att_end = t[:n_att, 1].reshape(batch, nhead).max(axis=1)   # ticket = sequence * nhead + head
+    item_end = t[n_att:, 1].reshape(batch, npanel)             # item = token block * npanel + panel
+    assert (item_end > att_end[:, None]).all()
+
+
 @pytest.mark.parametrize("batch,seq,hidden,nhead", [
     (2, 128, 768, 12), (3, 100, 256, 4), (1, 16, 64, 1), (16, 128, 768, 12), (2, 72, 208, 2),
 ])
