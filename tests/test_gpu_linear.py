@@ -190,9 +190,12 @@ def test_tile_empty_block_rows(et, orc, cuda):
     assert_close(_host(y), orc.linear_dense(x, w, b, 0), "tile empty rows")
 
 
+@pytest.mark.parametrize("T,inn,out", [(300, 256, 512), (2048, 768, 3072), (77, 64, 4096)])
 @pytest.mark.parametrize("sparsity", [0.0, 0.5, 0.9])
-def test_row(et, orc, cuda, sparsity):
-    T, inn, out = 300, 256, 512
+def test_row(et, orc, cuda, sparsity, T, inn, out):
+    """Row-pruned Linear: kept features computed compressed into the head of each output row,
+    then spread in place (pruned columns receive act(bias)); the compressed form on its own."""
+    import torch
     x, w, b = _case(et, 31, T, inn, out)
     row_id = et.synth.choose_ids(31, 5, out, sparsity)
     rid, rows = et.synth.dense_to_row(w, row_id)
@@ -202,6 +205,20 @@ def test_row(et, orc, cuda, sparsity):
         assert_close(_host(y), orc.linear_row(x, rid, rows, out, b, act), f"row s={sparsity}")
     yc = et.linear_row_compressed(_dev(x, cuda), _dev(rid, cuda), _dev(rows, cuda), _dev(b, cuda))
     assert_close(_host(yc), orc.linear_row_compressed(x, rid, rows, b), "row compressed")
+    # the spread output holds exactly the compressed values in the kept columns
+    y0 = et.linear_row(_dev(x, cuda), _dev(rid, cuda), _dev(rows, cuda), out, _dev(b, cuda), 0)
+    assert torch.equal(y0[:, torch.from_numpy(rid.astype(np.int64)).to(cuda)], yc)
+
+
+def test_row_kept_count_not_a_multiple_of_8(et, orc, cuda):
+    """A kept list the 16-byte stores cannot serve takes the fill + scatter path."""
+    T, inn, out = 130, 128, 256
+    x, w, b = _case(et, 32, T, inn, out)
+    row_id = et.synth.choose_ids(32, 5, out, 0.5)[:-3]
+    rid, rows = et.synth.dense_to_row(w, row_id)
+    y = et.linear_row(_dev(x, cuda), _dev(rid, cuda), _dev(rows, cuda), out, _dev(b, cuda), 2)
+    assert et.device_error() == 0
+    assert_close(_host(y), orc.linear_row(x, rid, rows, out, b, 2), "row, 125 kept")
 
 
 @pytest.mark.parametrize("T,inn,out", [(260, 512, 256),      # a row of X fits a shared-memory line
