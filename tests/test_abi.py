@@ -109,3 +109,30 @@ def test_peer_exchange_argument_checks(et):
     assert lib.et_hp_signal_partial_fwd((ctypes.c_void_p * 2)(0x1000, 0x2010), 0, 2, 128, 768, 1, None) == -2
     assert lib.et_hp_allgather_rows_fwd(bufs, 0, 2, 128, 768, 1, 2, None) == -1
     assert lib.et_peer_buffer_open(None, None) == -1
+
+
+def test_attention_fuse_o_single_launch_argument_checks(et):
+    """The one-kernel attention + output projection rejects bad arguments before touching a
+    device (error codes of include/et_b200.h: -1 invalid argument, -2 alignment, -3 shape)."""
+    lib = et.lib()
+    fn = lib.et_attention_fuse_o_single_launch_fwd
+    P = ctypes.c_void_p
+    fn.argtypes = [P, P, P, P, P, P, P, P, ctypes.c_int, P, P] + [ctypes.c_int] * 10 + [P, ctypes.c_float, P]
+    ok = dict(Q=0x1000, K=0x2000, V=0x3000, mask=None, Z=0x4000, rp=0x5000, ro=0x6000, tiles=0x7000,
+              nnz=10, bias=None, out=0x8000, batch=1, seq=128, nhead=12, dh_qk=64, dh_v=64, ldq=768,
+              ldk=768, ldv=768, emdim=768, mask_kind=0, vl=None, scale=0.125, stream=None)
+
+    def call(**kw):
+        a = dict(ok, **kw)
+        return fn(*[a[k] for k in ok])
+
+    assert call(Z=None) == -1 and call(out=None) == -1
+    assert call(Q=None) == -1 and call(ro=None) == -1
+    assert call(mask_kind=7) == -1
+    assert call(mask_kind=2) == -1          # padding mask without lengths
+    assert call(scale=0.0) == -1
+    assert call(dh_qk=40) == -3             # head width not a multiple of 16
+    assert call(ldq=760) == -3              # row pitch narrower than the heads
+    assert call(emdim=770) == -3
+    assert call(Q=0x1008) == -2
+
