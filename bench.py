@@ -250,7 +250,7 @@ def main():
     ap.add_argument("--tile-only", action="store_true",
                     help="launch the tile-pruned Linear alone (2048 x 768 -> 3072, 80 %% of the "
                          "tiles pruned, three times) and exit: the small case profilers capture")
-    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "tile_qkv", "fuse_o", "layer"],
+    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "row", "tile_qkv", "fuse_o", "layer"],
                     help="launch one more small case three times and exit (for profilers): fused V.O "
                          "attention, the CTA-pair GEMM at 8192^3, skip-LayerNorm, the 1x16 vector "
                          "kernel, the column-pruned Linear (gather + GEMM), a tile-pruned Q/K/V projection "
@@ -334,6 +334,12 @@ def main():
             pk = et.PackedTiles(*et.synth.dense_to_tile(W), HIDDEN, 3 * HIDDEN, dev)
             x = rnd(1, (T, HIDDEN))
             fn = lambda: et.linear_tile_packed(x, pk, None, et.ACT_NONE)
+        elif args.only == "row":   # 8192 x 768 -> 3072, half of the output rows kept, full-width output
+            W = et.synth.normal_fast(1, 2, (FF, HIDDEN), 0.02)
+            ids = et.synth.choose_ids(1, 3, FF, 0.5)
+            rid, rows = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_row(W, ids))
+            x = rnd(1, (4 * T, HIDDEN))
+            fn = lambda: et.linear_row(x, rid, rows, FF, None, et.ACT_GELU)
         elif args.only == "fuse_o":  # attention + 80 %-pruned O projection in one kernel
             qkv = rnd(1, (T, 3 * HIDDEN))
             Wo = et.synth.prune_tiles(et.synth.normal_fast(1, 45, (HIDDEN, HIDDEN), 0.02), 1, 46, 0.8)

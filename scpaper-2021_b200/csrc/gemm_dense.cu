@@ -448,8 +448,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // full row: kept feature i moves to column row_id[i], every other column gets act(bias[c]).
 // Every warp owns a shared-memory image of one full output row, filled once with act(bias[c]):
 // the pruned columns never change.  For a row it drops the kept features into the image
-// (2-byte loads that are coalesced across the warp, 2-byte shared-memory stores at ascending
-// positions: next to no bank conflicts) and then writes the image out with 16-byte stores.
+// (4-byte loads that are coalesced across the warp, 2-byte shared-memory stores at ascending
+// positions: few bank conflicts) and then writes the image out with 16-byte stores.
 // The warps of a CTA walk rows independently (no CTA-wide barrier per row).  Shared memory:
 // nn * 4 + warps * out * 2 bytes.
 constexpr int EXPAND_WARPS = 8;
@@ -475,22 +475,28 @@ expand_rows_kernel(__half* __restrict__ Y, const int* __restrict__ row_id,
             *reinterpret_cast<uint4*>(image + c) = *reinterpret_cast<const uint4*>(last + c);
     pdl_wait();  // the tables above are weights; Y comes from the GEMM
     __syncthreads();
-    const unsigned short* Yu = reinterpret_cast<const unsigned short*>(Y);
     unsigned short* img = reinterpret_cast<unsigned short*>(image);
     for (int r = blockIdx.x * EXPAND_WARPS + warp; r < rows; r += gridDim.x * EXPAND_WARPS) {
         const size_t base = static_cast<size_t>(r) * out;
-        // batches of 32 loads per lane in flight (2 KB per warp) before the stores that need them
-        for (int i0 = 0; i0 < nn; i0 += 32 * 32) {
-            unsigned short v[32];
+        // pairs of kept features per load; a batch of 32 loads per lane (4 KB per warp: a whole
+        // row of up to 2048 kept features) is in flight before the stores that need them
+        const uint32_t* Yw = reinterpret_cast<const uint32_t*>(Y) + base / 2;
+        const int npair = nn >> 1;
+        for (int p0 = 0; p0 < npair; p0 += 32 * 32) {
+            uint32_t v[32];
 #pragma unroll
             for (int u = 0; u < 32; ++u) {
-                const int i = i0 + u * 32 + lane;
-                v[u] = i < nn ? __ldcg(Yu + base + i) : static_cast<unsigned short>(0);
+                const int p = p0 + u * 32 + lane;
+                v[u] = p < npair ? __ldcg(Yw + p) : 0u;
             }
 #pragma unroll
             for (int u = 0; u < 32; ++u) {
-                const int i = i0 + u * 32 + lane;
-                if (i < nn) img[sid[i]] = v[u];
+                const int p = p0 + u * 32 + lane;
+                if (p < npair) {
+                    const int2 ids = *reinterpret_cast<const int2*>(sid + 2 * p);
+                    img[ids.x] = static_cast<unsigned short>(v[u] & 0xffffu);
+                    img[ids.y] = static_cast<unsigned short>(v[u] >> 16);
+                }
             }
         }
         __syncwarp();  // every kept feature of the row has been read before the row is overwritten
@@ -995,7 +1001,7 @@ int et_linear_row_fwd(const int32_t* row_id, const et_half* rows, int nn_row,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Kept features first, compressed, into the head of every row of Y (coalesced tile stores),
     // then one in-place pass that spreads them and fills the pruned columns.  Measured on B200
-    // with half the rows kept: 2048 x 768 -> 3072 in 18 us and 12288 x 1024 -> 4096 in 100 us,
+    // with half the rows kept: 2048 x 768 -> 3072 in 17 us and 12288 x 1024 -> 4096 in 95 us,
     // against 61 us and 324 us for a bias fill of Y followed by a GEMM whose epilogue scatters
     // single elements (dense GEMM: 12.4 / 82 us; three quarters pruned: 51 us for the larger
     // shape).  Consumers that accept the compressed layout (et_linear_row_compressed_fwd, what
