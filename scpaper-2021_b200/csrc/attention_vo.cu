@@ -23,8 +23,11 @@ constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int VO_THREADS = 192;
 constexpr int ATOM_BYTES = 128 * 128;
-constexpr int MAX_NC = 256;  // output features per CTA
-constexpr int VO_TMEM_COLS = 512;
+// NC output features per CTA: 256, or 128 / 64 behind a test hook.  A CTA recomputes the scores
+// and the softmax of every head whatever its width, so narrower chunks do more work in total
+// and spread it over more CTAs.  Tensor memory: scores in columns [0, 128), the accumulator
+// behind them.
+__host__ __device__ constexpr int vo_tmem_cols(int nc) { return nc <= 128 ? 256 : 512; }
 
 struct VoArgs {
     __half* out;
@@ -37,7 +40,8 @@ struct VoArgs {
     int* err_word;
 };
 
-__global__ void __launch_bounds__(VO_THREADS, 1)
+template <int NC>
+__global__ void __launch_bounds__(VO_THREADS, (NC <= 128 ? 2 : 1))
 attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmVO, const VoArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -48,7 +52,7 @@ attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + nqa * ATOM_BYTES;
     uint8_t* sVO = sK + nqa * ATOM_BYTES;
-    uint8_t* sP = sVO + (MAX_NC / 64) * ATOM_BYTES;
+    uint8_t* sP = sVO + (NC / 64) * ATOM_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATOM_BYTES);
     uint64_t* qk_full = bars + 0;
     uint64_t* qk_empty = bars + 1;
@@ -64,9 +68,9 @@ attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * BQ;
-    const int e0 = blockIdx.y * MAX_NC;
+    const int e0 = blockIdx.y * NC;
     const int b = blockIdx.z;
-    const int n_c = (a.emdim - e0) < MAX_NC ? (a.emdim - e0) : MAX_NC;  // multiple of 16
+    const int n_c = (a.emdim - e0) < NC ? (a.emdim - e0) : NC;  // multiple of 16
     const int nca = (n_c + 63) >> 6;
 
     int kv_len = a.seq;
@@ -95,7 +99,7 @@ attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, VO_TMEM_COLS);
+        tmem_alloc(tmem_slot, vo_tmem_cols(NC));
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -351,13 +355,15 @@ attention_vo_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, VO_TMEM_COLS);
+    if (warp == 1) tmem_dealloc(tmem_base, vo_tmem_cols(NC));
 }
 
 }  // namespace
 }  // namespace et
 
 namespace et {
+
+int g_vo_chunk = 0;  // test hook: 64 / 128 / 256 output features per CTA, 0 = automatic
 
 // out[t, c] = bias[c] (0 without a bias) for every element.
 __global__ void vo_fill_bias_kernel(__half* __restrict__ out, const __half* __restrict__ bias, int T,
@@ -425,17 +431,6 @@ int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half*
     if ((st = make(&tmK, K, ldk, nhead * dh_qk, batch)) != ET_OK) return st;
     if ((st = make(&tmVO, VO, emdim, emdim, batch * nhead)) != ET_OK) return st;
 
-    const int nqa = (dh_qk + 63) / 64;
-    const int smem_bytes = (2 * nqa + MAX_NC / 64 + 2) * ATOM_BYTES + 256 + 1024;
-    static std::atomic<bool> attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_vo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (2 * 2 + MAX_NC / 64 + 2) * ATOM_BYTES + 256 + 1024) != cudaSuccess)
-            return ET_ERR_CUDA;
-        attr_set[dev] = true;
-    }
     VoArgs a;
     a.out = reinterpret_cast<__half*>(out);
     a.bias_o = reinterpret_cast<const __half*>(bias_o);
@@ -449,12 +444,41 @@ int et_fused_vo_attention_fwd(const et_half* Q, const et_half* K, const et_half*
     a.mask_kind = mask_kind;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.err_word = err;
-    dim3 grid((seq + BQ - 1) / BQ, (emdim + MAX_NC - 1) / MAX_NC, batch);
-    return launch_kernel(attention_vo_kernel, grid, dim3(VO_THREADS), smem_bytes,
-                         static_cast<cudaStream_t>(stream), tmQ, tmK, tmVO, a) == cudaSuccess
-               ? ET_OK
-               : ET_ERR_CUDA;
+    // Measured on B200 (12 heads, 768 features; 256 / 128 / 64 features per CTA): 16 x 128 tokens
+    // 188 / 195 / 202 us, 64 x 128 376 / 385 / 603, 4 x 512 762 / 794 / 829, 1 x 4096 6.1 / 6.6 /
+    // 12.5 ms, and 181-186 us for a single 128-token sequence whatever the width: a CTA's time is
+    // set by its serial walk over the heads (about 15 us per head and key block with one set of
+    // buffers), not by how many CTAs there are, so the widest chunk runs unless the test hook
+    // asks for another.
+    int nc = 256;
+    if (g_vo_chunk == 64 || g_vo_chunk == 128) nc = g_vo_chunk;
+    const int nqa = (dh_qk + 63) / 64;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto go = [&](auto kern, int slot, int width) -> int {
+        const int smem_bytes = (2 * nqa + width / 64 + 2) * ATOM_BYTES + 256 + 1024;
+        static std::atomic<bool> attr_set[3][64] = {};
+        if (dev >= 0 && dev < 64 && !attr_set[slot][dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (2 * 2 + width / 64 + 2) * ATOM_BYTES + 256 + 1024) != cudaSuccess)
+                return ET_ERR_CUDA;
+            attr_set[slot][dev] = true;
+        }
+        dim3 grid((seq + BQ - 1) / BQ, (emdim + width - 1) / width, batch);
+        return launch_kernel(kern, grid, dim3(VO_THREADS), smem_bytes,
+                             static_cast<cudaStream_t>(stream), tmQ, tmK, tmVO, a) == cudaSuccess
+                   ? ET_OK
+                   : ET_ERR_CUDA;
+    };
+    if (nc == 64) return go(attention_vo_kernel<64>, 0, 64);
+    if (nc == 128) return go(attention_vo_kernel<128>, 1, 128);
+    return go(attention_vo_kernel<256>, 2, 256);
 }
+
+#ifdef ET_TEST_HOOKS
+// Test hook: output features per CTA of the pre-multiplied V.O attention (64 / 128 / 256), 0 = automatic.
+void et_debug_set_vo_chunk(int nc) { et::g_vo_chunk = nc; }
+#endif  // ET_TEST_HOOKS
 
 // ---- column-pruned V.O (Linear_VO_prune + Fused_prune_Multihead_attention) -----------------
 // The pre-multiplied weight keeps only the output features col_id[0 .. nnz_col): VO_c is

@@ -170,8 +170,21 @@ def test_fused_vo_attention(et, orc, cuda, batch, seq, nhead, dh, emdim, mask_ki
                  dump=f"fusedvo_{seq}_{emdim}_{mask_kind}")
     out2 = et.fused_vo_attention(_dev(q, cuda), _dev(k, cuda), vo, _dev(bo, cuda), batch, seq,
                                  nhead, dh, emdim, mask_kind)
+    import ctypes
     import torch
     assert torch.equal(out, out2), "head reduction must be deterministic"
+    # every width of the output chunk a CTA owns gives the same bits (heads are reduced in the
+    # same order inside every accumulator column)
+    L = et.lib()
+    try:
+        for nc in (64, 128, 256):
+            L.et_debug_set_vo_chunk(ctypes.c_int(nc))
+            o = et.fused_vo_attention(_dev(q, cuda), _dev(k, cuda), vo, _dev(bo, cuda), batch, seq,
+                                      nhead, dh, emdim, mask_kind)
+            assert et.device_error() == 0
+            assert torch.equal(out, o), f"chunk width {nc}"
+    finally:
+        L.et_debug_set_vo_chunk(ctypes.c_int(0))
 
 
 @pytest.mark.parametrize("batch,seq,nhead,dh,em,mask_kind,sparsity", [
