@@ -250,7 +250,7 @@ def main():
     ap.add_argument("--tile-only", action="store_true",
                     help="launch the tile-pruned Linear alone (2048 x 768 -> 3072, 80 %% of the "
                          "tiles pruned, three times) and exit: the small case profilers capture")
-    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "row", "tile_qkv", "fuse_o", "layer"],
+    ap.add_argument("--only", default="", choices=["", "vo", "pair", "layernorm", "1x16", "col", "row", "tile_qkv", "fuse_o", "hp_reduce", "layer"],
                     help="launch one more small case three times and exit (for profilers): fused V.O "
                          "attention, the CTA-pair GEMM at 8192^3, skip-LayerNorm, the 1x16 vector "
                          "kernel, the column-pruned Linear (gather + GEMM), a tile-pruned Q/K/V projection "
@@ -340,6 +340,23 @@ def main():
             rid, rows = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_row(W, ids))
             x = rnd(1, (4 * T, HIDDEN))
             fn = lambda: et.linear_row(x, rid, rows, FF, None, et.ACT_GELU)
+        elif args.only == "hp_reduce":  # head-parallel exchange, 8 ranks emulated on this GPU
+            # one 4096-token sequence: every rank publishes its partial, then rank 0 pulls its
+            # 512 rows of all eight partials, adds the residual, normalises and stores the rows
+            # into every rank's buffer (all buffers live on this GPU: local HBM, not NVLink)
+            exs = et.PeerExchange.local(8, 4096, HIDDEN)
+            x = rnd(1, (4096, HIDDEN))
+            gma = torch.ones(HIDDEN, dtype=torch.float16, device=dev)
+            for r, ex in enumerate(exs):
+                part = et.device_view(ex.partial(), (4096, HIDDEN), dev)
+                part.copy_(rnd(10 + r, (4096, HIDDEN), 0.3))
+
+            def fn():
+                for ex in exs:
+                    ex.epoch += 1
+                    ex.signal()
+                for ex in exs:
+                    ex.reduce_layernorm(x, None, gma, gma)
         elif args.only == "fuse_o":  # attention + 80 %-pruned O projection in one kernel
             qkv = rnd(1, (T, 3 * HIDDEN))
             Wo = et.synth.prune_tiles(et.synth.normal_fast(1, 45, (HIDDEN, HIDDEN), 0.02), 1, 46, 0.8)
