@@ -65,7 +65,7 @@ struct FuseOArgs {
     int* done;    // [batch][nqb] counters, zero at launch; the last CTA to finish zeroes them
     int* exited;  // CTAs that have finished, zero at launch
     int* ticket;  // next piece of work to hand out, zero at launch
-    unsigned long long* trace;  // bring-up builds: [ticket][4] = start ns, end ns, SM, CTA (else null)
+    unsigned long long* trace;  // test hook: [ticket][4] = start ns, end ns, SM, CTA (null: no trace)
     int n_done;   // batch * nqb
     int nqb;      // 128-query blocks per sequence
     int n_att;    // batch * nqb * nhead attention units
