@@ -622,6 +622,21 @@ def main():
             per_kernel["attention_fuse_o_tile80"] = {
                 "single_launch_us": fo[True], "two_chained_kernels_us": fo[False],
                 "product_path": "two chained kernels"}
+            # row-pruned Linear at the FFN1 shape, half of the output features kept: full-width
+            # output (compressed GEMM + in-place expand) and compressed output
+            ids_r = et.synth.choose_ids(1, 47, FF, 0.5)
+            Wr = et.synth.normal_fast(1, 48, (FF, HIDDEN), 0.02)
+            rid_r, rows_r = (torch.from_numpy(v).to(dev) for v in et.synth.dense_to_row(Wr, ids_r))
+            xr = [rnd(10 + i, (T, HIDDEN), 1.0) for i in range(NSETS)]
+            b_ff = torch.zeros(FF, dtype=torch.float16, device=dev)
+            t_full = time_kernel([lambda i=i: et.linear_row(xr[i], rid_r, rows_r, FF, b_ff, et.ACT_GELU)
+                                  for i in range(NSETS)]) * 1e6
+            t_comp = time_kernel([lambda i=i: et.linear_row_compressed(xr[i], rid_r, rows_r, b_ff)
+                                  for i in range(NSETS)]) * 1e6
+            per_kernel["ffn1_row_pruned_half"] = {
+                "full_width_output_us": t_full, "compressed_output_us": t_comp,
+                "dense_us": per_kernel["ffn1_gelu"]["us"], "kept_features": int(len(ids_r))}
+            del xr
             per_kernel["note"] = ("each kernel timed inside one CUDA graph that rotates over buffer "
                                   "sets larger than L2")
             del a, w, y, qkv, z, o
